@@ -1,0 +1,153 @@
+// Host-side preparation of one weight layer for the sm_100a layer kernel.
+//
+// Takes the role of the reference's per-layer inspector pass (src/network.cpp:97-121:
+// COOMatrix -> reorder -> CSRCSCMatrix -> BlockContainer -> MaxInReuseBSchedule::get_data,
+// src/inspector/gpu_block_scheduler.h:160-171) but makes no assumption on the pattern:
+// any CSC goes in.  What it derives:
+//   * per column the input rows in ascending order (the summation order of the reference's
+//     CPU loop, src/utils/cpu_spmm.h:12-43), padded to a common K that is a multiple of 4;
+//   * column classes: columns with identical (rows, weights) produce identical outputs, so
+//     each class is computed once and stored to all its member columns.  The challenge
+//     networks have 16 such columns per class (the 16-wide blocks the reference's
+//     n16384_l11_kernel shares its gathered rows over, all_network.cu:134-149);
+//   * whether all weights are one power-of-two constant w: then sum(y*w) == w*sum(y) bit for
+//     bit in fp32 (scaling by 2^e commutes with rounding), and the kernel adds first.
+#pragma once
+
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+namespace spdnn_impl {
+
+struct PreparedLayer {
+    int n = 0;               // neurons
+    int k = 0;               // padded entries per class (multiple of 4)
+    int classes = 0;         // U
+    bool uniform = false;    // all weights == w, w a power of two
+    float w = 0.0f;
+    bool identity_members = false;      // class u == column u (no two columns alike)
+    std::vector<int32_t> off;           // [U][k] input row * 32 (element offset inside a tile); padding -> row n (always zero)
+    std::vector<float> vals;            // [U][k] (empty when uniform); padding 0
+    std::vector<int32_t> mem_ptr;       // [U+1]
+    std::vector<int32_t> mem;           // member column * 32, classes in order of their first column
+    int64_t nnz = 0;
+    uint64_t content_hash = 0;          // of the canonical (sorted) layer, for sharing equal layers
+    uint64_t content_hash2 = 0;         // independent second hash (128 bits together)
+};
+
+inline uint64_t mix64(uint64_t x) {
+    x ^= x >> 30; x *= 0xBF58476D1CE4E5B9ull;
+    x ^= x >> 27; x *= 0x94D049BB133111EBull;
+    x ^= x >> 31;
+    return x;
+}
+
+inline bool is_pow2_float(float w) {
+    if (!(w > 0.0f) || !std::isfinite(w)) return false;
+    int e;
+    return std::frexp(w, &e) == 0.5f;
+}
+
+// Returns an empty string on success, else the reason the layer is rejected.
+inline std::string prepare_layer(int n, const int32_t *col_ptr, const int32_t *row_idx, const float *val,
+                                 PreparedLayer &out) {
+    if (n <= 0 || n > (1 << 26)) return "neurons must be in [1, 2^26]";
+    if (!col_ptr || !row_idx) return "col_ptr/row_idx is null";
+    if (col_ptr[0] != 0) return "col_ptr[0] must be 0";
+    int kmax = 0;
+    for (int c = 0; c < n; ++c) {
+        int64_t cnt = (int64_t)col_ptr[c + 1] - col_ptr[c];
+        if (cnt < 0) return "col_ptr must be non-decreasing";
+        if (cnt > 4096) return "more than 4096 non-zeros in one column is not supported";
+        kmax = std::max<int>(kmax, (int)cnt);
+    }
+    const int64_t nnz = col_ptr[n];
+    const int k = std::max(4, (kmax + 3) / 4 * 4);
+    const float w0 = val ? (nnz ? val[0] : 0.0625f) : 0.0625f;
+    bool uniform = is_pow2_float(w0);
+
+    // canonical per-column lists: ascending row, stable for equal rows (duplicates are kept
+    // as separate terms, as a COO with repeated entries would be summed)
+    std::vector<int32_t> rows((size_t)n * k, n);
+    std::vector<float> vals((size_t)n * k, 0.0f);
+    std::vector<std::pair<int32_t, float>> tmp;
+    for (int c = 0; c < n; ++c) {
+        const int s = col_ptr[c], e = col_ptr[c + 1];
+        tmp.clear();
+        for (int i = s; i < e; ++i) {
+            const int32_t r = row_idx[i];
+            if (r < 0 || r >= n) return "row index out of range in column " + std::to_string(c);
+            const float v = val ? val[i] : 0.0625f;
+            if (v != w0) uniform = false;
+            tmp.emplace_back(r, v);
+        }
+        std::stable_sort(tmp.begin(), tmp.end(),
+                         [](const std::pair<int32_t, float> &a, const std::pair<int32_t, float> &b) { return a.first < b.first; });
+        for (size_t i = 0; i < tmp.size(); ++i) {
+            rows[(size_t)c * k + i] = tmp[i].first;
+            vals[(size_t)c * k + i] = tmp[i].second;
+        }
+    }
+
+    // classes of identical columns
+    std::unordered_map<uint64_t, std::vector<int>> by_hash;   // hash -> class ids
+    std::vector<int> class_of(n), first_col;
+    by_hash.reserve((size_t)n * 2);
+    uint64_t layer_hash = mix64(0x5EEDull ^ (uint64_t)n ^ ((uint64_t)k << 32));
+    uint64_t layer_hash2 = mix64(0xC0FFEEull + (uint64_t)n * 31 + (uint64_t)k);
+    for (int c = 0; c < n; ++c) {
+        uint64_t h = 0x9E3779B97F4A7C15ull;
+        const int32_t *r = &rows[(size_t)c * k];
+        const float *v = &vals[(size_t)c * k];
+        for (int i = 0; i < k; ++i) {
+            uint32_t vb;
+            std::memcpy(&vb, &v[i], 4);
+            h = mix64(h ^ (((uint64_t)(uint32_t)r[i] << 32) | vb));
+        }
+        layer_hash = mix64(layer_hash ^ h);     // order-dependent chain over columns
+        layer_hash2 = mix64(layer_hash2 + h * 0x9E3779B97F4A7C15ull + (uint64_t)c);
+        auto &cands = by_hash[h];
+        int found = -1;
+        for (int cls : cands) {
+            const int fc = first_col[cls];
+            if (!std::memcmp(r, &rows[(size_t)fc * k], sizeof(int32_t) * k) &&
+                !std::memcmp(v, &vals[(size_t)fc * k], sizeof(float) * k)) { found = cls; break; }
+        }
+        if (found < 0) {
+            found = (int)first_col.size();
+            first_col.push_back(c);
+            cands.push_back(found);
+        }
+        class_of[c] = found;
+    }
+    const int u = (int)first_col.size();
+
+    out = PreparedLayer();
+    out.n = n; out.k = k; out.classes = u; out.uniform = uniform; out.w = w0; out.nnz = nnz;
+    out.content_hash = layer_hash;
+    out.content_hash2 = layer_hash2;
+    out.identity_members = (u == n);
+    out.off.resize((size_t)u * k);
+    if (!uniform) out.vals.resize((size_t)u * k);
+    for (int cls = 0; cls < u; ++cls) {
+        const int fc = first_col[cls];
+        for (int i = 0; i < k; ++i) {
+            out.off[(size_t)cls * k + i] = rows[(size_t)fc * k + i] * 32;
+            if (!uniform) out.vals[(size_t)cls * k + i] = vals[(size_t)fc * k + i];
+        }
+    }
+    out.mem_ptr.assign(u + 1, 0);
+    for (int c = 0; c < n; ++c) out.mem_ptr[class_of[c] + 1]++;
+    for (int cls = 0; cls < u; ++cls) out.mem_ptr[cls + 1] += out.mem_ptr[cls];
+    out.mem.resize(n);
+    std::vector<int32_t> fill(out.mem_ptr.begin(), out.mem_ptr.end() - 1);
+    for (int c = 0; c < n; ++c) out.mem[fill[class_of[c]]++] = c * 32;
+    return std::string();
+}
+
+}  // namespace spdnn_impl

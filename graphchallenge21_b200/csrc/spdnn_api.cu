@@ -1,0 +1,601 @@
+// C ABI of the sm_100a sparse-DNN inference path (declarations: include/spdnn_b200.h).
+//
+// Host side of what the reference does in ftxj::test_benchmark_graph_challenge
+// (src/microbenchmark/all_network.cu:207-526): own the device buffers, upload layers and
+// inputs, run the layer loop, hand back survivors.  Differences that matter to a caller:
+// errors come back as status codes instead of exit() (src/gpu_lib/gpu_runtime.h:6-17), the
+// layer loop has no host round-trip (the reference synchronises and copies active[] every
+// layer, all_network.cu:444-510) and is replayed from one CUDA graph, and everything
+// allocated is freed by spdnn_destroy.
+#include "../../include/spdnn_b200.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <memory>
+#include <new>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "layer_inspect.h"
+#include "spdnn_kernels.cuh"
+
+using namespace spdnn_impl;
+
+namespace {
+
+struct DevLayer {
+    int32_t *off = nullptr;
+    float *vals = nullptr;
+    int32_t *mem_ptr = nullptr;
+    int32_t *mem = nullptr;
+    int classes = 0, k = 0;
+    bool uniform = false, identity_members = false;
+    float w = 0.0f;
+    int64_t nnz = 0;
+    uint64_t h1 = 0, h2 = 0;
+    int device = 0;
+    ~DevLayer() {
+        cudaSetDevice(device);
+        cudaFree(off); cudaFree(vals); cudaFree(mem_ptr); cudaFree(mem);
+    }
+};
+
+}  // namespace
+
+struct spdnn {
+    int device = 0, n = 0, layers = 0;
+    float bias = 0.0f, clip = 32.0f;
+    int sm_count = 0;
+    cudaStream_t own_stream = nullptr, stream = nullptr;
+    cudaEvent_t ev_prep0 = nullptr, ev_prep1 = nullptr, ev_inf0 = nullptr, ev_inf1 = nullptr;
+
+    std::vector<std::shared_ptr<DevLayer>> layer;
+    std::unordered_map<uint64_t, std::weak_ptr<DevLayer>> shared;   // content hash -> layer
+
+    long long tile_stride = 0;
+    int tiles_cap = 0;
+    float *y[2] = {nullptr, nullptr};
+    LoopCtl *ctl = nullptr;            // layers + 1 records
+    int32_t *slot = nullptr;
+    uint32_t *mask = nullptr;
+    int32_t *ids[2] = {nullptr, nullptr};
+    unsigned int *counter = nullptr;
+    int32_t *status = nullptr;
+
+    void *stage = nullptr;             // device staging for host inputs / outputs
+    size_t stage_bytes = 0;
+
+    int batch = 0, first_id = 0;
+    bool input_ready = false, result_ready = false, in_flight = false, prep_timed = false;
+    cudaGraphExec_t graph_exec = nullptr;
+    bool graph_dirty = true;
+    int cpi_override = 0, grid_override = 0;
+
+    std::vector<LoopCtl> host_ctl;
+    spdnn_stats_t stats{};
+    int64_t prep_launches = 0;
+    std::string err;
+};
+
+namespace {
+
+int fail(spdnn *c, int code, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (c) c->err = buf;
+    return code;
+}
+
+#define CK(call)                                                                                      \
+    do {                                                                                              \
+        cudaError_t e__ = (call);                                                                     \
+        if (e__ != cudaSuccess)                                                                       \
+            return fail(c, SPDNN_ERR_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e__),   \
+                        __FILE__, __LINE__);                                                          \
+    } while (0)
+
+int free_buffers(spdnn *c) {
+    cudaFree(c->y[0]); cudaFree(c->y[1]); cudaFree(c->slot); cudaFree(c->mask);
+    cudaFree(c->ids[0]); cudaFree(c->ids[1]);
+    c->y[0] = c->y[1] = nullptr; c->slot = nullptr; c->mask = nullptr; c->ids[0] = c->ids[1] = nullptr;
+    c->tiles_cap = 0;
+    return SPDNN_OK;
+}
+
+int ensure_capacity(spdnn *c, int batch) {
+    const int tiles = (batch + 31) / 32;
+    if (tiles <= c->tiles_cap) return SPDNN_OK;
+    free_buffers(c);
+    c->graph_dirty = true;
+    const size_t ybytes = (size_t)tiles * (size_t)c->tile_stride * sizeof(float);
+    for (int i = 0; i < 2; ++i) {
+        CK(cudaMalloc(&c->y[i], ybytes));
+        CK(cudaMemsetAsync(c->y[i], 0, ybytes, c->stream));      // incl. the permanent zero row of every tile
+        CK(cudaMalloc(&c->ids[i], sizeof(int32_t) * (size_t)tiles * 32));
+    }
+    CK(cudaMalloc(&c->slot, sizeof(int32_t) * (size_t)tiles * 32));
+    CK(cudaMalloc(&c->mask, sizeof(uint32_t) * (size_t)tiles));
+    CK(cudaMemsetAsync(c->mask, 0, sizeof(uint32_t) * (size_t)tiles, c->stream));
+    c->tiles_cap = tiles;
+    return SPDNN_OK;
+}
+
+int ensure_stage(spdnn *c, size_t bytes) {
+    if (bytes <= c->stage_bytes) return SPDNN_OK;
+    CK(cudaStreamSynchronize(c->stream));
+    cudaFree(c->stage);
+    c->stage = nullptr; c->stage_bytes = 0;
+    CK(cudaMalloc(&c->stage, bytes));
+    c->stage_bytes = bytes;
+    return SPDNN_OK;
+}
+
+int begin_input(spdnn *c, int batch, int first_global_id) {
+    if (batch < 0) return fail(c, SPDNN_ERR_ARG, "batch must be >= 0");
+    if ((long long)first_global_id + batch > 0x7fffffffLL || first_global_id < 0)
+        return fail(c, SPDNN_ERR_ARG, "global image numbers must fit in int32");
+    if (c->in_flight) {
+        int rc = spdnn_sync(c, nullptr);
+        if (rc) return rc;
+    }
+    int rc = ensure_capacity(c, batch > 0 ? batch : 1);
+    if (rc) return rc;
+    c->batch = batch;
+    c->first_id = first_global_id;
+    c->input_ready = false;
+    c->result_ready = false;
+    c->prep_launches = 0;
+    CK(cudaEventRecord(c->ev_prep0, c->stream));
+    return SPDNN_OK;
+}
+
+int end_input(spdnn *c) {
+    init_loop_kernel<<<std::max(1, std::min(1024, (c->batch + 255) / 256)), 256, 0, c->stream>>>(
+        c->ctl, c->ids[0], c->batch, c->first_id);
+    CK(cudaGetLastError());
+    c->prep_launches += 1;
+    CK(cudaEventRecord(c->ev_prep1, c->stream));
+    c->prep_timed = true;
+    c->input_ready = true;
+    return SPDNN_OK;
+}
+
+int convert_dense_device(spdnn *c, const float *dev_rows, int rows, int first_tile) {
+    // rows is a multiple of 32 except for the last chunk
+    const dim3 block(32, 8), grid((rows + 31) / 32, (c->n + 31) / 32);
+    if (rows <= 0) return SPDNN_OK;
+    dense_to_tiles_kernel<<<grid, block, 0, c->stream>>>(dev_rows, c->y[0], c->n, rows, c->tile_stride, first_tile);
+    CK(cudaGetLastError());
+    c->prep_launches += 1;
+    return SPDNN_OK;
+}
+
+template <int KT, bool UNIFORM>
+int launch_layer_t(spdnn *c, const LayerDesc &d, const LayerArgs &a, int grid) {
+    layer_kernel<KT, UNIFORM><<<grid, kThreads, 0, c->stream>>>(d, a);
+    CK(cudaGetLastError());
+    return SPDNN_OK;
+}
+
+int launch_layer(spdnn *c, const LayerDesc &d, const LayerArgs &a, int grid, bool uniform) {
+    if (d.k == 32) return uniform ? launch_layer_t<32, true>(c, d, a, grid) : launch_layer_t<32, false>(c, d, a, grid);
+    return uniform ? launch_layer_t<0, true>(c, d, a, grid) : launch_layer_t<0, false>(c, d, a, grid);
+}
+
+template <int KT, bool UNIFORM>
+int blocks_per_sm_t() {
+    int b = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b, layer_kernel<KT, UNIFORM>, kThreads, 0) != cudaSuccess) b = 1;
+    return b > 0 ? b : 1;
+}
+
+int blocks_per_sm(int k, bool uniform) {
+    if (k == 32) return uniform ? blocks_per_sm_t<32, true>() : blocks_per_sm_t<32, false>();
+    return uniform ? blocks_per_sm_t<0, true>() : blocks_per_sm_t<0, false>();
+}
+
+int enqueue_layers(spdnn *c) {
+    for (int l = 0; l < c->layers; ++l) {
+        const DevLayer &L = *c->layer[l];
+        LayerDesc d;
+        d.off = L.off; d.vals = L.vals;
+        d.mem_ptr = L.identity_members ? nullptr : L.mem_ptr;
+        d.mem = L.mem;
+        d.classes = L.classes; d.k = L.k; d.w = L.w;
+        // Work item = (tile, block of classes).  Without duplicate columns every input row is
+        // used by ~K classes: keep a whole tile in one block when it fits the L1 so those
+        // re-reads hit there; otherwise small items for balance.
+        int cpi = 32;
+        if (L.identity_members && (size_t)c->tile_stride * 4 <= (size_t)160 * 1024) cpi = L.classes;
+        if (c->cpi_override > 0) cpi = c->cpi_override;
+        d.classes_per_item = std::max(1, std::min(cpi, L.classes));
+        LayerArgs a;
+        a.yin = c->y[l & 1]; a.yout = c->y[(l & 1) ^ 1];
+        a.tile_stride = c->tile_stride;
+        a.ctl_in = c->ctl + l; a.ctl_out = c->ctl + l + 1;
+        a.slot = c->slot; a.mask = c->mask; a.ids0 = c->ids[0]; a.ids1 = c->ids[1];
+        a.counter = c->counter; a.status = c->status;
+        a.bias = c->bias; a.clip = c->clip;
+        int grid = c->grid_override > 0 ? c->grid_override : c->sm_count * blocks_per_sm(L.k, L.uniform);
+        int rc = launch_layer(c, d, a, grid, L.uniform);
+        if (rc) return rc;
+    }
+    return SPDNN_OK;
+}
+
+int build_graph(spdnn *c) {
+    if (c->graph_exec) { cudaGraphExecDestroy(c->graph_exec); c->graph_exec = nullptr; }
+    cudaGraph_t g = nullptr;
+    CK(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+    int rc = enqueue_layers(c);
+    cudaError_t e = cudaStreamEndCapture(c->stream, &g);
+    if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+    if (e != cudaSuccess) return fail(c, SPDNN_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+    e = cudaGraphInstantiate(&c->graph_exec, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return fail(c, SPDNN_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
+    c->graph_dirty = false;
+    return SPDNN_OK;
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) { cudaGetDevice(&prev); cudaSetDevice(dev); }
+    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+}  // namespace
+
+extern "C" {
+
+const char *spdnn_version(void) { return "spdnn_b200 0.1 (sm_100a)"; }
+
+const char *spdnn_last_error(const spdnn_t *c) { return c ? c->err.c_str() : "null context"; }
+
+int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias, float clip) {
+    if (!out) return SPDNN_ERR_ARG;
+    *out = nullptr;
+    spdnn *c = new (std::nothrow) spdnn();
+    if (!c) return SPDNN_ERR_MEMORY;
+    *out = c;   // returned even on failure so that the caller can read the message; destroy it either way
+    if (neurons <= 0 || neurons > (1 << 26)) return fail(c, SPDNN_ERR_ARG, "neurons must be in [1, 2^26]");
+    if (layers <= 0) return fail(c, SPDNN_ERR_ARG, "layers must be positive");
+    if (!(clip > 0.0f)) return fail(c, SPDNN_ERR_ARG, "clip must be positive");
+    int count = 0;
+    CK(cudaGetDeviceCount(&count));
+    if (device < 0 || device >= count) return fail(c, SPDNN_ERR_ARG, "device %d not present (%d devices)", device, count);
+    c->device = device; c->n = neurons; c->layers = layers; c->bias = bias; c->clip = clip;
+    c->tile_stride = ((long long)neurons + 1) * 32;
+    DeviceGuard guard(device);
+    cudaDeviceProp prop;
+    CK(cudaGetDeviceProperties(&prop, device));
+    c->sm_count = prop.multiProcessorCount;
+    CK(cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking));
+    c->stream = c->own_stream;
+    CK(cudaEventCreate(&c->ev_prep0)); CK(cudaEventCreate(&c->ev_prep1));
+    CK(cudaEventCreate(&c->ev_inf0)); CK(cudaEventCreate(&c->ev_inf1));
+    c->layer.resize(layers);
+    CK(cudaMalloc(&c->ctl, sizeof(LoopCtl) * (size_t)(layers + 1)));
+    CK(cudaMemset(c->ctl, 0, sizeof(LoopCtl) * (size_t)(layers + 1)));
+    CK(cudaMalloc(&c->counter, sizeof(unsigned int)));
+    CK(cudaMemset(c->counter, 0, sizeof(unsigned int)));
+    CK(cudaMalloc(&c->status, sizeof(int32_t)));
+    CK(cudaMemset(c->status, 0, sizeof(int32_t)));
+    c->host_ctl.resize(layers + 1);
+    if (const char *e = getenv("SPDNN_CLASSES_PER_ITEM")) c->cpi_override = atoi(e);
+    if (const char *e = getenv("SPDNN_GRID")) c->grid_override = atoi(e);
+    return SPDNN_OK;
+}
+
+void spdnn_destroy(spdnn_t *c) {
+    if (!c) return;
+    DeviceGuard guard(c->device);
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    if (c->graph_exec) cudaGraphExecDestroy(c->graph_exec);
+    free_buffers(c);
+    cudaFree(c->ctl); cudaFree(c->counter); cudaFree(c->status); cudaFree(c->stage);
+    c->layer.clear();
+    if (c->ev_prep0) cudaEventDestroy(c->ev_prep0);
+    if (c->ev_prep1) cudaEventDestroy(c->ev_prep1);
+    if (c->ev_inf0) cudaEventDestroy(c->ev_inf0);
+    if (c->ev_inf1) cudaEventDestroy(c->ev_inf1);
+    if (c->own_stream) cudaStreamDestroy(c->own_stream);
+    delete c;
+}
+
+int spdnn_set_stream(spdnn_t *c, void *cuda_stream) {
+    if (!c) return SPDNN_ERR_ARG;
+    DeviceGuard guard(c->device);
+    if (c->in_flight) {
+        int rc = spdnn_sync(c, nullptr);
+        if (rc) return rc;
+    }
+    CK(cudaStreamSynchronize(c->stream));
+    c->stream = cuda_stream ? (cudaStream_t)cuda_stream : c->own_stream;
+    c->graph_dirty = true;    // the graph is re-captured on the stream it will be launched on
+    return SPDNN_OK;
+}
+
+int spdnn_set_layer_csc(spdnn_t *c, int layer, const int32_t *col_ptr, const int32_t *row_idx, const float *val) {
+    if (!c) return SPDNN_ERR_ARG;
+    if (layer < 0 || layer >= c->layers) return fail(c, SPDNN_ERR_ARG, "layer %d out of range [0, %d)", layer, c->layers);
+    if (!col_ptr || !row_idx) return fail(c, SPDNN_ERR_ARG, "col_ptr and row_idx must not be null");
+    DeviceGuard guard(c->device);
+    if (c->in_flight) {
+        int rc = spdnn_sync(c, nullptr);
+        if (rc) return rc;
+    }
+    PreparedLayer p;
+    std::string why;
+    try {
+        why = prepare_layer(c->n, col_ptr, row_idx, val, p);
+    } catch (const std::bad_alloc &) {
+        return fail(c, SPDNN_ERR_MEMORY, "out of host memory preparing layer %d", layer);
+    }
+    if (!why.empty()) return fail(c, SPDNN_ERR_ARG, "layer %d: %s", layer, why.c_str());
+    c->graph_dirty = true;
+    // equal layers share one device copy
+    auto it = c->shared.find(p.content_hash);
+    if (it != c->shared.end()) {
+        if (auto sp = it->second.lock()) {
+            if (sp->h2 == p.content_hash2 && sp->classes == p.classes && sp->k == p.k && sp->nnz == p.nnz) {
+                c->layer[layer] = sp;
+                return SPDNN_OK;
+            }
+        }
+    }
+    auto L = std::make_shared<DevLayer>();
+    L->device = c->device;
+    L->classes = p.classes; L->k = p.k; L->uniform = p.uniform; L->identity_members = p.identity_members;
+    L->w = p.w; L->nnz = p.nnz; L->h1 = p.content_hash; L->h2 = p.content_hash2;
+    CK(cudaMalloc(&L->off, sizeof(int32_t) * std::max<size_t>(p.off.size(), 4)));
+    CK(cudaMemcpyAsync(L->off, p.off.data(), sizeof(int32_t) * p.off.size(), cudaMemcpyHostToDevice, c->stream));
+    if (!p.uniform) {
+        CK(cudaMalloc(&L->vals, sizeof(float) * std::max<size_t>(p.vals.size(), 4)));
+        CK(cudaMemcpyAsync(L->vals, p.vals.data(), sizeof(float) * p.vals.size(), cudaMemcpyHostToDevice, c->stream));
+    }
+    CK(cudaMalloc(&L->mem_ptr, sizeof(int32_t) * p.mem_ptr.size()));
+    CK(cudaMemcpyAsync(L->mem_ptr, p.mem_ptr.data(), sizeof(int32_t) * p.mem_ptr.size(), cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMalloc(&L->mem, sizeof(int32_t) * std::max<size_t>(p.mem.size(), 1)));
+    CK(cudaMemcpyAsync(L->mem, p.mem.data(), sizeof(int32_t) * p.mem.size(), cudaMemcpyHostToDevice, c->stream));
+    CK(cudaStreamSynchronize(c->stream));     // p's host vectors die with this call
+    c->layer[layer] = L;
+    c->shared[p.content_hash] = L;
+    return SPDNN_OK;
+}
+
+int spdnn_set_layer_coo(spdnn_t *c, int layer, int64_t nnz, const int32_t *in_neuron, const int32_t *out_neuron,
+                        const float *val, int index_base) {
+    if (!c) return SPDNN_ERR_ARG;
+    if (nnz < 0 || nnz > 0x7fffffffLL) return fail(c, SPDNN_ERR_ARG, "nnz out of range");
+    if (nnz && (!in_neuron || !out_neuron)) return fail(c, SPDNN_ERR_ARG, "triplet arrays must not be null");
+    const int n = c->n;
+    try {
+        std::vector<int32_t> col_ptr((size_t)n + 1, 0), rows((size_t)nnz);
+        std::vector<float> vals(val ? (size_t)nnz : 0);
+        for (int64_t i = 0; i < nnz; ++i) {
+            const int64_t b = (int64_t)out_neuron[i] - index_base, a = (int64_t)in_neuron[i] - index_base;
+            if (b < 0 || b >= n || a < 0 || a >= n)
+                return fail(c, SPDNN_ERR_ARG, "layer %d: triplet %lld (%d, %d) out of range", layer, (long long)i,
+                            in_neuron[i], out_neuron[i]);
+            col_ptr[b + 1]++;
+        }
+        for (int i = 0; i < n; ++i) col_ptr[i + 1] += col_ptr[i];
+        std::vector<int32_t> fill(col_ptr.begin(), col_ptr.end() - 1);
+        for (int64_t i = 0; i < nnz; ++i) {
+            const int b = out_neuron[i] - index_base;
+            const int p = fill[b]++;
+            rows[p] = in_neuron[i] - index_base;
+            if (val) vals[p] = val[i];
+        }
+        return spdnn_set_layer_csc(c, layer, col_ptr.data(), rows.data(), val ? vals.data() : nullptr);
+    } catch (const std::bad_alloc &) {
+        return fail(c, SPDNN_ERR_MEMORY, "out of host memory converting layer %d", layer);
+    }
+}
+
+int spdnn_set_input_dense_device(spdnn_t *c, const float *y0_dev, int batch, int first_global_id) {
+    if (!c) return SPDNN_ERR_ARG;
+    if (!y0_dev && batch > 0) return fail(c, SPDNN_ERR_ARG, "input pointer is null");
+    DeviceGuard guard(c->device);
+    int rc = begin_input(c, batch, first_global_id);
+    if (rc) return rc;
+    rc = convert_dense_device(c, y0_dev, batch, 0);
+    if (rc) return rc;
+    return end_input(c);
+}
+
+int spdnn_set_input_dense(spdnn_t *c, const float *y0, int batch, int first_global_id) {
+    if (!c) return SPDNN_ERR_ARG;
+    if (!y0 && batch > 0) return fail(c, SPDNN_ERR_ARG, "input pointer is null");
+    DeviceGuard guard(c->device);
+    int rc = begin_input(c, batch, first_global_id);
+    if (rc) return rc;
+    // staged through a device buffer in chunks of whole tiles
+    const size_t row_bytes = sizeof(float) * (size_t)c->n;
+    size_t chunk_rows = std::max<size_t>(32, ((size_t)512 << 20) / row_bytes / 32 * 32);
+    chunk_rows = std::min<size_t>(chunk_rows, (size_t)(batch + 31) / 32 * 32);
+    if (batch > 0) {
+        rc = ensure_stage(c, chunk_rows * row_bytes);
+        if (rc) return rc;
+    }
+    for (size_t r0 = 0; r0 < (size_t)batch; r0 += chunk_rows) {
+        const size_t rows = std::min(chunk_rows, (size_t)batch - r0);
+        CK(cudaMemcpyAsync(c->stage, y0 + r0 * c->n, rows * row_bytes, cudaMemcpyHostToDevice, c->stream));
+        rc = convert_dense_device(c, (const float *)c->stage, (int)rows, (int)(r0 / 32));
+        if (rc) return rc;
+    }
+    return end_input(c);
+}
+
+int spdnn_set_input_coo(spdnn_t *c, int64_t nnz, const int32_t *img, const int32_t *neuron, const float *val,
+                        int batch, int first_global_id, int index_base) {
+    if (!c) return SPDNN_ERR_ARG;
+    if (nnz < 0) return fail(c, SPDNN_ERR_ARG, "nnz must be >= 0");
+    if (nnz && (!img || !neuron)) return fail(c, SPDNN_ERR_ARG, "triplet arrays must not be null");
+    DeviceGuard guard(c->device);
+    int rc = begin_input(c, batch, first_global_id);
+    if (rc) return rc;
+    const int tiles = (batch + 31) / 32;
+    if (tiles) CK(cudaMemsetAsync(c->y[0], 0, sizeof(float) * (size_t)tiles * c->tile_stride, c->stream));
+    const int64_t chunk = std::min<int64_t>(std::max<int64_t>(nnz, 1), (int64_t)32 << 20);
+    const size_t per = val ? 12 : 8;
+    if (nnz) {
+        rc = ensure_stage(c, (size_t)chunk * per);
+        if (rc) return rc;
+    }
+    for (int64_t s = 0; s < nnz; s += chunk) {
+        const int64_t m = std::min(chunk, nnz - s);
+        int32_t *d_img = (int32_t *)c->stage, *d_neu = d_img + chunk;
+        float *d_val = val ? (float *)(d_neu + chunk) : nullptr;
+        CK(cudaMemcpyAsync(d_img, img + s, sizeof(int32_t) * (size_t)m, cudaMemcpyHostToDevice, c->stream));
+        CK(cudaMemcpyAsync(d_neu, neuron + s, sizeof(int32_t) * (size_t)m, cudaMemcpyHostToDevice, c->stream));
+        if (val) CK(cudaMemcpyAsync(d_val, val + s, sizeof(float) * (size_t)m, cudaMemcpyHostToDevice, c->stream));
+        const int grid = (int)std::min<int64_t>((m + 255) / 256, (int64_t)c->sm_count * 16);
+        coo_to_tiles_kernel<<<grid, 256, 0, c->stream>>>(d_img, d_neu, d_val, m, index_base, c->n, batch, c->y[0],
+                                                         c->tile_stride, c->status);
+        CK(cudaGetLastError());
+        c->prep_launches += 1;
+    }
+    return end_input(c);
+}
+
+int spdnn_infer_async(spdnn_t *c) {
+    if (!c) return SPDNN_ERR_ARG;
+    if (!c->input_ready) return fail(c, SPDNN_ERR_STATE, "no input set (or the last input was already consumed)");
+    for (int l = 0; l < c->layers; ++l)
+        if (!c->layer[l]) return fail(c, SPDNN_ERR_STATE, "layer %d was never set", l);
+    DeviceGuard guard(c->device);
+    if (c->graph_dirty) {
+        int rc = build_graph(c);
+        if (rc) return rc;
+    }
+    CK(cudaEventRecord(c->ev_inf0, c->stream));
+    CK(cudaGraphLaunch(c->graph_exec, c->stream));
+    CK(cudaEventRecord(c->ev_inf1, c->stream));
+    c->input_ready = false;
+    c->in_flight = true;
+    return SPDNN_OK;
+}
+
+int spdnn_sync(spdnn_t *c, spdnn_stats_t *stats) {
+    if (!c) return SPDNN_ERR_ARG;
+    DeviceGuard guard(c->device);
+    if (c->in_flight) {
+        CK(cudaMemcpyAsync(c->host_ctl.data(), c->ctl, sizeof(LoopCtl) * (size_t)(c->layers + 1), cudaMemcpyDeviceToHost,
+                           c->stream));
+        int32_t st = 0;
+        CK(cudaMemcpyAsync(&st, c->status, sizeof(int32_t), cudaMemcpyDeviceToHost, c->stream));
+        CK(cudaStreamSynchronize(c->stream));
+        c->in_flight = false;
+        if (st != 0) {
+            cudaMemsetAsync(c->status, 0, sizeof(int32_t), c->stream);
+            return fail(c, SPDNN_ERR_DEVICE, "device-side check failed (code %d: %s)", st,
+                        st == 3 ? "input triplet out of range" : "survivor count inconsistent");
+        }
+        spdnn_stats_t s{};
+        s.layers = c->layers; s.batch = c->batch;
+        s.survivors = c->host_ctl[c->layers].live;
+        CK(cudaEventElapsedTime(&s.infer_ms, c->ev_inf0, c->ev_inf1));
+        if (c->prep_timed) CK(cudaEventElapsedTime(&s.prepare_ms, c->ev_prep0, c->ev_prep1));
+        double bytes = 0.0;
+        for (int l = 0; l < c->layers; ++l) {
+            bytes += 4.0 * c->n * ((double)c->host_ctl[l].live + (double)c->host_ctl[l + 1].live);
+            bytes += 4.0 * (c->n + 1) + 8.0 * (double)c->layer[l]->nnz;
+        }
+        s.algorithmic_bytes = bytes;
+        s.kernel_launches = c->layers + c->prep_launches;
+        c->stats = s;
+        c->result_ready = true;
+    }
+    if (stats) *stats = c->stats;
+    return SPDNN_OK;
+}
+
+int spdnn_infer(spdnn_t *c, spdnn_stats_t *stats) {
+    int rc = spdnn_infer_async(c);
+    if (rc) return rc;
+    return spdnn_sync(c, stats);
+}
+
+int spdnn_get_layer_live(spdnn_t *c, int32_t *live, int capacity) {
+    if (!c || !live) return SPDNN_ERR_ARG;
+    if (c->in_flight) { int rc = spdnn_sync(c, nullptr); if (rc) return rc; }
+    if (!c->result_ready) return fail(c, SPDNN_ERR_STATE, "no result: call spdnn_infer first");
+    if (capacity < c->layers) return fail(c, SPDNN_ERR_ARG, "capacity %d < layers %d", capacity, c->layers);
+    for (int l = 0; l < c->layers; ++l) live[l] = c->host_ctl[l + 1].live;
+    return SPDNN_OK;
+}
+
+int spdnn_get_categories(spdnn_t *c, int32_t *ids, int capacity, int *count) {
+    if (!c || !count) return SPDNN_ERR_ARG;
+    if (c->in_flight) { int rc = spdnn_sync(c, nullptr); if (rc) return rc; }
+    if (!c->result_ready) return fail(c, SPDNN_ERR_STATE, "no result: call spdnn_infer first");
+    const LoopCtl fin = c->host_ctl[c->layers];
+    *count = fin.live;
+    if (fin.live == 0) return SPDNN_OK;
+    if (!ids || capacity < fin.live) return fail(c, SPDNN_ERR_ARG, "capacity %d < survivors %d", capacity, fin.live);
+    DeviceGuard guard(c->device);
+    CK(cudaMemcpyAsync(ids, c->ids[fin.ids_buf], sizeof(int32_t) * (size_t)fin.live, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    return SPDNN_OK;
+}
+
+int spdnn_get_activations(spdnn_t *c, float *y, int64_t capacity_rows) {
+    if (!c) return SPDNN_ERR_ARG;
+    if (c->in_flight) { int rc = spdnn_sync(c, nullptr); if (rc) return rc; }
+    if (!c->result_ready) return fail(c, SPDNN_ERR_STATE, "no result: call spdnn_infer first");
+    const int live = c->host_ctl[c->layers].live;
+    if (live == 0) return SPDNN_OK;
+    if (!y || capacity_rows < live) return fail(c, SPDNN_ERR_ARG, "capacity %lld < survivors %d", (long long)capacity_rows, live);
+    DeviceGuard guard(c->device);
+    const size_t row_bytes = sizeof(float) * (size_t)c->n;
+    size_t chunk_rows = std::max<size_t>(32, ((size_t)512 << 20) / row_bytes / 32 * 32);
+    chunk_rows = std::min<size_t>(chunk_rows, (size_t)(live + 31) / 32 * 32);
+    int rc = ensure_stage(c, chunk_rows * row_bytes);
+    if (rc) return rc;
+    const float *fin = c->y[c->layers & 1];
+    // the kernel indexes images from 0; a chunk is selected by offsetting the output pointer
+    // and launching only its tile rows
+    for (size_t r0 = 0; r0 < (size_t)live; r0 += chunk_rows) {
+        const size_t rows = std::min(chunk_rows, (size_t)live - r0);
+        const dim3 block(32, 8), grid((unsigned)((rows + 31) / 32), (c->n + 31) / 32);
+        tiles_to_dense_kernel<<<grid, block, 0, c->stream>>>(fin, c->tile_stride, c->ctl + c->layers, c->slot, c->n,
+                                                            (float *)c->stage, (int)r0);
+        CK(cudaGetLastError());
+        CK(cudaMemcpyAsync(y + r0 * c->n, c->stage, rows * row_bytes, cudaMemcpyDeviceToHost, c->stream));
+    }
+    CK(cudaStreamSynchronize(c->stream));
+    return SPDNN_OK;
+}
+
+int spdnn_get_layer_info(spdnn_t *c, int layer, int *classes, int *k, int *uniform) {
+    if (!c) return SPDNN_ERR_ARG;
+    if (layer < 0 || layer >= c->layers) return fail(c, SPDNN_ERR_ARG, "layer %d out of range", layer);
+    if (!c->layer[layer]) return fail(c, SPDNN_ERR_STATE, "layer %d was never set", layer);
+    if (classes) *classes = c->layer[layer]->classes;
+    if (k) *k = c->layer[layer]->k;
+    if (uniform) *uniform = c->layer[layer]->uniform ? 1 : 0;
+    return SPDNN_OK;
+}
+
+int spdnn_inspect_layer_csc(int neurons, const int32_t *col_ptr, const int32_t *row_idx, const float *val,
+                            int *classes, int *k, int *uniform) {
+    PreparedLayer p;
+    try {
+        if (!prepare_layer(neurons, col_ptr, row_idx, val, p).empty()) return SPDNN_ERR_ARG;
+    } catch (const std::bad_alloc &) {
+        return SPDNN_ERR_MEMORY;
+    }
+    if (classes) *classes = p.classes;
+    if (k) *k = p.k;
+    if (uniform) *uniform = p.uniform ? 1 : 0;
+    return SPDNN_OK;
+}
+
+}  // extern "C"

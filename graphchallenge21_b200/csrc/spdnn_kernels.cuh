@@ -1,0 +1,306 @@
+// sm_100a kernels of the sparse-DNN inference path.
+//
+// Activation layout ("tiles"): images are grouped 32 to a tile; a tile stores row r
+// (neuron r) of its 32 images contiguously: Y[tile][r][lane], lane = image within the tile,
+// r = 0..N, where row N is a permanent all-zero row that padded column entries point at.
+// One warp lane owns one image, so every gather of a weight row is one coalesced 128-byte
+// request and the per-image "any non-zero" test is a warp ballot.
+//
+// One launch per layer does what the reference spreads over a kernel, a D2H copy, a host
+// scan and an H2D copy (src/microbenchmark/all_network.cu:344-510): SpMM + bias + ReLU +
+// clip (its kernels :15-153 with __ReLU :8-10), the active[] flags (:57-59) as ballots, and
+// the rebuild of the work list (:455-463) by the last block to finish (prefix sum over
+// the per-tile ballots).  Dead images are dropped on read by the next layer: lane j of tile
+// t reads the image in slot[32 t + j] and writes position 32 t + j, so outputs are always
+// dense and no separate compaction pass over the activations exists.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace spdnn_impl {
+
+constexpr int kThreads = 256;          // 8 warps per block
+constexpr int kWarps = kThreads / 32;
+
+// Per-layer weights as the kernel reads them (passed by value).
+struct LayerDesc {
+    const int32_t *off;       // [U][K] element offset (row*32) of each class's inputs, ascending input order
+    const float *vals;        // [U][K] weights, or nullptr: every weight is w
+    const int32_t *mem_ptr;   // [U+1] member ranges, or nullptr: class u is column u
+    const int32_t *mem;       // member column offsets (column*32)
+    int classes;              // U
+    int k;                    // entries per class, multiple of 4
+    float w;                  // the uniform weight (power of two)
+    int classes_per_item;     // classes one block handles for one tile
+};
+
+// Loop state kept on the device, one record per layer boundary (record l = state entering
+// layer l; record L = final result).
+struct LoopCtl {
+    int32_t live;        // images alive
+    int32_t identity;    // 1: image j sits in slot j of the input buffer (no indirection)
+    int32_t ids_buf;     // which of the two id arrays holds the ids in current order
+    int32_t reserved;
+};
+
+struct LayerArgs {
+    const float *yin;
+    float *yout;
+    long long tile_stride;     // elements per tile = (N+1)*32
+    const LoopCtl *ctl_in;
+    LoopCtl *ctl_out;
+    int32_t *slot;             // work list: slot[j] = position in yin of live image j
+    uint32_t *mask;            // per output tile: ballot of alive lanes (zero on entry, zero on exit)
+    int32_t *ids0, *ids1;      // global image numbers, double buffered
+    unsigned int *counter;     // blocks finished (zero on entry, zero on exit)
+    int32_t *status;           // set non-zero when the kernel finds an inconsistency
+    float bias, clip;
+};
+
+__device__ __forceinline__ float relu_clip(float x, float clip) {
+    // x<0 ? 0 : x>clip ? clip : x   (all_network.cu:8-10)
+    return x < 0.0f ? 0.0f : (x > clip ? clip : x);
+}
+
+// Sum of one class for this lane's image: the K inputs in ascending input order, one fp32
+// add after the other, starting from 0 -- the order of src/utils/cpu_spmm.h:14-43.
+template <int KT, bool UNIFORM>
+__device__ __forceinline__ float class_sum(const LayerDesc &d, int u, const float *__restrict__ yin) {
+    float acc = 0.0f;
+    if (KT > 0) {
+        constexpr int KA = KT > 0 ? KT : 4;      // array extent (the branch is dead for KT == 0)
+        const int4 *o4 = reinterpret_cast<const int4 *>(d.off + (size_t)u * KT);
+        int o[KA];
+#pragma unroll
+        for (int i = 0; i < KT / 4; ++i) {
+            const int4 t = __ldg(o4 + i);
+            o[4 * i + 0] = t.x; o[4 * i + 1] = t.y; o[4 * i + 2] = t.z; o[4 * i + 3] = t.w;
+        }
+        float v[KA];
+#pragma unroll
+        for (int i = 0; i < KT; ++i) v[i] = __ldg(yin + o[i]);
+        if (UNIFORM) {
+#pragma unroll
+            for (int i = 0; i < KT; ++i) acc = __fadd_rn(acc, v[i]);
+        } else {
+            const float4 *w4 = reinterpret_cast<const float4 *>(d.vals + (size_t)u * KT);
+#pragma unroll
+            for (int i = 0; i < KT / 4; ++i) {
+                const float4 t = __ldg(w4 + i);
+                acc = __fadd_rn(acc, __fmul_rn(v[4 * i + 0], t.x));
+                acc = __fadd_rn(acc, __fmul_rn(v[4 * i + 1], t.y));
+                acc = __fadd_rn(acc, __fmul_rn(v[4 * i + 2], t.z));
+                acc = __fadd_rn(acc, __fmul_rn(v[4 * i + 3], t.w));
+            }
+        }
+    } else {
+        const int k = d.k;
+        const int4 *o4 = reinterpret_cast<const int4 *>(d.off + (size_t)u * k);
+        const float4 *w4 = UNIFORM ? nullptr : reinterpret_cast<const float4 *>(d.vals + (size_t)u * k);
+        for (int i = 0; i < k / 4; ++i) {
+            const int4 t = __ldg(o4 + i);
+            const float a = __ldg(yin + t.x), b = __ldg(yin + t.y), c = __ldg(yin + t.z), e = __ldg(yin + t.w);
+            if (UNIFORM) {
+                acc = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(acc, a), b), c), e);
+            } else {
+                const float4 q = __ldg(w4 + i);
+                acc = __fadd_rn(acc, __fmul_rn(a, q.x));
+                acc = __fadd_rn(acc, __fmul_rn(b, q.y));
+                acc = __fadd_rn(acc, __fmul_rn(c, q.z));
+                acc = __fadd_rn(acc, __fmul_rn(e, q.w));
+            }
+        }
+    }
+    // uniform power-of-two weight: w * sum(y) == sum(w * y) bit for bit
+    return UNIFORM ? __fmul_rn(acc, d.w) : acc;
+}
+
+// The last block to finish turns the per-tile ballots into the next layer's work list.
+__device__ __forceinline__ void rebuild_worklist(const LayerArgs &a, int live_in, int ids_buf) {
+    __shared__ int s_warp[kWarps];
+    __shared__ int s_total;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int ntiles = (live_in + 31) >> 5;
+    const int per = (ntiles + kThreads - 1) / kThreads;
+    const int t0 = min(tid * per, ntiles), t1 = min(t0 + per, ntiles);
+    int cnt = 0;
+    for (int t = t0; t < t1; ++t) cnt += __popc(__ldcg(a.mask + t));
+    // exclusive block scan of cnt
+    int inc = cnt;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += o;
+    }
+    if (lane == 31) s_warp[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        int w = lane < kWarps ? s_warp[lane] : 0;
+#pragma unroll
+        for (int d = 1; d < kWarps; d <<= 1) {
+            const int o = __shfl_up_sync(0xffffffffu, w, d);
+            if (lane >= d) w += o;
+        }
+        if (lane < kWarps) s_warp[lane] = w;          // inclusive over warps
+        if (lane == kWarps - 1) s_total = w;
+    }
+    __syncthreads();
+    int base = inc - cnt + (warp ? s_warp[warp - 1] : 0);
+    const int total = s_total;
+    if (total > live_in && tid == 0) atomicExch(a.status, 2);
+    const bool same = (total == live_in);      // nobody died: positions are already dense
+    if (!same) {
+        const int32_t *ids_old = ids_buf ? a.ids1 : a.ids0;
+        int32_t *ids_new = ids_buf ? a.ids0 : a.ids1;
+        for (int t = t0; t < t1; ++t) {
+            uint32_t m = __ldcg(a.mask + t);
+            while (m) {
+                const int b = __ffs(m) - 1;
+                m &= m - 1;
+                const int pos = t * 32 + b;
+                a.slot[base] = pos;
+                ids_new[base] = ids_old[pos];
+                ++base;
+            }
+        }
+    }
+    for (int t = t0; t < t1; ++t) a.mask[t] = 0u;
+    if (tid == 0) {
+        LoopCtl c;
+        c.live = total;
+        c.identity = same ? 1 : 0;
+        c.ids_buf = same ? ids_buf : (ids_buf ^ 1);
+        c.reserved = 0;
+        *a.ctl_out = c;
+        *a.counter = 0u;
+    }
+}
+
+// One layer.  Grid: persistent blocks striding over work items (tile, class block),
+// tile-major so that blocks running at the same time work on neighbouring tiles.
+template <int KT, bool UNIFORM>
+__global__ void __launch_bounds__(kThreads) layer_kernel(const LayerDesc d, const LayerArgs a) {
+    __shared__ unsigned int s_mask;
+    __shared__ int s_last;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const LoopCtl ctl = *a.ctl_in;
+    const int live_in = ctl.live;
+    const int ntiles = (live_in + 31) >> 5;
+    const int cpi = d.classes_per_item;
+    const int ncb = (d.classes + cpi - 1) / cpi;
+    const long long items = (long long)ntiles * ncb;
+
+    for (long long item = blockIdx.x; item < items; item += gridDim.x) {
+        const int tile = (int)(item / ncb);
+        const int cb = (int)(item - (long long)tile * ncb);
+        if (tid == 0) s_mask = 0u;
+        __syncthreads();
+        const int j = tile * 32 + lane;
+        const bool valid = j < live_in;
+        const int jj = valid ? j : tile * 32;               // padding lanes shadow lane 0 and are masked out
+        const int src = ctl.identity ? jj : __ldg(a.slot + jj);
+        const float *__restrict__ yin = a.yin + (size_t)(src >> 5) * a.tile_stride + (src & 31);
+        float *__restrict__ yout = a.yout + (size_t)tile * a.tile_stride + lane;
+        bool any = false;
+        const int u_end = min(d.classes, (cb + 1) * cpi);
+        for (int u = cb * cpi + warp; u < u_end; u += kWarps) {
+            const float s = class_sum<KT, UNIFORM>(d, u, yin);
+            const float y = relu_clip(__fadd_rn(s, a.bias), a.clip);
+            any |= (y != 0.0f);
+            if (d.mem_ptr == nullptr) {
+                yout[(size_t)u * 32] = y;
+            } else {
+                const int mb = __ldg(d.mem_ptr + u), me = __ldg(d.mem_ptr + u + 1);
+                for (int m = mb; m < me; ++m) yout[__ldg(d.mem + m)] = y;
+            }
+        }
+        const unsigned int m = __ballot_sync(0xffffffffu, any && valid);
+        if (lane == 0 && m) atomicOr(&s_mask, m);
+        __syncthreads();
+        if (tid == 0 && s_mask) atomicOr(a.mask + tile, s_mask);
+    }
+
+    // last block done: rebuild the work list (wait-free: nobody spins)
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        const unsigned int t = atomicAdd(a.counter, 1u);
+        s_last = (t == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    rebuild_worklist(a, live_in, ctl.ids_buf);
+}
+
+// ---- layout conversion and bookkeeping kernels -------------------------------------------
+
+// Row-major [batch][N] -> tiles.  Block (32, 8), grid (ceil(batch/32), ceil(N/32)).
+__global__ void dense_to_tiles_kernel(const float *__restrict__ in, float *__restrict__ out, int n, int batch,
+                                      long long tile_stride, int first_tile) {
+    __shared__ float t[32][33];
+    const int c0 = blockIdx.y * 32, tile = blockIdx.x;
+    const int img0 = tile * 32;
+#pragma unroll
+    for (int r = threadIdx.y; r < 32; r += 8) {
+        const int img = img0 + r, c = c0 + threadIdx.x;
+        t[r][threadIdx.x] = (img < batch && c < n) ? in[(size_t)img * n + c] : 0.0f;
+    }
+    __syncthreads();
+    float *o = out + (size_t)(first_tile + tile) * tile_stride;
+#pragma unroll
+    for (int r = threadIdx.y; r < 32; r += 8) {
+        const int c = c0 + r;
+        if (c < n) o[(size_t)c * 32 + threadIdx.x] = t[threadIdx.x][r];
+    }
+}
+
+// COO triplets -> tiles (the tiles must have been zeroed).  Out-of-range triplets raise status.
+__global__ void coo_to_tiles_kernel(const int32_t *__restrict__ img, const int32_t *__restrict__ neuron,
+                                    const float *__restrict__ val, long long nnz, int index_base, int n, int batch,
+                                    float *__restrict__ out, long long tile_stride, int32_t *status) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nnz; i += (long long)gridDim.x * blockDim.x) {
+        const int b = img[i] - index_base, c = neuron[i] - index_base;
+        if (b < 0 || b >= batch || c < 0 || c >= n) { atomicExch(status, 3); continue; }
+        out[(size_t)(b >> 5) * tile_stride + (size_t)c * 32 + (b & 31)] = val ? val[i] : 1.0f;
+    }
+}
+
+// Tiles -> row-major [rows][N] for the live images j_base, j_base+1, ... in work-list order
+// (row 0 of `out` is image j_base).  Block (32, 8), grid (ceil(rows/32), ceil(N/32)).
+__global__ void tiles_to_dense_kernel(const float *__restrict__ y, long long tile_stride, const LoopCtl *ctl,
+                                      const int32_t *__restrict__ slot, int n, float *__restrict__ out, int j_base) {
+    __shared__ float t[32][33];
+    const LoopCtl c = *ctl;
+    const int j0 = j_base + blockIdx.x * 32;
+    if (j0 >= c.live) return;
+    const int c0 = blockIdx.y * 32;
+    const int j = j0 + threadIdx.x;
+    const int jj = j < c.live ? j : j0;
+    const int src = c.identity ? jj : slot[jj];
+    const float *base = y + (size_t)(src >> 5) * tile_stride + (src & 31);
+#pragma unroll
+    for (int r = threadIdx.y; r < 32; r += 8) {
+        const int col = c0 + r;
+        t[r][threadIdx.x] = col < n ? base[(size_t)col * 32] : 0.0f;    // t[col][image]
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = threadIdx.y; r < 32; r += 8) {
+        const int img = j0 + r, col = c0 + threadIdx.x;
+        if (img < c.live && col < n) out[(size_t)(img - j_base) * n + col] = t[threadIdx.x][r];
+    }
+}
+
+__global__ void init_loop_kernel(LoopCtl *ctl, int32_t *ids0, int batch, int first_global_id) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < batch; i += gridDim.x * blockDim.x)
+        ids0[i] = first_global_id + i;
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        LoopCtl c;
+        c.live = batch; c.identity = 1; c.ids_buf = 0; c.reserved = 0;
+        *ctl = c;
+    }
+}
+
+}  // namespace spdnn_impl

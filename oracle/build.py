@@ -1,0 +1,74 @@
+"""Builds the test oracle.  Nothing built here is part of the shipped library.
+
+    python oracle/build.py          # liboracle.so (C restatement) and, when the reference
+                                    # tree is present, _ref/ref_harness
+
+``_ref/ref_harness`` is the reference's own CPU checkers (src/utils/cpu_spmm.h,
+src/utils/cpu_spmm_fuse.h) compiled from the reference's sources where they lie; only the
+binary lands in ``oracle/_ref/`` (git-ignored).  No reference source is copied.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF = os.environ.get("SPDNN_REFERENCE", "/root/reference")
+
+
+def _compilers(names):
+    seen = []
+    for c in names:
+        p = shutil.which(c) if c and not os.path.isabs(c) else c
+        if p and os.path.exists(p) and p not in seen:
+            seen.append(p)
+    return seen
+
+
+def _newer(target, *sources):
+    return os.path.exists(target) and all(os.path.getmtime(target) >= os.path.getmtime(s) for s in sources)
+
+
+def build_oracle(force: bool = False) -> str:
+    """Compile spdnn_oracle.c into liboracle.so (OpenMP when a compiler supports it)."""
+    src = os.path.join(HERE, "spdnn_oracle.c")
+    out = os.path.join(HERE, "liboracle.so")
+    if not force and _newer(out, src):
+        return out
+    errors = []
+    for omp in (["-fopenmp"], []):
+        for cc in _compilers(["/usr/bin/gcc", "gcc", os.environ.get("CC", ""), "cc"]):
+            cmd = [cc, "-O2", "-ffp-contract=off", "-shared", "-fPIC", *omp, "-o", out, src]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode == 0:
+                return out
+            errors.append(" ".join(cmd) + "\n" + r.stderr[-400:])
+    raise RuntimeError("could not build the oracle:\n" + "\n".join(errors))
+
+
+def build_ref(force: bool = False) -> str | None:
+    """Compile the harness against the reference headers; None when the reference is absent
+    and no earlier build exists."""
+    src = os.path.join(HERE, "ref_harness.cpp")
+    out = os.path.join(HERE, "_ref", "ref_harness")
+    if not os.path.isdir(os.path.join(REF, "src", "utils")):
+        return out if os.path.exists(out) else None
+    if not force and _newer(out, src):
+        return out
+    os.makedirs(os.path.dirname(out), exist_ok=True)
+    errors = []
+    for cxx in _compilers(["/usr/bin/g++", "g++", os.environ.get("CXX", ""), "c++"]):
+        cmd = [cxx, "-std=c++11", "-O3", "-pthread", "-I" + os.path.join(REF, "src"), "-o", out, src]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode == 0:
+            return out
+        errors.append(" ".join(cmd) + "\n" + r.stderr[-400:])
+    raise RuntimeError("could not build the reference harness:\n" + "\n".join(errors))
+
+
+if __name__ == "__main__":
+    force = "--force" in sys.argv
+    print(build_oracle(force))
+    print(build_ref(force))

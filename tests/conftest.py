@@ -1,0 +1,33 @@
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+def rows_of(net, layers=None):
+    return [net.layer_rows(l) for l in range(net.layers if layers is None else layers)]
+
+
+@pytest.fixture(scope="session")
+def oracle():
+    from oracle import c_oracle
+    c_oracle.lib()
+    return c_oracle
+
+
+def mixed_density_images(neurons, batch, seed=0xABCD, lo=0.05, hi=0.6):
+    """Binary inputs whose per-image density is spread over [lo, hi]: keeps a share of the
+    images alive on networks without locality (pattern 'random')."""
+    from graphchallenge21_b200.generator import rand_unit
+    idx = np.arange(batch * neurons, dtype=np.uint64).reshape(batch, neurons)
+    dens = lo + (hi - lo) * rand_unit(seed, 3, np.arange(batch, dtype=np.uint64))
+    return (rand_unit(seed, 4, idx) < dens[:, None]).astype(np.float32)

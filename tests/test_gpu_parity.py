@@ -1,0 +1,213 @@
+"""GPU parity tests: the CUDA path through the C ABI against the oracle, bit for bit."""
+import ctypes as C
+import glob
+import os
+
+import numpy as np
+import pytest
+
+from conftest import ROOT, mixed_density_images, rows_of
+from graphchallenge21_b200 import SpDNN, SpDNNError, _lib, generator
+from graphchallenge21_b200.generator import SyntheticNetwork, synthetic_images
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = sorted(glob.glob(os.path.join(ROOT, "tests", "golden", "*.npz")))
+REL_TOL = 1e-5        # stated tolerance for activations; the tests below get 0 (bit-exact)
+
+
+def run_gpu(net, y0, first=0, how="dense", layers=None, vals=None):
+    n, L = net.neurons, (net.layers if layers is None else layers)
+    with SpDNN(n, L, float(net.bias)) as g:
+        for l in range(L):
+            if vals is None:
+                g.set_layer_csc(l, *net.layer_csc(l))
+            else:
+                g.set_layer_rows(l, net.layer_rows(l), vals[l])
+        if how == "dense":
+            g.set_input_dense(y0, first)
+        elif how == "coo":
+            img, neu, val = generator.dense_to_coo_1based(y0)
+            g.set_input_coo(img, neu, val, y0.shape[0], first, index_base=1)
+        elif how == "device":
+            import torch
+            g.set_input_dense(torch.from_numpy(y0).cuda(), first)
+        res = g.infer()
+        return g.categories().copy(), g.activations(), g.layer_live().copy(), res
+
+
+def check(got, want):
+    cats, act, live, res = got
+    wc, wa, wl = want
+    assert np.array_equal(live, wl), (live.tolist(), wl.tolist())
+    assert np.array_equal(cats, wc)
+    assert res.survivors == len(wc)
+    assert act.shape == wa.shape
+    if wa.size:
+        rel = np.abs(act - wa) / np.maximum(np.abs(wa), 1e-30)
+        assert rel.max() <= REL_TOL
+        assert np.array_equal(act, wa), "activations are expected to be bit-exact"
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p) for p in GOLDEN])
+@pytest.mark.parametrize("how", ["dense", "coo", "device"])
+def test_golden_vectors(path, how):
+    g = np.load(path)
+    n, L = int(g["neurons"]), int(g["layers"])
+    net = SyntheticNetwork(n, L, str(g["pattern"]), seed=int(g["seed"]), bias=float(g["bias"]))
+    y0 = np.unpackbits(g["y0_bits"], axis=1)[:, :n].astype(np.float32)
+    check(run_gpu(net, y0, how=how), (g["categories"], g["activations"], g["live"]))
+
+
+@pytest.mark.parametrize("pattern,n,L,b", [("radix16", 1024, 120, 6000), ("radix16", 4096, 30, 777),
+                                           ("random", 1024, 12, 1500), ("radix16", 16384, 12, 100)])
+def test_against_oracle(pattern, n, L, b, oracle):
+    net = SyntheticNetwork(n, L, pattern)
+    y0 = synthetic_images(n, b) if pattern == "radix16" else mixed_density_images(n, b)
+    want = oracle.infer(y0, [(r, None) for r in rows_of(net)], float(net.bias), first_image=500)
+    got = run_gpu(net, y0, first=500)
+    check(got, want)
+    assert 0 < len(want[0]) < b          # the case exercises compaction
+
+
+def test_general_weights_and_ragged_columns(oracle):
+    n, b, L = 512, 200, 6
+    rng = np.random.default_rng(11)
+    y0 = mixed_density_images(n, b)
+    rows, vals = [], []
+    for l in range(L):
+        k = 20 if l % 2 else 37           # 37 -> padded to 40: the generic-K kernel
+        r = np.sort(np.stack([rng.choice(n, k, replace=False) for _ in range(n)]), axis=1).astype(np.int64)
+        drop = rng.random((n, k)) < 0.1
+        r[drop] = n + 1
+        r.sort(axis=1)
+        r[r == n + 1] = -1
+        rows.append(r.astype(np.int32))
+        vals.append(rng.uniform(0.02, 0.2, (n, k)).astype(np.float32))
+
+    class Net:
+        neurons, layers, bias = n, L, np.float32(-0.25)
+        def layer_rows(self, l): return rows[l]
+    # the oracle wants one K for all layers: pad the shorter layers on its side
+    kmax = max(r.shape[1] for r in rows)
+    prow = [np.pad(r, ((0, 0), (0, kmax - r.shape[1])), constant_values=-1) for r in rows]
+    pval = [np.pad(v, ((0, 0), (0, kmax - v.shape[1]))) for v in vals]
+    want = oracle.infer(y0, list(zip(prow, pval)), -0.25)
+    got = run_gpu(Net(), y0, vals=vals)
+    check(got, want)
+
+
+def test_uniform_non_power_of_two_weight_uses_general_path(oracle):
+    n, b, L = 1024, 300, 5
+    net = SyntheticNetwork(n, L, "radix16")
+    y0 = synthetic_images(n, b)
+    vals = [np.full((n, 32), 0.07, np.float32) for _ in range(L)]
+    want = oracle.infer(y0, [(net.layer_rows(l), vals[l]) for l in range(L)], float(net.bias))
+    with SpDNN(n, L, float(net.bias)) as g:
+        for l in range(L):
+            g.set_layer_rows(l, net.layer_rows(l), vals[l])
+        assert g.layer_info(0) == {"classes": 64, "k": 32, "uniform": False}
+        g.set_input_dense(y0)
+        res = g.infer()
+        check((g.categories().copy(), g.activations(), g.layer_live().copy(), res), want)
+
+
+def test_edge_batches(oracle):
+    n, L = 1024, 8
+    net = SyntheticNetwork(n, L, "radix16")
+    layers = [(r, None) for r in rows_of(net)]
+    with SpDNN(n, L, float(net.bias)) as g:
+        for l in range(L):
+            g.set_layer_csc(l, *net.layer_csc(l))
+        # the same context serves batches of different sizes, empty and all-dead included
+        for b in (1, 31, 32, 33, 0, 257, 64):
+            y0 = synthetic_images(n, b, first_image=3 * b)
+            g.set_input_dense(y0, 10)
+            res = g.infer()
+            want = oracle.infer(y0, layers, float(net.bias), first_image=10)
+            check((g.categories().copy(), g.activations(), g.layer_live().copy(), res), want)
+        y0 = np.zeros((40, n), np.float32)
+        g.set_input_dense(y0)
+        assert g.infer().survivors == 0 and len(g.categories()) == 0 and g.layer_live().tolist() == [0] * L
+
+
+def test_infer_is_repeatable_and_input_is_consumed():
+    n, L, b = 1024, 10, 500
+    net = SyntheticNetwork(n, L, "radix16")
+    y0 = synthetic_images(n, b)
+    with SpDNN(n, L, float(net.bias)) as g:
+        for l in range(L):
+            g.set_layer_csc(l, *net.layer_csc(l))
+        outs = []
+        for _ in range(3):
+            g.set_input_dense(y0)
+            g.infer()
+            outs.append((g.categories().copy(), g.activations()))
+        assert all(np.array_equal(outs[0][0], o[0]) and np.array_equal(outs[0][1], o[1]) for o in outs)
+        with pytest.raises(SpDNNError) as e:
+            g.infer()
+        assert e.value.code == -4
+
+
+def test_error_paths():
+    n, L = 1024, 2
+    net = SyntheticNetwork(n, L, "radix16")
+    with SpDNN(n, L, float(net.bias)) as g:
+        cp, ri, v = net.layer_csc(0)
+        bad = ri.copy(); bad[7] = n
+        with pytest.raises(SpDNNError):
+            g.set_layer_csc(0, cp, bad, v)
+        with pytest.raises(SpDNNError):
+            g.set_layer_csc(5, cp, ri, v)
+        g.set_layer_csc(0, cp, ri, v)
+        g.set_input_dense(synthetic_images(n, 8))
+        with pytest.raises(SpDNNError) as e:      # layer 1 missing
+            g.infer()
+        assert e.value.code == -4
+        g.set_layer_csc(1, *net.layer_csc(1))
+        # out-of-range input triplet: reported by the device-side check, context stays usable
+        g.set_input_coo(np.array([1, 99], np.int32), np.array([1, 1], np.int32), None, 8, 0, 1)
+        with pytest.raises(SpDNNError) as e:
+            g.infer()
+        assert e.value.code == -5
+        g.set_input_dense(synthetic_images(n, 8))
+        g.infer()
+    with pytest.raises(SpDNNError):
+        SpDNN(n, L, -0.3, device=99)
+
+
+def test_shards_compose(oracle):
+    """Batch sharding: running two halves with their global offsets gives the two halves of
+    the full category list (what the multi-GPU path relies on)."""
+    n, L, b = 1024, 20, 900
+    net = SyntheticNetwork(n, L, "radix16")
+    y0 = synthetic_images(n, b)
+    full = run_gpu(net, y0)[0]
+    lo = run_gpu(net, y0[:450], first=0)[0]
+    hi = run_gpu(net, y0[450:], first=450)[0]
+    assert np.array_equal(np.concatenate([lo, hi]), full)
+
+
+def test_full_size_properties_config1():
+    """N=1024, L=1920, B=60000 (too slow for the CPU oracle in full): size-independent
+    properties -- deterministic across runs, survivors saturate to {0, 32}, live counts never
+    grow, and the first 6000 images give exactly the categories of a 6000-image run."""
+    n, L, b = 1024, 1920, 60000
+    net = SyntheticNetwork(n, L, "radix16")
+    y0 = synthetic_images(n, b)
+    with SpDNN(n, L, float(net.bias)) as g:
+        for l in range(L):
+            g.set_layer_csc(l, *net.layer_csc(l))
+        g.set_input_dense(y0)
+        r1 = g.infer()
+        c1, live1 = g.categories().copy(), g.layer_live().copy()
+        a1 = g.activations()
+        g.set_input_dense(y0[:6000])
+        g.infer()
+        c2 = g.categories().copy()
+    assert (np.diff(live1) <= 0).all() and live1[-1] == len(c1) == r1.survivors
+    assert 0.05 * b < len(c1) < 0.8 * b
+    assert (np.diff(c1) > 0).all()
+    assert np.isin(a1, (0.0, 32.0)).all() and (a1 != 0).any(axis=1).all()
+    assert np.array_equal(c2, c1[c1 < 6000])
+    assert r1.kernel_launches >= L
