@@ -79,7 +79,7 @@ static COOMatrix make_coo(const Layer &L) {
 
 int main(int argc, char **argv) {
     if (argc < 3) {
-        fprintf(stderr, "usage: %s verify|fuse|time <case file> [tsv dir | threads]\n", argv[0]);
+        fprintf(stderr, "usage: %s verify|fuse|time <case file> [tsv dir | threads [repetitions]]\n", argv[0]);
         return 2;
     }
     std::string mode = argv[1];
@@ -119,6 +119,8 @@ int main(int argc, char **argv) {
         int threads = argc > 3 ? atoi(argv[3]) : (int)std::thread::hardware_concurrency();
         if (threads < 1) threads = 1;
         if (threads > c.batch) threads = c.batch;
+        int reps = argc > 4 ? atoi(argv[4]) : 1;
+        if (reps < 1) reps = 1;
         std::vector<COOMatrix> w;
         for (int l = 0; l < c.layers; ++l) {
             w.push_back(make_coo(c.layer[l]));
@@ -127,6 +129,7 @@ int main(int argc, char **argv) {
         NullBuf sink;                                          // the checker prints per call
         std::streambuf *old = std::cout.rdbuf(&sink);
         auto t0 = std::chrono::steady_clock::now();
+        for (int rep = 0; rep < reps; ++rep)
         for (int l = 0; l < c.layers; ++l) {
             const float *in = l == 0 ? c.input.data() : c.layer[l - 1].act.data();
             std::vector<std::thread> pool;
@@ -141,9 +144,9 @@ int main(int argc, char **argv) {
         }
         double s = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
         std::cout.rdbuf(old);
-        double edges = (double)c.batch * c.n * 32.0 * c.layers;
-        printf("{\"seconds\": %.6f, \"threads\": %d, \"batch\": %d, \"neurons\": %d, \"layers\": %d, \"edges_per_s\": %.6e}\n",
-               s, threads, c.batch, c.n, c.layers, edges / s);
+        double edges = (double)c.batch * c.n * 32.0 * c.layers * reps;
+        printf("{\"seconds\": %.6f, \"threads\": %d, \"batch\": %d, \"neurons\": %d, \"layers\": %d, \"repetitions\": %d, \"edges_per_s\": %.6e}\n",
+               s, threads, c.batch, c.n, c.layers, reps, edges / s);
         return 0;
     }
     fprintf(stderr, "unknown mode %s\n", mode.c_str());
