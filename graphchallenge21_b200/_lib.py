@@ -9,7 +9,9 @@ import ctypes as C
 import os
 
 PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG, "libspdnn_b200.so")
+# SPDNN_B200_LIB may point at another build of the same library (e.g. one compiled with
+# different tuning macros); by default the in-tree build is used.
+LIB_PATH = os.environ.get("SPDNN_B200_LIB") or os.path.join(PKG, "libspdnn_b200.so")
 
 OK = 0
 
@@ -51,6 +53,8 @@ def load():
     if _lib is not None:
         return _lib
     if not os.path.exists(LIB_PATH):
+        if os.environ.get("SPDNN_B200_LIB"):
+            raise FileNotFoundError(LIB_PATH)
         from . import build
         build.build_library()
     lib = C.CDLL(LIB_PATH)

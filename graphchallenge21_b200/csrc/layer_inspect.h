@@ -34,7 +34,7 @@ struct PreparedLayer {
     std::vector<int32_t> off;           // [U][k] input row * 32 (element offset inside a tile); padding -> row n (always zero)
     std::vector<float> vals;            // [U][k] (empty when uniform); padding 0
     std::vector<int32_t> mem_ptr;       // [U+1]
-    std::vector<int32_t> mem;           // member column * 32, classes in order of their first column
+    std::vector<int32_t> mem;           // member column * 32, ascending inside a class
     int64_t nnz = 0;
     uint64_t content_hash = 0;          // of the canonical (sorted) layer, for sharing equal layers
     uint64_t content_hash2 = 0;         // independent second hash (128 bits together)
@@ -127,6 +127,60 @@ inline std::string prepare_layer(int n, const int32_t *col_ptr, const int32_t *r
     }
     const int u = (int)first_col.size();
 
+    // Order of the classes in device memory.  Where columns repeat (u well below n) classes
+    // are chained greedily so that each is followed by the unvisited class sharing most input
+    // rows with it: a warp that walks a run of such classes re-reads the shared rows while they
+    // are still in L1.  Without repeats every row is shared by ~k unrelated classes and the
+    // order of first appearance is kept.
+    std::vector<int> order;
+    order.reserve(u);
+    if (u <= n / 2) {
+        std::vector<int> rp((size_t)n + 2, 0);
+        for (int cls = 0; cls < u; ++cls)
+            for (int i = 0; i < k; ++i) {
+                const int r = rows[(size_t)first_col[cls] * k + i];
+                if (r < n) rp[r + 2]++;
+            }
+        for (int r = 0; r < n; ++r) rp[r + 2] += rp[r + 1];
+        std::vector<int> rc((size_t)rp[n + 1]);
+        for (int cls = 0; cls < u; ++cls)
+            for (int i = 0; i < k; ++i) {
+                const int r = rows[(size_t)first_col[cls] * k + i];
+                if (r < n) rc[rp[r + 1]++] = cls;
+            }
+        // rp[r] .. rp[r+1] now delimits the classes that read row r
+        std::vector<char> visited(u, 0);
+        std::vector<int> cnt(u, 0), touched;
+        for (int start = 0; start < u; ++start) {
+            if (visited[start]) continue;
+            int cur = start;
+            for (;;) {
+                visited[cur] = 1;
+                order.push_back(cur);
+                touched.clear();
+                for (int i = 0; i < k; ++i) {
+                    const int r = rows[(size_t)first_col[cur] * k + i];
+                    if (r >= n) continue;
+                    for (int q = rp[r]; q < rp[r + 1]; ++q) {
+                        const int other = rc[q];
+                        if (!visited[other] && cnt[other]++ == 0) touched.push_back(other);
+                    }
+                }
+                int best = -1, best_cnt = 0;
+                for (int t : touched) {
+                    if (cnt[t] > best_cnt || (cnt[t] == best_cnt && t < best)) { best = t; best_cnt = cnt[t]; }
+                    cnt[t] = 0;
+                }
+                if (best < 0 || best_cnt * 4 < k) break;
+                cur = best;
+            }
+        }
+    } else {
+        for (int cls = 0; cls < u; ++cls) order.push_back(cls);
+    }
+    std::vector<int> new_id(u);
+    for (int pos = 0; pos < u; ++pos) new_id[order[pos]] = pos;
+
     out = PreparedLayer();
     out.n = n; out.k = k; out.classes = u; out.uniform = uniform; out.w = w0; out.nnz = nnz;
     out.content_hash = layer_hash;
@@ -134,19 +188,19 @@ inline std::string prepare_layer(int n, const int32_t *col_ptr, const int32_t *r
     out.identity_members = (u == n);
     out.off.resize((size_t)u * k);
     if (!uniform) out.vals.resize((size_t)u * k);
-    for (int cls = 0; cls < u; ++cls) {
-        const int fc = first_col[cls];
+    for (int pos = 0; pos < u; ++pos) {
+        const int fc = first_col[order[pos]];
         for (int i = 0; i < k; ++i) {
-            out.off[(size_t)cls * k + i] = rows[(size_t)fc * k + i] * 32;
-            if (!uniform) out.vals[(size_t)cls * k + i] = vals[(size_t)fc * k + i];
+            out.off[(size_t)pos * k + i] = rows[(size_t)fc * k + i] * 32;
+            if (!uniform) out.vals[(size_t)pos * k + i] = vals[(size_t)fc * k + i];
         }
     }
     out.mem_ptr.assign(u + 1, 0);
-    for (int c = 0; c < n; ++c) out.mem_ptr[class_of[c] + 1]++;
+    for (int c = 0; c < n; ++c) out.mem_ptr[new_id[class_of[c]] + 1]++;
     for (int cls = 0; cls < u; ++cls) out.mem_ptr[cls + 1] += out.mem_ptr[cls];
     out.mem.resize(n);
     std::vector<int32_t> fill(out.mem_ptr.begin(), out.mem_ptr.end() - 1);
-    for (int c = 0; c < n; ++c) out.mem[fill[class_of[c]]++] = c * 32;
+    for (int c = 0; c < n; ++c) out.mem[fill[new_id[class_of[c]]]++] = c * 32;
     return std::string();
 }
 

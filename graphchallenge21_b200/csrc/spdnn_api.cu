@@ -61,7 +61,7 @@ struct spdnn {
     int32_t *slot = nullptr;
     uint32_t *mask = nullptr;
     int32_t *ids[2] = {nullptr, nullptr};
-    unsigned int *counter = nullptr;
+    unsigned int *counter = nullptr;   // [0] blocks finished, [1] next work item
     int32_t *status = nullptr;
 
     void *stage = nullptr;             // device staging for host inputs / outputs
@@ -219,7 +219,7 @@ int enqueue_layers(spdnn *c) {
         a.tile_stride = c->tile_stride;
         a.ctl_in = c->ctl + l; a.ctl_out = c->ctl + l + 1;
         a.slot = c->slot; a.mask = c->mask; a.ids0 = c->ids[0]; a.ids1 = c->ids[1];
-        a.counter = c->counter; a.status = c->status;
+        a.counter = c->counter; a.work = c->counter + 1; a.status = c->status;
         a.bias = c->bias; a.clip = c->clip;
         int grid = c->grid_override > 0 ? c->grid_override : c->sm_count * blocks_per_sm(L.k, L.uniform);
         int rc = launch_layer(c, d, a, grid, L.uniform);
@@ -282,8 +282,8 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
     c->layer.resize(layers);
     CK(cudaMalloc(&c->ctl, sizeof(LoopCtl) * (size_t)(layers + 1)));
     CK(cudaMemset(c->ctl, 0, sizeof(LoopCtl) * (size_t)(layers + 1)));
-    CK(cudaMalloc(&c->counter, sizeof(unsigned int)));
-    CK(cudaMemset(c->counter, 0, sizeof(unsigned int)));
+    CK(cudaMalloc(&c->counter, 2 * sizeof(unsigned int)));
+    CK(cudaMemset(c->counter, 0, 2 * sizeof(unsigned int)));
     CK(cudaMalloc(&c->status, sizeof(int32_t)));
     CK(cudaMemset(c->status, 0, sizeof(int32_t)));
     c->host_ctl.resize(layers + 1);

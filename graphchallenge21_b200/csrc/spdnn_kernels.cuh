@@ -22,6 +22,11 @@ namespace spdnn_impl {
 
 constexpr int kThreads = 256;          // 8 warps per block
 constexpr int kWarps = kThreads / 32;
+// Blocks per SM the register allocator plans for: 3 leaves room (<= 85 registers) to issue
+// all 32 gathers of a class before the first add, which is what hides the memory latency.
+#ifndef SPDNN_MIN_BLOCKS
+#define SPDNN_MIN_BLOCKS 3
+#endif
 
 // Per-layer weights as the kernel reads them (passed by value).
 struct LayerDesc {
@@ -54,6 +59,7 @@ struct LayerArgs {
     uint32_t *mask;            // per output tile: ballot of alive lanes (zero on entry, zero on exit)
     int32_t *ids0, *ids1;      // global image numbers, double buffered
     unsigned int *counter;     // blocks finished (zero on entry, zero on exit)
+    unsigned int *work;        // next work item to hand out (zero on entry, zero on exit)
     int32_t *status;           // set non-zero when the kernel finds an inconsistency
     float bias, clip;
 };
@@ -174,14 +180,19 @@ __device__ __forceinline__ void rebuild_worklist(const LayerArgs &a, int live_in
         c.reserved = 0;
         *a.ctl_out = c;
         *a.counter = 0u;
+        *a.work = 0u;
     }
 }
 
-// One layer.  Grid: persistent blocks striding over work items (tile, class block),
-// tile-major so that blocks running at the same time work on neighbouring tiles.
+// One layer.  Grid: persistent blocks that draw work items (tile, block of classes) from an
+// atomic counter, tile-major, so that blocks running at the same time work on neighbouring
+// tiles and an uneven last wave costs one item, not one block's whole share.  Inside an item
+// every warp takes a contiguous run of classes: the host orders classes so that neighbours
+// share input rows, and the second read of a row then hits in L1.
 template <int KT, bool UNIFORM>
-__global__ void __launch_bounds__(kThreads) layer_kernel(const LayerDesc d, const LayerArgs a) {
+__global__ void __launch_bounds__(kThreads, SPDNN_MIN_BLOCKS) layer_kernel(const LayerDesc d, const LayerArgs a) {
     __shared__ unsigned int s_mask;
+    __shared__ unsigned int s_item;
     __shared__ int s_last;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const LoopCtl ctl = *a.ctl_in;
@@ -189,13 +200,19 @@ __global__ void __launch_bounds__(kThreads) layer_kernel(const LayerDesc d, cons
     const int ntiles = (live_in + 31) >> 5;
     const int cpi = d.classes_per_item;
     const int ncb = (d.classes + cpi - 1) / cpi;
-    const long long items = (long long)ntiles * ncb;
+    const unsigned int items = (unsigned int)ntiles * (unsigned int)ncb;
+    const int per_warp = (cpi + kWarps - 1) / kWarps;
 
-    for (long long item = blockIdx.x; item < items; item += gridDim.x) {
-        const int tile = (int)(item / ncb);
-        const int cb = (int)(item - (long long)tile * ncb);
-        if (tid == 0) s_mask = 0u;
+    for (;;) {
+        if (tid == 0) {
+            s_item = atomicAdd(a.work, 1u);
+            s_mask = 0u;
+        }
         __syncthreads();
+        const unsigned int item = s_item;
+        if (item >= items) break;
+        const int tile = (int)(item / (unsigned int)ncb);
+        const int cb = (int)(item - (unsigned int)tile * (unsigned int)ncb);
         const int j = tile * 32 + lane;
         const bool valid = j < live_in;
         const int jj = valid ? j : tile * 32;               // padding lanes shadow lane 0 and are masked out
@@ -204,14 +221,24 @@ __global__ void __launch_bounds__(kThreads) layer_kernel(const LayerDesc d, cons
         float *__restrict__ yout = a.yout + (size_t)tile * a.tile_stride + lane;
         bool any = false;
         const int u_end = min(d.classes, (cb + 1) * cpi);
-        for (int u = cb * cpi + warp; u < u_end; u += kWarps) {
+        const int u0 = cb * cpi + warp * per_warp;
+        const int u1 = min(u0 + per_warp, u_end);
+        for (int u = u0; u < u1; ++u) {
+            // member list of the class, fetched before the gathers so that it is there when
+            // the sum is: lane m holds member m
+            int mb = u, me = u + 1, mreg = u * 32;
+            if (d.mem_ptr != nullptr) {
+                mb = __ldg(d.mem_ptr + u);
+                me = __ldg(d.mem_ptr + u + 1);
+                mreg = (mb + lane < me) ? __ldg(d.mem + mb + lane) : 0;
+            }
             const float s = class_sum<KT, UNIFORM>(d, u, yin);
             const float y = relu_clip(__fadd_rn(s, a.bias), a.clip);
             any |= (y != 0.0f);
-            if (d.mem_ptr == nullptr) {
-                yout[(size_t)u * 32] = y;
+            const int cnt = me - mb;
+            if (cnt <= 32) {
+                for (int m = 0; m < cnt; ++m) yout[__shfl_sync(0xffffffffu, mreg, m)] = y;
             } else {
-                const int mb = __ldg(d.mem_ptr + u), me = __ldg(d.mem_ptr + u + 1);
                 for (int m = mb; m < me; ++m) yout[__ldg(d.mem + m)] = y;
             }
         }
@@ -222,7 +249,6 @@ __global__ void __launch_bounds__(kThreads) layer_kernel(const LayerDesc d, cons
     }
 
     // last block done: rebuild the work list (wait-free: nobody spins)
-    __syncthreads();
     if (tid == 0) {
         __threadfence();
         const unsigned int t = atomicAdd(a.counter, 1u);
