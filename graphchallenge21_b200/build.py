@@ -55,10 +55,10 @@ def _sources(*names: str) -> list[str]:
 
 
 def build_library(force: bool = False) -> str:
-    deps = _sources("spdnn_api.cu", "spdnn_kernels.cuh", "layer_inspect.h")
+    deps = _sources("spdnn_api.cu", "spdnn_static.cu", "spdnn_kernels.cuh", "layer_inspect.h")
     if force or _stale(LIB, deps):
         _run([_nvcc(), *ARCH, *_host_cxx(), "-lineinfo", "-O3", "-std=c++17", "-shared", "-Xcompiler", "-fPIC",
-              "-o", LIB, os.path.join(CSRC, "spdnn_api.cu")])
+              "-o", LIB, os.path.join(CSRC, "spdnn_api.cu"), os.path.join(CSRC, "spdnn_static.cu")])
     return LIB
 
 

@@ -263,7 +263,7 @@ __global__ void __launch_bounds__(kThreads, SPDNN_MIN_BLOCKS) layer_kernel(const
 // ---- layout conversion and bookkeeping kernels -------------------------------------------
 
 // Row-major [batch][N] -> tiles.  Block (32, 8), grid (ceil(batch/32), ceil(N/32)).
-__global__ void dense_to_tiles_kernel(const float *__restrict__ in, float *__restrict__ out, int n, int batch,
+static __global__ void dense_to_tiles_kernel(const float *__restrict__ in, float *__restrict__ out, int n, int batch,
                                       long long tile_stride, int first_tile) {
     __shared__ float t[32][33];
     const int c0 = blockIdx.y * 32, tile = blockIdx.x;
@@ -283,7 +283,7 @@ __global__ void dense_to_tiles_kernel(const float *__restrict__ in, float *__res
 }
 
 // COO triplets -> tiles (the tiles must have been zeroed).  Out-of-range triplets raise status.
-__global__ void coo_to_tiles_kernel(const int32_t *__restrict__ img, const int32_t *__restrict__ neuron,
+static __global__ void coo_to_tiles_kernel(const int32_t *__restrict__ img, const int32_t *__restrict__ neuron,
                                     const float *__restrict__ val, long long nnz, int index_base, int n, int batch,
                                     float *__restrict__ out, long long tile_stride, int32_t *status) {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nnz; i += (long long)gridDim.x * blockDim.x) {
@@ -295,7 +295,7 @@ __global__ void coo_to_tiles_kernel(const int32_t *__restrict__ img, const int32
 
 // Tiles -> row-major [rows][N] for the live images j_base, j_base+1, ... in work-list order
 // (row 0 of `out` is image j_base).  Block (32, 8), grid (ceil(rows/32), ceil(N/32)).
-__global__ void tiles_to_dense_kernel(const float *__restrict__ y, long long tile_stride, const LoopCtl *ctl,
+static __global__ void tiles_to_dense_kernel(const float *__restrict__ y, long long tile_stride, const LoopCtl *ctl,
                                       const int32_t *__restrict__ slot, int n, float *__restrict__ out, int j_base) {
     __shared__ float t[32][33];
     const LoopCtl c = *ctl;
@@ -319,7 +319,7 @@ __global__ void tiles_to_dense_kernel(const float *__restrict__ y, long long til
     }
 }
 
-__global__ void init_loop_kernel(LoopCtl *ctl, int32_t *ids0, int batch, int first_global_id) {
+static __global__ void init_loop_kernel(LoopCtl *ctl, int32_t *ids0, int batch, int first_global_id) {
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < batch; i += gridDim.x * blockDim.x)
         ids0[i] = first_global_id + i;
     if (blockIdx.x == 0 && threadIdx.x == 0) {

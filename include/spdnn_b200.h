@@ -41,8 +41,12 @@ enum {
     SPDNN_ERR_CUDA = -2,     /* a CUDA runtime call failed; message holds the CUDA error */
     SPDNN_ERR_MEMORY = -3,   /* host or device allocation failed */
     SPDNN_ERR_STATE = -4,    /* call made before its prerequisites (layers/input missing) */
-    SPDNN_ERR_DEVICE = -5    /* a kernel reported an internal inconsistency */
+    SPDNN_ERR_DEVICE = -5,   /* a kernel reported an internal inconsistency */
+    SPDNN_ERR_LIMIT = -6     /* a fixed capacity of the library was exceeded */
 };
+
+/* Largest number of images one spdnn_layer_static call accepts (its scratch is a fixed array). */
+#define SPDNN_STATIC_MAX_IMAGES 2097152
 
 /* Filled by spdnn_infer / spdnn_sync. */
 typedef struct spdnn_stats {
@@ -125,6 +129,36 @@ int spdnn_get_layer_info(spdnn_t *ctx, int layer, int *classes, int *k, int *uni
  * inspector stand-alone (src/main.cpp:57-92). */
 int spdnn_inspect_layer_csc(int neurons, const int32_t *col_ptr, const int32_t *row_idx, const float *val,
                             int *classes, int *k, int *uniform);
+
+/* One layer, for callers that cannot allocate device memory when they run it (a plugin inside
+ * another runtime's memory pool, a callback where cudaMalloc's implicit synchronisation is
+ * forbidden, a process whose footprint is frozen after start-up).  This entry point has no
+ * counterpart in the reference; it runs the same layer arithmetic as spdnn_infer on buffers
+ * the caller owns and keeps its own scratch (survivor ballots, block counters) in a fixed
+ * array inside the loaded module, so it calls no cudaMalloc / cudaFree and needs no context.
+ *
+ *   yin, yout      device, tile layout: tile t holds images 32t..32t+31 as [neurons + 1][32]
+ *                  floats (row r = neuron r for the 32 images, row `neurons` = zeros, used
+ *                  as padding target); yout must not alias yin
+ *   live_in        images to process; image j is read from position in_positions[j] of yin
+ *                  (device array, or NULL for j) and written to position j of yout
+ *   off            device [neurons][k]: for output neuron c the k input rows times 32,
+ *                  ascending; pad short columns with neurons * 32.  k: multiple of 4
+ *   vals           device [neurons][k] weights, or NULL: every weight is w (a power of two)
+ *   survivors      device out, capacity live_in: ascending positions in yout of the images
+ *                  with a non-zero activation; survivor_count: device out, their number
+ *   cuda_stream    cudaStream_t as void* (NULL = default stream); the call only enqueues
+ *   err, err_len   optional host buffer that receives the message of a failure
+ *
+ * Limits: at most SPDNN_STATIC_MAX_IMAGES images per call (SPDNN_ERR_LIMIT beyond that: split
+ * the batch).  The scratch array (about 264 KB) is held by every GPU that loads the library
+ * until the process exits and is shared by all calls on that GPU: calls that overlap on the
+ * device race, so keep them on one stream or order them with events.  The first call on a
+ * device also looks up the array's device address and the launch shape; make that call
+ * before any stream capture. */
+int spdnn_layer_static(const float *yin, float *yout, int neurons, int live_in, const int32_t *in_positions,
+                       const int32_t *off, const float *vals, int k, float w, float bias, float clip,
+                       int32_t *survivors, int32_t *survivor_count, void *cuda_stream, char *err, int err_len);
 
 const char *spdnn_last_error(const spdnn_t *ctx);
 void spdnn_destroy(spdnn_t *ctx);
