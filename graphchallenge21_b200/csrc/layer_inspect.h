@@ -35,6 +35,10 @@ struct PreparedLayer {
     std::vector<float> vals;            // [U][k] (empty when uniform); padding 0
     std::vector<int32_t> mem_ptr;       // [U+1]
     std::vector<int32_t> mem;           // member column * 32, ascending inside a class
+    // tables of the shared-memory-resident kernel (empty when it cannot be used): byte offsets into
+    // an activation buffer of row_bytes per row whose rows are permuted by phys_row()
+    std::vector<int32_t> roff;          // [U][k]
+    std::vector<int32_t> rmem;          // [n], grouped like mem
     int64_t nnz = 0;
     uint64_t content_hash = 0;          // of the canonical (sorted) layer, for sharing equal layers
     uint64_t content_hash2 = 0;         // independent second hash (128 bits together)
@@ -54,8 +58,18 @@ inline bool is_pow2_float(float w) {
 }
 
 // Returns an empty string on success, else the reason the layer is rejected.
+// Row permutation of the resident kernel's shared-memory buffers: the low bit is flipped by the
+// parity of the upper bits (a bijection on [0, 2m)), which spreads rows of equal parity over
+// both halves of the shared-memory banks.
+inline int phys_row(int r) {
+    int x = r >> 1;
+    x ^= x >> 16; x ^= x >> 8; x ^= x >> 4; x ^= x >> 2; x ^= x >> 1;
+    return r ^ (x & 1);
+}
+
+// resident_row_bytes: bytes per row of the resident kernel's buffers (0 = do not build its tables).
 inline std::string prepare_layer(int n, const int32_t *col_ptr, const int32_t *row_idx, const float *val,
-                                 PreparedLayer &out) {
+                                 PreparedLayer &out, int resident_row_bytes = 0) {
     if (n <= 0 || n > (1 << 26)) return "neurons must be in [1, 2^26]";
     if (!col_ptr || !row_idx) return "col_ptr/row_idx is null";
     if (col_ptr[0] != 0) return "col_ptr[0] must be 0";
@@ -201,6 +215,16 @@ inline std::string prepare_layer(int n, const int32_t *col_ptr, const int32_t *r
     out.mem.resize(n);
     std::vector<int32_t> fill(out.mem_ptr.begin(), out.mem_ptr.end() - 1);
     for (int c = 0; c < n; ++c) out.mem[fill[new_id[class_of[c]]]++] = c * 32;
+    if (resident_row_bytes > 0) {
+        const int zero_row = (n + 1) & ~1;     // first row past the permuted range
+        out.roff.resize(out.off.size());
+        for (size_t i = 0; i < out.off.size(); ++i) {
+            const int r = out.off[i] / 32;
+            out.roff[i] = (r < n ? phys_row(r) : zero_row) * resident_row_bytes;
+        }
+        out.rmem.resize(out.mem.size());
+        for (size_t i = 0; i < out.mem.size(); ++i) out.rmem[i] = phys_row(out.mem[i] / 32) * resident_row_bytes;
+    }
     return std::string();
 }
 

@@ -20,6 +20,7 @@
 
 #include "layer_inspect.h"
 #include "spdnn_kernels.cuh"
+#include "spdnn_resident.cuh"
 
 using namespace spdnn_impl;
 
@@ -30,6 +31,7 @@ struct DevLayer {
     float *vals = nullptr;
     int32_t *mem_ptr = nullptr;
     int32_t *mem = nullptr;
+    int32_t *roff = nullptr, *rmem = nullptr;     // tables of the resident kernel (or null)
     int classes = 0, k = 0;
     bool uniform = false, identity_members = false;
     float w = 0.0f;
@@ -38,7 +40,7 @@ struct DevLayer {
     int device = 0;
     ~DevLayer() {
         cudaSetDevice(device);
-        cudaFree(off); cudaFree(vals); cudaFree(mem_ptr); cudaFree(mem);
+        cudaFree(off); cudaFree(vals); cudaFree(mem_ptr); cudaFree(mem); cudaFree(roff); cudaFree(rmem);
     }
 };
 
@@ -57,7 +59,14 @@ struct spdnn {
     long long tile_stride = 0;
     int tiles_cap = 0;
     float *y[2] = {nullptr, nullptr};
-    LoopCtl *ctl = nullptr;            // layers + 1 records
+    LoopCtl *ctl = nullptr;            // one record per launch boundary (at most layers + 1)
+    int32_t *died_at = nullptr;        // [layers] images that died in each layer
+    ResLayer *res_table = nullptr;     // [layers] tables of the resident kernel
+    int res_ti = 0;                    // images per block of the resident kernel (0 = not usable)
+    size_t res_smem = 0;
+    int chunk_first = 4, chunk_max = 128;
+    int nsteps = 0;                    // launches of the last captured schedule
+    std::vector<int32_t> host_died, host_live;
     int32_t *slot = nullptr;
     uint32_t *mask = nullptr;
     int32_t *ids[2] = {nullptr, nullptr};
@@ -156,7 +165,7 @@ int begin_input(spdnn *c, int batch, int first_global_id) {
 
 int end_input(spdnn *c) {
     init_loop_kernel<<<std::max(1, std::min(1024, (c->batch + 255) / 256)), 256, 0, c->stream>>>(
-        c->ctl, c->ids[0], c->batch, c->first_id);
+        c->ctl, c->ids[0], c->batch, c->first_id, c->died_at, c->layers);
     CK(cudaGetLastError());
     c->prep_launches += 1;
     CK(cudaEventRecord(c->ev_prep1, c->stream));
@@ -199,38 +208,122 @@ int blocks_per_sm(int k, bool uniform) {
     return uniform ? blocks_per_sm_t<0, true>() : blocks_per_sm_t<0, false>();
 }
 
-int enqueue_layers(spdnn *c) {
+template <int TI, int KT, bool UNIFORM>
+int launch_resident_t(spdnn *c, const ResArgs &a, int grid) {
+    static bool configured[64] = {};
+    if (!configured[c->device & 63]) {
+        CK(cudaFuncSetAttribute(resident_kernel<TI, KT, UNIFORM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)c->res_smem));
+        configured[c->device & 63] = true;
+    }
+    resident_kernel<TI, KT, UNIFORM><<<grid, kThreads, c->res_smem, c->stream>>>(a);
+    CK(cudaGetLastError());
+    return SPDNN_OK;
+}
+
+template <int TI>
+int launch_resident_ti(spdnn *c, const ResArgs &a, int grid, bool k32, bool uniform) {
+    if (k32) return uniform ? launch_resident_t<TI, 32, true>(c, a, grid) : launch_resident_t<TI, 32, false>(c, a, grid);
+    return uniform ? launch_resident_t<TI, 0, true>(c, a, grid) : launch_resident_t<TI, 0, false>(c, a, grid);
+}
+
+int launch_resident(spdnn *c, const ResArgs &a, int grid, bool k32, bool uniform) {
+    switch (c->res_ti) {
+        case 16: return launch_resident_ti<16>(c, a, grid, k32, uniform);
+        case 8: return launch_resident_ti<8>(c, a, grid, k32, uniform);
+        default: return launch_resident_ti<4>(c, a, grid, k32, uniform);
+    }
+}
+
+// Uploads the resident kernel's per-layer table (outside stream capture).
+int upload_res_table(spdnn *c) {
+    if (!c->res_ti) return SPDNN_OK;
+    std::vector<ResLayer> t(c->layers);
     for (int l = 0; l < c->layers; ++l) {
         const DevLayer &L = *c->layer[l];
-        LayerDesc d;
-        d.off = L.off; d.vals = L.vals;
-        d.mem_ptr = L.identity_members ? nullptr : L.mem_ptr;
-        d.mem = L.mem;
-        d.classes = L.classes; d.k = L.k; d.w = L.w;
-        // Work item = (tile, block of classes).  Without duplicate columns every input row is
-        // used by ~K classes: keep a whole tile in one block when it fits the L1 so those
-        // re-reads hit there; otherwise small items for balance.
-        int cpi = 32;
-        if (L.identity_members && (size_t)c->tile_stride * 4 <= (size_t)160 * 1024) cpi = L.classes;
-        if (c->cpi_override > 0) cpi = c->cpi_override;
-        d.classes_per_item = std::max(1, std::min(cpi, L.classes));
-        LayerArgs a;
-        a.yin = c->y[l & 1]; a.yout = c->y[(l & 1) ^ 1];
-        a.tile_stride = c->tile_stride;
-        a.ctl_in = c->ctl + l; a.ctl_out = c->ctl + l + 1;
-        a.slot = c->slot; a.mask = c->mask; a.ids0 = c->ids[0]; a.ids1 = c->ids[1];
-        a.counter = c->counter; a.work = c->counter + 1; a.status = c->status;
-        a.bias = c->bias; a.clip = c->clip;
-        int grid = c->grid_override > 0 ? c->grid_override : c->sm_count * blocks_per_sm(L.k, L.uniform);
-        int rc = launch_layer(c, d, a, grid, L.uniform);
-        if (rc) return rc;
+        t[l].roff = L.roff; t[l].vals = L.vals; t[l].mem_ptr = L.mem_ptr; t[l].rmem = L.rmem;
+        t[l].classes = L.classes; t[l].k = L.k; t[l].w = L.w; t[l].reserved = 0;
     }
+    CK(cudaMemcpyAsync(c->res_table, t.data(), sizeof(ResLayer) * t.size(), cudaMemcpyHostToDevice, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    return SPDNN_OK;
+}
+
+// Enqueues the whole network: chunks of layers through the resident kernel when a group of
+// images fits in shared memory (chunk lengths 4, 8, 16, ... up to chunk_max: short while images
+// still die, long once the survivors are stable), one launch per layer otherwise.
+int enqueue_layers(spdnn *c) {
+    int step = 0;
+    int l = 0;
+    int chunk = c->chunk_first;
+    while (l < c->layers) {
+        const DevLayer &L = *c->layer[l];
+        const float *yin = c->y[step & 1];
+        float *yout = c->y[(step & 1) ^ 1];
+        if (c->res_ti && L.roff) {
+            // a chunk holds layers of one kernel variant (all k == 32 or not, all uniform or not)
+            const bool k32 = (L.k == 32), uniform = L.uniform;
+            int f = 1;
+            while (f < chunk && l + f < c->layers) {
+                const DevLayer &M = *c->layer[l + f];
+                if (!M.roff || M.uniform != uniform || (k32 && M.k != 32)) break;
+                ++f;
+            }
+            bool all32 = k32;
+            for (int i = 0; i < f && all32; ++i) all32 = (c->layer[l + i]->k == 32);
+            ResArgs a;
+            a.yin = yin; a.yout = yout; a.tile_stride = c->tile_stride;
+            a.ctl_in = c->ctl + step; a.ctl_out = c->ctl + step + 1;
+            a.slot = c->slot; a.mask = c->mask; a.ids0 = c->ids[0]; a.ids1 = c->ids[1];
+            a.counter = c->counter; a.work = c->counter + 1; a.status = c->status;
+            a.layers = c->res_table + l; a.died_at = c->died_at + l; a.nlayers = f;
+            a.n = c->n; a.rows_even = (c->n + 1) & ~1; a.bias = c->bias; a.clip = c->clip;
+            const int grid = std::max(1, (c->tiles_cap * 32 + c->res_ti - 1) / c->res_ti);
+            int rc = launch_resident(c, a, grid, all32, uniform);
+            if (rc) return rc;
+            l += f;
+            chunk = std::min(chunk * 2, c->chunk_max);
+        } else {
+            LayerDesc d;
+            d.off = L.off; d.vals = L.vals;
+            d.mem_ptr = L.identity_members ? nullptr : L.mem_ptr;
+            d.mem = L.mem;
+            d.classes = L.classes; d.k = L.k; d.w = L.w;
+            // Work item = (tile, block of classes).  Without duplicate columns every input row is
+            // used by ~K classes: keep a whole tile in one block when it fits the L1 so those
+            // re-reads hit there; otherwise small items for balance.
+            int cpi = 16;
+            if (L.identity_members && (size_t)c->tile_stride * 4 <= (size_t)160 * 1024) cpi = L.classes;
+            if (c->cpi_override > 0) cpi = c->cpi_override;
+            d.classes_per_item = std::max(1, std::min(cpi, L.classes));
+            LayerArgs a;
+            a.yin = yin; a.yout = yout;
+            a.tile_stride = c->tile_stride;
+            a.ctl_in = c->ctl + step; a.ctl_out = c->ctl + step + 1;
+            a.slot = c->slot; a.mask = c->mask; a.ids0 = c->ids[0]; a.ids1 = c->ids[1];
+            a.counter = c->counter; a.work = c->counter + 1; a.status = c->status;
+            a.died_at = c->died_at + l;
+            a.bias = c->bias; a.clip = c->clip;
+            const long long ncb = (L.classes + d.classes_per_item - 1) / d.classes_per_item;
+            if ((long long)c->tiles_cap * ncb >= 0xffffffffLL) return fail(c, SPDNN_ERR_LIMIT, "batch too large for one launch");
+            int grid = c->grid_override > 0 ? c->grid_override : c->sm_count * blocks_per_sm(L.k, L.uniform);
+            int rc = launch_layer(c, d, a, grid, L.uniform);
+            if (rc) return rc;
+            l += 1;
+        }
+        ++step;
+    }
+    c->nsteps = step;
     return SPDNN_OK;
 }
 
 int build_graph(spdnn *c) {
     if (c->graph_exec) { cudaGraphExecDestroy(c->graph_exec); c->graph_exec = nullptr; }
     cudaGraph_t g = nullptr;
+    {
+        int rc0 = upload_res_table(c);
+        if (rc0) return rc0;
+    }
     CK(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
     int rc = enqueue_layers(c);
     cudaError_t e = cudaStreamEndCapture(c->stream, &g);
@@ -286,7 +379,32 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
     CK(cudaMemset(c->counter, 0, 2 * sizeof(unsigned int)));
     CK(cudaMalloc(&c->status, sizeof(int32_t)));
     CK(cudaMemset(c->status, 0, sizeof(int32_t)));
+    CK(cudaMalloc(&c->died_at, sizeof(int32_t) * (size_t)layers));
+    CK(cudaMemset(c->died_at, 0, sizeof(int32_t) * (size_t)layers));
+    CK(cudaMalloc(&c->res_table, sizeof(ResLayer) * (size_t)layers));
     c->host_ctl.resize(layers + 1);
+    c->host_died.assign(layers, 0);
+    c->host_live.assign(layers, 0);
+    {
+        // resident kernel: two activation buffers of (rows_even + 2) rows x TI images must fit in
+        // the shared memory one block may opt in to
+        int optin = 0;
+        CK(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+        const size_t rows = (size_t)((neurons + 1) & ~1) + 2;
+        for (int ti : {16, 8, 4}) {
+            const size_t need = 2 * rows * (size_t)ti * 4;
+            if (need + 1024 <= (size_t)optin) { c->res_ti = ti; c->res_smem = need; break; }
+        }
+        if (const char *e = getenv("SPDNN_RESIDENT")) if (atoi(e) == 0) c->res_ti = 0;
+        if (const char *e = getenv("SPDNN_RESIDENT_TI")) {
+            const int ti = atoi(e);
+            if ((ti == 16 || ti == 8 || ti == 4) && 2 * rows * (size_t)ti * 4 + 1024 <= (size_t)optin) {
+                c->res_ti = ti; c->res_smem = 2 * rows * (size_t)ti * 4;
+            }
+        }
+        if (const char *e = getenv("SPDNN_CHUNK_FIRST")) c->chunk_first = std::max(1, atoi(e));
+        if (const char *e = getenv("SPDNN_CHUNK_MAX")) c->chunk_max = std::max(1, atoi(e));
+    }
     if (const char *e = getenv("SPDNN_CLASSES_PER_ITEM")) c->cpi_override = atoi(e);
     if (const char *e = getenv("SPDNN_GRID")) c->grid_override = atoi(e);
     return SPDNN_OK;
@@ -299,6 +417,7 @@ void spdnn_destroy(spdnn_t *c) {
     if (c->graph_exec) cudaGraphExecDestroy(c->graph_exec);
     free_buffers(c);
     cudaFree(c->ctl); cudaFree(c->counter); cudaFree(c->status); cudaFree(c->stage);
+    cudaFree(c->died_at); cudaFree(c->res_table);
     c->layer.clear();
     if (c->ev_prep0) cudaEventDestroy(c->ev_prep0);
     if (c->ev_prep1) cudaEventDestroy(c->ev_prep1);
@@ -333,7 +452,7 @@ int spdnn_set_layer_csc(spdnn_t *c, int layer, const int32_t *col_ptr, const int
     PreparedLayer p;
     std::string why;
     try {
-        why = prepare_layer(c->n, col_ptr, row_idx, val, p);
+        why = prepare_layer(c->n, col_ptr, row_idx, val, p, c->res_ti * 4);
     } catch (const std::bad_alloc &) {
         return fail(c, SPDNN_ERR_MEMORY, "out of host memory preparing layer %d", layer);
     }
@@ -363,6 +482,12 @@ int spdnn_set_layer_csc(spdnn_t *c, int layer, const int32_t *col_ptr, const int
     CK(cudaMemcpyAsync(L->mem_ptr, p.mem_ptr.data(), sizeof(int32_t) * p.mem_ptr.size(), cudaMemcpyHostToDevice, c->stream));
     CK(cudaMalloc(&L->mem, sizeof(int32_t) * std::max<size_t>(p.mem.size(), 1)));
     CK(cudaMemcpyAsync(L->mem, p.mem.data(), sizeof(int32_t) * p.mem.size(), cudaMemcpyHostToDevice, c->stream));
+    if (!p.roff.empty()) {
+        CK(cudaMalloc(&L->roff, sizeof(int32_t) * std::max<size_t>(p.roff.size(), 4)));
+        CK(cudaMemcpyAsync(L->roff, p.roff.data(), sizeof(int32_t) * p.roff.size(), cudaMemcpyHostToDevice, c->stream));
+        CK(cudaMalloc(&L->rmem, sizeof(int32_t) * std::max<size_t>(p.rmem.size(), 1)));
+        CK(cudaMemcpyAsync(L->rmem, p.rmem.data(), sizeof(int32_t) * p.rmem.size(), cudaMemcpyHostToDevice, c->stream));
+    }
     CK(cudaStreamSynchronize(c->stream));     // p's host vectors die with this call
     c->layer[layer] = L;
     c->shared[p.content_hash] = L;
@@ -487,7 +612,9 @@ int spdnn_sync(spdnn_t *c, spdnn_stats_t *stats) {
     if (!c) return SPDNN_ERR_ARG;
     DeviceGuard guard(c->device);
     if (c->in_flight) {
-        CK(cudaMemcpyAsync(c->host_ctl.data(), c->ctl, sizeof(LoopCtl) * (size_t)(c->layers + 1), cudaMemcpyDeviceToHost,
+        CK(cudaMemcpyAsync(c->host_ctl.data(), c->ctl, sizeof(LoopCtl) * (size_t)(c->nsteps + 1), cudaMemcpyDeviceToHost,
+                           c->stream));
+        CK(cudaMemcpyAsync(c->host_died.data(), c->died_at, sizeof(int32_t) * (size_t)c->layers, cudaMemcpyDeviceToHost,
                            c->stream));
         int32_t st = 0;
         CK(cudaMemcpyAsync(&st, c->status, sizeof(int32_t), cudaMemcpyDeviceToHost, c->stream));
@@ -500,16 +627,28 @@ int spdnn_sync(spdnn_t *c, spdnn_stats_t *stats) {
         }
         spdnn_stats_t s{};
         s.layers = c->layers; s.batch = c->batch;
-        s.survivors = c->host_ctl[c->layers].live;
+        s.survivors = c->host_ctl[c->nsteps].live;
+        {
+            long long live = c->batch;
+            for (int l = 0; l < c->layers; ++l) {
+                live -= c->host_died[l];
+                c->host_live[l] = (int32_t)live;
+            }
+            if (live != s.survivors) {
+                return fail(c, SPDNN_ERR_DEVICE, "survivor bookkeeping inconsistent (%lld by layer, %lld final)", live,
+                            (long long)s.survivors);
+            }
+        }
         CK(cudaEventElapsedTime(&s.infer_ms, c->ev_inf0, c->ev_inf1));
         if (c->prep_timed) CK(cudaEventElapsedTime(&s.prepare_ms, c->ev_prep0, c->ev_prep1));
         double bytes = 0.0;
         for (int l = 0; l < c->layers; ++l) {
-            bytes += 4.0 * c->n * ((double)c->host_ctl[l].live + (double)c->host_ctl[l + 1].live);
+            const double live_in = l ? (double)c->host_live[l - 1] : (double)c->batch;
+            bytes += 4.0 * c->n * (live_in + (double)c->host_live[l]);
             bytes += 4.0 * (c->n + 1) + 8.0 * (double)c->layer[l]->nnz;
         }
         s.algorithmic_bytes = bytes;
-        s.kernel_launches = c->layers + c->prep_launches;
+        s.kernel_launches = c->nsteps + c->prep_launches;
         c->stats = s;
         c->result_ready = true;
     }
@@ -528,7 +667,7 @@ int spdnn_get_layer_live(spdnn_t *c, int32_t *live, int capacity) {
     if (c->in_flight) { int rc = spdnn_sync(c, nullptr); if (rc) return rc; }
     if (!c->result_ready) return fail(c, SPDNN_ERR_STATE, "no result: call spdnn_infer first");
     if (capacity < c->layers) return fail(c, SPDNN_ERR_ARG, "capacity %d < layers %d", capacity, c->layers);
-    for (int l = 0; l < c->layers; ++l) live[l] = c->host_ctl[l + 1].live;
+    for (int l = 0; l < c->layers; ++l) live[l] = c->host_live[l];
     return SPDNN_OK;
 }
 
@@ -536,7 +675,7 @@ int spdnn_get_categories(spdnn_t *c, int32_t *ids, int capacity, int *count) {
     if (!c || !count) return SPDNN_ERR_ARG;
     if (c->in_flight) { int rc = spdnn_sync(c, nullptr); if (rc) return rc; }
     if (!c->result_ready) return fail(c, SPDNN_ERR_STATE, "no result: call spdnn_infer first");
-    const LoopCtl fin = c->host_ctl[c->layers];
+    const LoopCtl fin = c->host_ctl[c->nsteps];
     *count = fin.live;
     if (fin.live == 0) return SPDNN_OK;
     if (!ids || capacity < fin.live) return fail(c, SPDNN_ERR_ARG, "capacity %d < survivors %d", capacity, fin.live);
@@ -550,7 +689,7 @@ int spdnn_get_activations(spdnn_t *c, float *y, int64_t capacity_rows) {
     if (!c) return SPDNN_ERR_ARG;
     if (c->in_flight) { int rc = spdnn_sync(c, nullptr); if (rc) return rc; }
     if (!c->result_ready) return fail(c, SPDNN_ERR_STATE, "no result: call spdnn_infer first");
-    const int live = c->host_ctl[c->layers].live;
+    const int live = c->host_ctl[c->nsteps].live;
     if (live == 0) return SPDNN_OK;
     if (!y || capacity_rows < live) return fail(c, SPDNN_ERR_ARG, "capacity %lld < survivors %d", (long long)capacity_rows, live);
     DeviceGuard guard(c->device);
@@ -559,13 +698,13 @@ int spdnn_get_activations(spdnn_t *c, float *y, int64_t capacity_rows) {
     chunk_rows = std::min<size_t>(chunk_rows, (size_t)(live + 31) / 32 * 32);
     int rc = ensure_stage(c, chunk_rows * row_bytes);
     if (rc) return rc;
-    const float *fin = c->y[c->layers & 1];
+    const float *fin = c->y[c->nsteps & 1];
     // the kernel indexes images from 0; a chunk is selected by offsetting the output pointer
     // and launching only its tile rows
     for (size_t r0 = 0; r0 < (size_t)live; r0 += chunk_rows) {
         const size_t rows = std::min(chunk_rows, (size_t)live - r0);
         const dim3 block(32, 8), grid((unsigned)((rows + 31) / 32), (c->n + 31) / 32);
-        tiles_to_dense_kernel<<<grid, block, 0, c->stream>>>(fin, c->tile_stride, c->ctl + c->layers, c->slot, c->n,
+        tiles_to_dense_kernel<<<grid, block, 0, c->stream>>>(fin, c->tile_stride, c->ctl + c->nsteps, c->slot, c->n,
                                                             (float *)c->stage, (int)r0);
         CK(cudaGetLastError());
         CK(cudaMemcpyAsync(y + r0 * c->n, c->stage, rows * row_bytes, cudaMemcpyDeviceToHost, c->stream));

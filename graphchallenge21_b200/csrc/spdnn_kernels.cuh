@@ -61,6 +61,7 @@ struct LayerArgs {
     unsigned int *counter;     // blocks finished (zero on entry, zero on exit)
     unsigned int *work;        // next work item to hand out (zero on entry, zero on exit)
     int32_t *status;           // set non-zero when the kernel finds an inconsistency
+    int32_t *died_at;          // where the per-layer kernel records how many images died in its layer (or nullptr)
     float bias, clip;
 };
 
@@ -181,6 +182,7 @@ __device__ __forceinline__ void rebuild_worklist(const LayerArgs &a, int live_in
         *a.ctl_out = c;
         *a.counter = 0u;
         *a.work = 0u;
+        if (a.died_at) *a.died_at = live_in - total;
     }
 }
 
@@ -319,9 +321,11 @@ static __global__ void tiles_to_dense_kernel(const float *__restrict__ y, long l
     }
 }
 
-static __global__ void init_loop_kernel(LoopCtl *ctl, int32_t *ids0, int batch, int first_global_id) {
+static __global__ void init_loop_kernel(LoopCtl *ctl, int32_t *ids0, int batch, int first_global_id, int32_t *died_at,
+                                        int layers) {
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < batch; i += gridDim.x * blockDim.x)
         ids0[i] = first_global_id + i;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < layers; i += gridDim.x * blockDim.x) died_at[i] = 0;
     if (blockIdx.x == 0 && threadIdx.x == 0) {
         LoopCtl c;
         c.live = batch; c.identity = 1; c.ids_buf = 0; c.reserved = 0;

@@ -1,0 +1,262 @@
+// Resident kernel: several consecutive layers in ONE launch with the activations of a group
+// of images held in shared memory from the first to the last of those layers.
+//
+// Images are independent through the network, so a block that owns TI images can apply layer
+// after layer without touching global memory for Y: two activation buffers of (N + 2) x TI
+// floats ping-pong inside the block's shared memory (TI = 16 for N <= 1758, 8 or 4 for larger
+// N, as 227 KB allow), only the small per-layer index tables stream in through L1/L2.  This is
+// the idea of the reference's two-layer fusion (src/fuse/fuse.h:9-53, src/microbenchmark/fuse.cu:16-110:
+// layer-0 output kept in shared memory for layer 1) taken to a whole chunk of layers, made
+// possible by B200's shared-memory size.  HBM traffic per chunk is one read and one write of
+// the live images instead of one per layer.
+//
+// Thread mapping: a thread owns one class (group of identical columns) for FOUR images and
+// keeps a float4 of accumulators; every gather is one 16-byte shared-memory load, every pair
+// of adds one packed add.rn.f32x2 (sm_100 packed fp32), each element added in the same
+// ascending-input order as everywhere else, so results stay bit-identical to the per-layer
+// kernel and to the CPU loop of src/utils/cpu_spmm.h:14-43.
+//
+// Rows of the shared-memory buffers are permuted (row r sits at r ^ parity(r >> 1)) so that
+// classes whose rows all share one parity do not pile onto the same half of the banks; the
+// permutation is folded into the offset tables on the host and costs nothing here.
+//
+// Survivors: an image dies in the layer after which all its activations are zero
+// (all_network.cu:57-59, 455-463) and stays dead; inside a chunk its activations are forced to
+// zero from then on, the layer of death is counted in died_at[], and at the end of the chunk the
+// per-tile ballots and the last-block work-list rebuild are those of the per-layer kernel.
+#pragma once
+
+#include "spdnn_kernels.cuh"
+
+namespace spdnn_impl {
+
+// Per-layer tables of the resident kernel (one entry per layer, in device memory).
+struct ResLayer {
+    const int32_t *roff;      // [U][K] byte offset of each input row inside an activation buffer (permuted rows)
+    const float *vals;        // [U][K] or nullptr
+    const int32_t *mem_ptr;   // [U+1]
+    const int32_t *rmem;      // [N] byte offsets of the member rows, grouped by class
+    int classes, k;
+    float w;
+    int reserved;
+};
+
+struct ResArgs {
+    const float *yin;
+    float *yout;
+    long long tile_stride;
+    const LoopCtl *ctl_in;
+    LoopCtl *ctl_out;
+    int32_t *slot;
+    uint32_t *mask;
+    int32_t *ids0, *ids1;
+    unsigned int *counter, *work;
+    int32_t *status;
+    const ResLayer *layers;   // first layer of this chunk
+    int32_t *died_at;         // first layer of this chunk
+    int nlayers;
+    int n;                    // neurons
+    int rows_even;            // n rounded up to even: index of the zero row
+    float bias, clip;
+};
+
+__host__ __device__ __forceinline__ int resident_phys_row(int r) {
+    // flip the low bit by the parity of the upper bits: a bijection on [0, 2m)
+    int x = r >> 1;
+    x ^= x >> 16; x ^= x >> 8; x ^= x >> 4; x ^= x >> 2; x ^= x >> 1;
+    return r ^ (x & 1);
+}
+
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+#ifndef SPDNN_NO_F32X2
+    unsigned long long ra, rb, rd;
+    float2 d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    return d;
+#else
+    return make_float2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y));
+#endif
+}
+
+__device__ __forceinline__ void acc4(float4 &acc, const float4 v) {
+    const float2 lo = add2(make_float2(acc.x, acc.y), make_float2(v.x, v.y));
+    const float2 hi = add2(make_float2(acc.z, acc.w), make_float2(v.z, v.w));
+    acc = make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+
+__device__ __forceinline__ float4 mul4(const float4 v, float w) {
+    return make_float4(__fmul_rn(v.x, w), __fmul_rn(v.y, w), __fmul_rn(v.z, w), __fmul_rn(v.w, w));
+}
+
+// Sum of one class for this thread's four images; `in` already points at the thread's 16-byte
+// column of the current activation buffer.
+template <int KT, bool UNIFORM>
+__device__ __forceinline__ float4 class_sum_resident(const ResLayer &L, int u, const unsigned char *in) {
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (KT > 0) {
+        constexpr int KA = KT > 0 ? KT : 4;
+        const int4 *o4 = reinterpret_cast<const int4 *>(L.roff + (size_t)u * KT);
+        int o[KA];
+#pragma unroll
+        for (int i = 0; i < KT / 4; ++i) {
+            const int4 t = __ldg(o4 + i);
+            o[4 * i + 0] = t.x; o[4 * i + 1] = t.y; o[4 * i + 2] = t.z; o[4 * i + 3] = t.w;
+        }
+        if (UNIFORM) {
+#pragma unroll
+            for (int i = 0; i < KT; ++i) acc4(acc, *reinterpret_cast<const float4 *>(in + o[i]));
+        } else {
+            const float4 *w4 = reinterpret_cast<const float4 *>(L.vals + (size_t)u * KT);
+#pragma unroll
+            for (int i = 0; i < KT / 4; ++i) {
+                const float4 t = __ldg(w4 + i);
+                acc4(acc, mul4(*reinterpret_cast<const float4 *>(in + o[4 * i + 0]), t.x));
+                acc4(acc, mul4(*reinterpret_cast<const float4 *>(in + o[4 * i + 1]), t.y));
+                acc4(acc, mul4(*reinterpret_cast<const float4 *>(in + o[4 * i + 2]), t.z));
+                acc4(acc, mul4(*reinterpret_cast<const float4 *>(in + o[4 * i + 3]), t.w));
+            }
+        }
+    } else {
+        const int k = L.k;
+        const int4 *o4 = reinterpret_cast<const int4 *>(L.roff + (size_t)u * k);
+        const float4 *w4 = UNIFORM ? nullptr : reinterpret_cast<const float4 *>(L.vals + (size_t)u * k);
+        for (int i = 0; i < k / 4; ++i) {
+            const int4 t = __ldg(o4 + i);
+            float4 a = *reinterpret_cast<const float4 *>(in + t.x), b = *reinterpret_cast<const float4 *>(in + t.y);
+            float4 c = *reinterpret_cast<const float4 *>(in + t.z), e = *reinterpret_cast<const float4 *>(in + t.w);
+            if (!UNIFORM) {
+                const float4 q = __ldg(w4 + i);
+                a = mul4(a, q.x); b = mul4(b, q.y); c = mul4(c, q.z); e = mul4(e, q.w);
+            }
+            acc4(acc, a); acc4(acc, b); acc4(acc, c); acc4(acc, e);
+        }
+    }
+    return UNIFORM ? mul4(acc, L.w) : acc;
+}
+
+// Grid: one block per TI live images (launched for the worst case; surplus blocks only take
+// part in the last-block ticket).  Dynamic shared memory: 2 * (rows_even + 2) * TI * 4 bytes.
+template <int TI, int KT, bool UNIFORM>
+__global__ void __launch_bounds__(kThreads, 1) resident_kernel(const ResArgs a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ unsigned int s_alive[3];
+    __shared__ int s_last;
+    constexpr int LPC = TI / 4;                  // threads per class
+    constexpr int CPI = kThreads / LPC;          // classes per pass of the block
+    constexpr int RS = TI * 4;                   // bytes per row
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int sub = tid % LPC, grp = tid / LPC;
+    const LoopCtl ctl = *a.ctl_in;
+    const int live_in = ctl.live;
+    const int nblk = (live_in + TI - 1) / TI;
+    const int buf_bytes = (a.rows_even + 2) * RS;
+
+    if ((int)blockIdx.x < nblk) {
+        unsigned char *cur = smem, *nxt = smem + buf_bytes;
+        const int j0 = blockIdx.x * TI;
+        // ---- load the block's images (dead images were dropped: read through the work list)
+        const float *p[4];
+        unsigned int my_valid = 0;
+        bool contiguous = ctl.identity != 0;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int j = j0 + sub * 4 + q;
+            const bool v = j < live_in;
+            my_valid |= (v ? 1u : 0u) << q;
+            const int jj = v ? j : j0;
+            const int src = ctl.identity ? jj : __ldg(a.slot + jj);
+            p[q] = a.yin + (size_t)(src >> 5) * a.tile_stride + (src & 31);
+        }
+        if (my_valid != 0xFu) contiguous = false;
+        for (int r = grp; r < a.n; r += CPI) {
+            float4 v;
+            if (contiguous) {
+                v = __ldg(reinterpret_cast<const float4 *>(p[0] + (size_t)r * 32));
+            } else {
+                v.x = (my_valid & 1u) ? __ldg(p[0] + (size_t)r * 32) : 0.0f;
+                v.y = (my_valid & 2u) ? __ldg(p[1] + (size_t)r * 32) : 0.0f;
+                v.z = (my_valid & 4u) ? __ldg(p[2] + (size_t)r * 32) : 0.0f;
+                v.w = (my_valid & 8u) ? __ldg(p[3] + (size_t)r * 32) : 0.0f;
+            }
+            *reinterpret_cast<float4 *>(cur + resident_phys_row(r) * RS + sub * 16) = v;
+        }
+        // rows n .. rows_even + 1 of both buffers are the zero rows padded entries point at
+        for (int r = a.n + grp; r < a.rows_even + 2; r += CPI) {
+            *reinterpret_cast<float4 *>(cur + (r < a.rows_even ? resident_phys_row(r) : r) * RS + sub * 16) = make_float4(0, 0, 0, 0);
+            *reinterpret_cast<float4 *>(nxt + (r < a.rows_even ? resident_phys_row(r) : r) * RS + sub * 16) = make_float4(0, 0, 0, 0);
+        }
+        if (tid == 0) s_alive[0] = 0u;
+        // LPC divides 32, so every warp holds all sub-columns: the OR over a warp is the block's
+        // mask of valid images (bit i = image j0 + i), identical in every thread
+        unsigned int alive_prev = __reduce_or_sync(0xffffffffu, my_valid << (sub * 4));
+        __syncthreads();
+
+        // ---- the layers of this chunk
+        for (int li = 0; li < a.nlayers; ++li) {
+            const ResLayer L = a.layers[li];
+            if (tid == 0) s_alive[(li + 1) % 3] = 0u;
+            unsigned int bits = 0;
+            const unsigned char *in = cur + sub * 16;
+            for (int u = grp; u < L.classes; u += CPI) {
+                const int mb = __ldg(L.mem_ptr + u), me = __ldg(L.mem_ptr + u + 1);
+                const float4 s = class_sum_resident<KT, UNIFORM>(L, u, in);
+                float4 y;
+                y.x = relu_clip(__fadd_rn(s.x, a.bias), a.clip);
+                y.y = relu_clip(__fadd_rn(s.y, a.bias), a.clip);
+                y.z = relu_clip(__fadd_rn(s.z, a.bias), a.clip);
+                y.w = relu_clip(__fadd_rn(s.w, a.bias), a.clip);
+                const unsigned int al = alive_prev >> (sub * 4);      // dead images stay dead
+                if (!(al & 1u)) y.x = 0.0f;
+                if (!(al & 2u)) y.y = 0.0f;
+                if (!(al & 4u)) y.z = 0.0f;
+                if (!(al & 8u)) y.w = 0.0f;
+                bits |= (y.x != 0.0f ? 1u : 0u) | (y.y != 0.0f ? 2u : 0u) | (y.z != 0.0f ? 4u : 0u) | (y.w != 0.0f ? 8u : 0u);
+                for (int m = mb; m < me; ++m)
+                    *reinterpret_cast<float4 *>(nxt + __ldg(L.rmem + m) + sub * 16) = y;
+            }
+            const unsigned int wm = __reduce_or_sync(0xffffffffu, bits << (sub * 4));
+            if (lane == 0 && wm) atomicOr(&s_alive[li % 3], wm);
+            __syncthreads();
+            const unsigned int alive_now = s_alive[li % 3] & alive_prev;
+            if (tid == 0) {
+                const int died = __popc(alive_prev & ~alive_now);
+                if (died) atomicAdd(a.died_at + li, died);
+            }
+            alive_prev = alive_now;
+            unsigned char *t = cur; cur = nxt; nxt = t;
+            if (alive_prev == 0u) break;
+        }
+
+        // ---- write the survivors' activations back (dead blocks write nothing)
+        if (alive_prev != 0u) {
+            const int tile = j0 >> 5, lane0 = j0 & 31;
+            float *out = a.yout + (size_t)tile * a.tile_stride + lane0 + sub * 4;
+            for (int r = grp; r < a.n; r += CPI)
+                *reinterpret_cast<float4 *>(out + (size_t)r * 32) =
+                    *reinterpret_cast<const float4 *>(cur + resident_phys_row(r) * RS + sub * 16);
+            if (tid == 0) atomicOr(a.mask + tile, alive_prev << lane0);
+        }
+    }
+
+    // ---- last block done: rebuild the work list
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        s_last = (atomicAdd(a.counter, 1u) == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    LayerArgs la;
+    la.yin = a.yin; la.yout = a.yout; la.tile_stride = a.tile_stride;
+    la.ctl_in = a.ctl_in; la.ctl_out = a.ctl_out; la.slot = a.slot; la.mask = a.mask;
+    la.ids0 = a.ids0; la.ids1 = a.ids1; la.counter = a.counter; la.work = a.work; la.status = a.status;
+    la.died_at = nullptr;
+    la.bias = a.bias; la.clip = a.clip;
+    rebuild_worklist(la, live_in, ctl.ids_buf);
+}
+
+}  // namespace spdnn_impl
