@@ -18,7 +18,8 @@ OK = 0
 
 class Stats(C.Structure):
     _fields_ = [("layers", C.c_int32), ("batch", C.c_int32), ("survivors", C.c_int64), ("prepare_ms", C.c_float),
-                ("infer_ms", C.c_float), ("algorithmic_bytes", C.c_double), ("kernel_launches", C.c_int64)]
+                ("infer_ms", C.c_float), ("algorithmic_bytes", C.c_double), ("kernel_launches", C.c_int64),
+                ("loop_launches", C.c_int32), ("resident_group", C.c_int32)]
 
 
 # every entry point include/spdnn_b200.h declares

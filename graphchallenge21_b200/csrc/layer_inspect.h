@@ -37,8 +37,10 @@ struct PreparedLayer {
     std::vector<int32_t> mem;           // member column * 32, ascending inside a class
     // tables of the shared-memory-resident kernel (empty when it cannot be used): byte offsets into
     // an activation buffer of row_bytes per row whose rows are permuted by phys_row()
-    std::vector<int32_t> roff;          // [U][k]
-    std::vector<int32_t> rmem;          // [n], grouped like mem
+    // one blob: int32 roff[U][k + 4] | int32 mem_ptr[U + 1] | int32 rmem[n] | float vals[U][k + 4] (if not
+    // uniform); sections start on 16-byte boundaries
+    std::vector<int32_t> rblob;
+    int o_mem_ptr = 0, o_rmem = 0, o_vals = 0;      // section starts in 4-byte words
     int64_t nnz = 0;
     uint64_t content_hash = 0;          // of the canonical (sorted) layer, for sharing equal layers
     uint64_t content_hash2 = 0;         // independent second hash (128 bits together)
@@ -217,13 +219,24 @@ inline std::string prepare_layer(int n, const int32_t *col_ptr, const int32_t *r
     for (int c = 0; c < n; ++c) out.mem[fill[new_id[class_of[c]]]++] = c * 32;
     if (resident_row_bytes > 0) {
         const int zero_row = (n + 1) & ~1;     // first row past the permuted range
-        out.roff.resize(out.off.size());
-        for (size_t i = 0; i < out.off.size(); ++i) {
-            const int r = out.off[i] / 32;
-            out.roff[i] = (r < n ? phys_row(r) : zero_row) * resident_row_bytes;
-        }
-        out.rmem.resize(out.mem.size());
-        for (size_t i = 0; i < out.mem.size(); ++i) out.rmem[i] = phys_row(out.mem[i] / 32) * resident_row_bytes;
+        const int kp = k + 4;
+        auto round4 = [](size_t x) { return (x + 3) / 4 * 4; };
+        const size_t s_roff = round4((size_t)u * kp), s_ptr = round4((size_t)u + 1), s_mem = round4((size_t)n);
+        out.o_mem_ptr = (int)s_roff;
+        out.o_rmem = (int)(s_roff + s_ptr);
+        out.o_vals = uniform ? 0 : (int)(s_roff + s_ptr + s_mem);
+        out.rblob.assign(s_roff + s_ptr + s_mem + (uniform ? 0 : s_roff), 0);
+        for (int cls = 0; cls < u; ++cls)
+            for (int i = 0; i < kp; ++i) {
+                const int r = i < k ? out.off[(size_t)cls * k + i] / 32 : n;
+                out.rblob[(size_t)cls * kp + i] = (r < n ? phys_row(r) : zero_row) * resident_row_bytes;
+                if (!uniform) {
+                    const float v = i < k ? out.vals[(size_t)cls * k + i] : 0.0f;
+                    std::memcpy(&out.rblob[(size_t)out.o_vals + (size_t)cls * kp + i], &v, 4);
+                }
+            }
+        for (int cls = 0; cls <= u; ++cls) out.rblob[(size_t)out.o_mem_ptr + cls] = out.mem_ptr[cls];
+        for (size_t i = 0; i < out.mem.size(); ++i) out.rblob[(size_t)out.o_rmem + i] = phys_row(out.mem[i] / 32) * resident_row_bytes;
     }
     return std::string();
 }

@@ -31,7 +31,8 @@ struct DevLayer {
     float *vals = nullptr;
     int32_t *mem_ptr = nullptr;
     int32_t *mem = nullptr;
-    int32_t *roff = nullptr, *rmem = nullptr;     // tables of the resident kernel (or null)
+    int32_t *rblob = nullptr;                     // tables of the resident kernel in one blob (or null)
+    int rblob_bytes = 0, o_mem_ptr = 0, o_rmem = 0, o_vals = 0;
     int classes = 0, k = 0;
     bool uniform = false, identity_members = false;
     float w = 0.0f;
@@ -40,7 +41,7 @@ struct DevLayer {
     int device = 0;
     ~DevLayer() {
         cudaSetDevice(device);
-        cudaFree(off); cudaFree(vals); cudaFree(mem_ptr); cudaFree(mem); cudaFree(roff); cudaFree(rmem);
+        cudaFree(off); cudaFree(vals); cudaFree(mem_ptr); cudaFree(mem); cudaFree(rblob);
     }
 };
 
@@ -63,7 +64,9 @@ struct spdnn {
     int32_t *died_at = nullptr;        // [layers] images that died in each layer
     ResLayer *res_table = nullptr;     // [layers] tables of the resident kernel
     int res_ti = 0;                    // images per block of the resident kernel (0 = not usable)
-    size_t res_smem = 0;
+    size_t res_smem = 0;               // bytes of its two activation buffers
+    int smem_optin = 0;                // shared memory one block may opt in to
+    bool stage_tables = true;          // bring the per-layer tables into shared memory with bulk copies
     int chunk_first = 4, chunk_max = 128;
     int nsteps = 0;                    // launches of the last captured schedule
     std::vector<int32_t> host_died, host_live;
@@ -208,23 +211,30 @@ int blocks_per_sm(int k, bool uniform) {
     return uniform ? blocks_per_sm_t<0, true>() : blocks_per_sm_t<0, false>();
 }
 
-template <int TI, int KT, bool UNIFORM>
+template <int TI, int KT, bool UNIFORM, bool STAGED>
 int launch_resident_t(spdnn *c, const ResArgs &a, int grid) {
     static bool configured[64] = {};
     if (!configured[c->device & 63]) {
-        CK(cudaFuncSetAttribute(resident_kernel<TI, KT, UNIFORM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                (int)c->res_smem));
+        CK(cudaFuncSetAttribute(resident_kernel<TI, KT, UNIFORM, STAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                c->smem_optin - 1024));     // the kernel also has a little static shared memory
         configured[c->device & 63] = true;
     }
-    resident_kernel<TI, KT, UNIFORM><<<grid, kThreads, c->res_smem, c->stream>>>(a);
+    const size_t smem = c->res_smem + 2 * (size_t)a.table_bytes;
+    resident_kernel<TI, KT, UNIFORM, STAGED><<<grid, kThreads, smem, c->stream>>>(a);
     CK(cudaGetLastError());
     return SPDNN_OK;
 }
 
+template <int TI, bool STAGED>
+int launch_resident_s(spdnn *c, const ResArgs &a, int grid, bool k32, bool uniform) {
+    if (k32) return uniform ? launch_resident_t<TI, 32, true, STAGED>(c, a, grid) : launch_resident_t<TI, 32, false, STAGED>(c, a, grid);
+    return uniform ? launch_resident_t<TI, 0, true, STAGED>(c, a, grid) : launch_resident_t<TI, 0, false, STAGED>(c, a, grid);
+}
+
 template <int TI>
 int launch_resident_ti(spdnn *c, const ResArgs &a, int grid, bool k32, bool uniform) {
-    if (k32) return uniform ? launch_resident_t<TI, 32, true>(c, a, grid) : launch_resident_t<TI, 32, false>(c, a, grid);
-    return uniform ? launch_resident_t<TI, 0, true>(c, a, grid) : launch_resident_t<TI, 0, false>(c, a, grid);
+    return a.table_bytes > 0 ? launch_resident_s<TI, true>(c, a, grid, k32, uniform)
+                             : launch_resident_s<TI, false>(c, a, grid, k32, uniform);
 }
 
 int launch_resident(spdnn *c, const ResArgs &a, int grid, bool k32, bool uniform) {
@@ -241,8 +251,9 @@ int upload_res_table(spdnn *c) {
     std::vector<ResLayer> t(c->layers);
     for (int l = 0; l < c->layers; ++l) {
         const DevLayer &L = *c->layer[l];
-        t[l].roff = L.roff; t[l].vals = L.vals; t[l].mem_ptr = L.mem_ptr; t[l].rmem = L.rmem;
-        t[l].classes = L.classes; t[l].k = L.k; t[l].w = L.w; t[l].reserved = 0;
+        t[l].blob = L.rblob; t[l].blob_bytes = L.rblob_bytes;
+        t[l].o_mem_ptr = L.o_mem_ptr; t[l].o_rmem = L.o_rmem; t[l].o_vals = L.o_vals;
+        t[l].classes = L.classes; t[l].k = L.k; t[l].w = L.w;
     }
     CK(cudaMemcpyAsync(c->res_table, t.data(), sizeof(ResLayer) * t.size(), cudaMemcpyHostToDevice, c->stream));
     CK(cudaStreamSynchronize(c->stream));
@@ -260,13 +271,13 @@ int enqueue_layers(spdnn *c) {
         const DevLayer &L = *c->layer[l];
         const float *yin = c->y[step & 1];
         float *yout = c->y[(step & 1) ^ 1];
-        if (c->res_ti && L.roff) {
+        if (c->res_ti && L.rblob) {
             // a chunk holds layers of one kernel variant (all k == 32 or not, all uniform or not)
             const bool k32 = (L.k == 32), uniform = L.uniform;
             int f = 1;
             while (f < chunk && l + f < c->layers) {
                 const DevLayer &M = *c->layer[l + f];
-                if (!M.roff || M.uniform != uniform || (k32 && M.k != 32)) break;
+                if (!M.rblob || M.uniform != uniform || (k32 && M.k != 32)) break;
                 ++f;
             }
             bool all32 = k32;
@@ -277,6 +288,11 @@ int enqueue_layers(spdnn *c) {
             a.slot = c->slot; a.mask = c->mask; a.ids0 = c->ids[0]; a.ids1 = c->ids[1];
             a.counter = c->counter; a.work = c->counter + 1; a.status = c->status;
             a.layers = c->res_table + l; a.died_at = c->died_at + l; a.nlayers = f;
+            // stage the tables in shared memory when two of the chunk's largest fit beside the activations
+            int tb = 0;
+            for (int i = 0; i < f; ++i) tb = std::max(tb, c->layer[l + i]->rblob_bytes);
+            tb = (tb + 127) / 128 * 128;
+            a.table_bytes = (c->stage_tables && c->res_smem + 2 * (size_t)tb + 2048 <= (size_t)c->smem_optin) ? tb : 0;
             a.n = c->n; a.rows_even = (c->n + 1) & ~1; a.bias = c->bias; a.clip = c->clip;
             const int grid = std::max(1, (c->tiles_cap * 32 + c->res_ti - 1) / c->res_ti);
             int rc = launch_resident(c, a, grid, all32, uniform);
@@ -390,6 +406,8 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
         // the shared memory one block may opt in to
         int optin = 0;
         CK(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
+        c->smem_optin = optin;
+        if (const char *e = getenv("SPDNN_STAGE_TABLES")) c->stage_tables = atoi(e) != 0;
         const size_t rows = (size_t)((neurons + 1) & ~1) + 2;
         for (int ti : {16, 8, 4}) {
             const size_t need = 2 * rows * (size_t)ti * 4;
@@ -482,11 +500,11 @@ int spdnn_set_layer_csc(spdnn_t *c, int layer, const int32_t *col_ptr, const int
     CK(cudaMemcpyAsync(L->mem_ptr, p.mem_ptr.data(), sizeof(int32_t) * p.mem_ptr.size(), cudaMemcpyHostToDevice, c->stream));
     CK(cudaMalloc(&L->mem, sizeof(int32_t) * std::max<size_t>(p.mem.size(), 1)));
     CK(cudaMemcpyAsync(L->mem, p.mem.data(), sizeof(int32_t) * p.mem.size(), cudaMemcpyHostToDevice, c->stream));
-    if (!p.roff.empty()) {
-        CK(cudaMalloc(&L->roff, sizeof(int32_t) * std::max<size_t>(p.roff.size(), 4)));
-        CK(cudaMemcpyAsync(L->roff, p.roff.data(), sizeof(int32_t) * p.roff.size(), cudaMemcpyHostToDevice, c->stream));
-        CK(cudaMalloc(&L->rmem, sizeof(int32_t) * std::max<size_t>(p.rmem.size(), 1)));
-        CK(cudaMemcpyAsync(L->rmem, p.rmem.data(), sizeof(int32_t) * p.rmem.size(), cudaMemcpyHostToDevice, c->stream));
+    if (!p.rblob.empty()) {
+        L->rblob_bytes = (int)(sizeof(int32_t) * p.rblob.size());
+        L->o_mem_ptr = p.o_mem_ptr; L->o_rmem = p.o_rmem; L->o_vals = p.o_vals;
+        CK(cudaMalloc(&L->rblob, (size_t)L->rblob_bytes));
+        CK(cudaMemcpyAsync(L->rblob, p.rblob.data(), (size_t)L->rblob_bytes, cudaMemcpyHostToDevice, c->stream));
     }
     CK(cudaStreamSynchronize(c->stream));     // p's host vectors die with this call
     c->layer[layer] = L;
@@ -649,6 +667,8 @@ int spdnn_sync(spdnn_t *c, spdnn_stats_t *stats) {
         }
         s.algorithmic_bytes = bytes;
         s.kernel_launches = c->nsteps + c->prep_launches;
+        s.loop_launches = c->nsteps;
+        s.resident_group = (c->nsteps < c->layers) ? c->res_ti : 0;
         c->stats = s;
         c->result_ready = true;
     }

@@ -31,14 +31,19 @@
 namespace spdnn_impl {
 
 // Per-layer tables of the resident kernel (one entry per layer, in device memory).
+// All tables of a layer sit in one 16-byte aligned blob so that ONE bulk asynchronous copy
+// (TMA, cp.async.bulk) brings them into shared memory:
+//   int32 roff[U][K + 4]   byte offset of each input row inside an activation buffer (permuted rows);
+//                          4 ints of padding per class spread consecutive classes over the banks
+//   int32 mem_ptr[U + 1]   member ranges
+//   int32 rmem[N]          byte offsets of the member rows, grouped by class
+//   float vals[U][K + 4]   only when the weights are not one constant
 struct ResLayer {
-    const int32_t *roff;      // [U][K] byte offset of each input row inside an activation buffer (permuted rows)
-    const float *vals;        // [U][K] or nullptr
-    const int32_t *mem_ptr;   // [U+1]
-    const int32_t *rmem;      // [N] byte offsets of the member rows, grouped by class
+    const int32_t *blob;
+    int blob_bytes;           // multiple of 16
+    int o_mem_ptr, o_rmem, o_vals;   // offsets inside the blob, in 4-byte words (o_vals = 0: uniform weight)
     int classes, k;
     float w;
-    int reserved;
 };
 
 struct ResArgs {
@@ -55,6 +60,7 @@ struct ResArgs {
     const ResLayer *layers;   // first layer of this chunk
     int32_t *died_at;         // first layer of this chunk
     int nlayers;
+    int table_bytes;          // shared memory reserved per staged table (0 = read the tables from global memory)
     int n;                    // neurons
     int rows_even;            // n rounded up to even: index of the zero row
     float bias, clip;
@@ -91,28 +97,59 @@ __device__ __forceinline__ float4 mul4(const float4 v, float w) {
     return make_float4(__fmul_rn(v.x, w), __fmul_rn(v.y, w), __fmul_rn(v.z, w), __fmul_rn(v.w, w));
 }
 
+// ---- bulk asynchronous copy (TMA) of a layer's table blob into shared memory -------------------
+__device__ __forceinline__ unsigned int smem_u32(const void *p) { return (unsigned int)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned long long *bar, unsigned int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void bulk_load_table(void *dst, const void *src, unsigned int bytes, unsigned long long *bar) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Bounded wait: returns false when the copy has not landed after kMbarSpinLimit polls.
+constexpr int kMbarSpinLimit = 1 << 22;
+__device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned int parity) {
+    for (int i = 0; i < kMbarSpinLimit; ++i) {
+        unsigned int done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(smem_u32(bar)), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
 // Sum of one class for this thread's four images; `in` already points at the thread's 16-byte
-// column of the current activation buffer.
-template <int KT, bool UNIFORM>
-__device__ __forceinline__ float4 class_sum_resident(const ResLayer &L, int u, const unsigned char *in) {
+// column of the current activation buffer, `offs`/`vals` at the class's K entries (in shared
+// memory when STAGED, else in global memory).
+template <int KT, bool UNIFORM, bool STAGED>
+__device__ __forceinline__ float4 class_sum_resident(const int32_t *offs, const float *vals, int k, float w,
+                                                     const unsigned char *in) {
     float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    const int4 *o4 = reinterpret_cast<const int4 *>(offs);
+    const float4 *w4 = reinterpret_cast<const float4 *>(vals);
     if (KT > 0) {
         constexpr int KA = KT > 0 ? KT : 4;
-        const int4 *o4 = reinterpret_cast<const int4 *>(L.roff + (size_t)u * KT);
         int o[KA];
 #pragma unroll
         for (int i = 0; i < KT / 4; ++i) {
-            const int4 t = __ldg(o4 + i);
+            const int4 t = STAGED ? o4[i] : __ldg(o4 + i);
             o[4 * i + 0] = t.x; o[4 * i + 1] = t.y; o[4 * i + 2] = t.z; o[4 * i + 3] = t.w;
         }
         if (UNIFORM) {
 #pragma unroll
             for (int i = 0; i < KT; ++i) acc4(acc, *reinterpret_cast<const float4 *>(in + o[i]));
         } else {
-            const float4 *w4 = reinterpret_cast<const float4 *>(L.vals + (size_t)u * KT);
 #pragma unroll
             for (int i = 0; i < KT / 4; ++i) {
-                const float4 t = __ldg(w4 + i);
+                const float4 t = STAGED ? w4[i] : __ldg(w4 + i);
                 acc4(acc, mul4(*reinterpret_cast<const float4 *>(in + o[4 * i + 0]), t.x));
                 acc4(acc, mul4(*reinterpret_cast<const float4 *>(in + o[4 * i + 1]), t.y));
                 acc4(acc, mul4(*reinterpret_cast<const float4 *>(in + o[4 * i + 2]), t.z));
@@ -120,30 +157,30 @@ __device__ __forceinline__ float4 class_sum_resident(const ResLayer &L, int u, c
             }
         }
     } else {
-        const int k = L.k;
-        const int4 *o4 = reinterpret_cast<const int4 *>(L.roff + (size_t)u * k);
-        const float4 *w4 = UNIFORM ? nullptr : reinterpret_cast<const float4 *>(L.vals + (size_t)u * k);
         for (int i = 0; i < k / 4; ++i) {
-            const int4 t = __ldg(o4 + i);
+            const int4 t = STAGED ? o4[i] : __ldg(o4 + i);
             float4 a = *reinterpret_cast<const float4 *>(in + t.x), b = *reinterpret_cast<const float4 *>(in + t.y);
             float4 c = *reinterpret_cast<const float4 *>(in + t.z), e = *reinterpret_cast<const float4 *>(in + t.w);
             if (!UNIFORM) {
-                const float4 q = __ldg(w4 + i);
+                const float4 q = STAGED ? w4[i] : __ldg(w4 + i);
                 a = mul4(a, q.x); b = mul4(b, q.y); c = mul4(c, q.z); e = mul4(e, q.w);
             }
             acc4(acc, a); acc4(acc, b); acc4(acc, c); acc4(acc, e);
         }
     }
-    return UNIFORM ? mul4(acc, L.w) : acc;
+    return UNIFORM ? mul4(acc, w) : acc;
 }
 
 // Grid: one block per TI live images (launched for the worst case; surplus blocks only take
-// part in the last-block ticket).  Dynamic shared memory: 2 * (rows_even + 2) * TI * 4 bytes.
-template <int TI, int KT, bool UNIFORM>
+// part in the last-block ticket).  Dynamic shared memory: 2 * (rows_even + 2) * TI * 4 bytes for
+// the activations, then (STAGED) two table buffers of table_bytes each: while layer l is
+// computed from one, thread 0 has the table of layer l + 1 copied into the other.
+template <int TI, int KT, bool UNIFORM, bool STAGED>
 __global__ void __launch_bounds__(kThreads, 1) resident_kernel(const ResArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ unsigned int s_alive[3];
-    __shared__ int s_last;
+    __shared__ int s_last, s_fail;
+    __shared__ __align__(8) unsigned long long s_bar[2];
     constexpr int LPC = TI / 4;                  // threads per class
     constexpr int CPI = kThreads / LPC;          // classes per pass of the block
     constexpr int RS = TI * 4;                   // bytes per row
@@ -156,7 +193,15 @@ __global__ void __launch_bounds__(kThreads, 1) resident_kernel(const ResArgs a) 
 
     if ((int)blockIdx.x < nblk) {
         unsigned char *cur = smem, *nxt = smem + buf_bytes;
+        unsigned char *tbl[2] = {smem + 2 * buf_bytes, smem + 2 * buf_bytes + a.table_bytes};
         const int j0 = blockIdx.x * TI;
+        if (STAGED && tid == 0) {
+            mbar_init(&s_bar[0], 1);
+            mbar_init(&s_bar[1], 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            s_fail = 0;
+            bulk_load_table(tbl[0], a.layers[0].blob, (unsigned int)a.layers[0].blob_bytes, &s_bar[0]);
+        }
         // ---- load the block's images (dead images were dropped: read through the work list)
         const float *p[4];
         unsigned int my_valid = 0;
@@ -195,14 +240,33 @@ __global__ void __launch_bounds__(kThreads, 1) resident_kernel(const ResArgs a) 
         __syncthreads();
 
         // ---- the layers of this chunk
-        for (int li = 0; li < a.nlayers; ++li) {
+        int li = 0;
+        for (; li < a.nlayers; ++li) {
             const ResLayer L = a.layers[li];
-            if (tid == 0) s_alive[(li + 1) % 3] = 0u;
+            if (tid == 0) {
+                s_alive[(li + 1) % 3] = 0u;
+                // the other table buffer was last read in layer li - 1, which every thread has left
+                if (STAGED && li + 1 < a.nlayers) {
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    bulk_load_table(tbl[(li + 1) & 1], a.layers[li + 1].blob, (unsigned int)a.layers[li + 1].blob_bytes,
+                                    &s_bar[(li + 1) & 1]);
+                }
+            }
+            const int32_t *T = L.blob;
+            bool ready = true;
+            if (STAGED) {
+                ready = mbar_wait(&s_bar[li & 1], (unsigned int)((li >> 1) & 1));
+                if (!ready) s_fail = 1;
+                T = reinterpret_cast<const int32_t *>(tbl[li & 1]);
+            }
+            const int kp = L.k + 4;
             unsigned int bits = 0;
             const unsigned char *in = cur + sub * 16;
-            for (int u = grp; u < L.classes; u += CPI) {
-                const int mb = __ldg(L.mem_ptr + u), me = __ldg(L.mem_ptr + u + 1);
-                const float4 s = class_sum_resident<KT, UNIFORM>(L, u, in);
+            for (int u = grp; ready && u < L.classes; u += CPI) {
+                const int mb = STAGED ? T[L.o_mem_ptr + u] : __ldg(T + L.o_mem_ptr + u);
+                const int me = STAGED ? T[L.o_mem_ptr + u + 1] : __ldg(T + L.o_mem_ptr + u + 1);
+                const float4 s = class_sum_resident<KT, UNIFORM, STAGED>(
+                    T + (size_t)u * kp, reinterpret_cast<const float *>(T + L.o_vals) + (size_t)u * kp, L.k, L.w, in);
                 float4 y;
                 y.x = relu_clip(__fadd_rn(s.x, a.bias), a.clip);
                 y.y = relu_clip(__fadd_rn(s.y, a.bias), a.clip);
@@ -215,7 +279,7 @@ __global__ void __launch_bounds__(kThreads, 1) resident_kernel(const ResArgs a) 
                 if (!(al & 8u)) y.w = 0.0f;
                 bits |= (y.x != 0.0f ? 1u : 0u) | (y.y != 0.0f ? 2u : 0u) | (y.z != 0.0f ? 4u : 0u) | (y.w != 0.0f ? 8u : 0u);
                 for (int m = mb; m < me; ++m)
-                    *reinterpret_cast<float4 *>(nxt + __ldg(L.rmem + m) + sub * 16) = y;
+                    *reinterpret_cast<float4 *>(nxt + (STAGED ? T[L.o_rmem + m] : __ldg(T + L.o_rmem + m)) + sub * 16) = y;
             }
             const unsigned int wm = __reduce_or_sync(0xffffffffu, bits << (sub * 4));
             if (lane == 0 && wm) atomicOr(&s_alive[li % 3], wm);
@@ -227,7 +291,18 @@ __global__ void __launch_bounds__(kThreads, 1) resident_kernel(const ResArgs a) 
             }
             alive_prev = alive_now;
             unsigned char *t = cur; cur = nxt; nxt = t;
-            if (alive_prev == 0u) break;
+            if (STAGED && s_fail) {          // a table never arrived: report it and drop the block's images
+                if (tid == 0) atomicExch(a.status, 4);
+                alive_prev = 0u;
+            }
+            if (alive_prev == 0u) { ++li; break; }
+        }
+        if (STAGED && li < a.nlayers) {
+            // the loop was left early with the table of layer li still on its way: wait for it
+            // (bounded) so that the block does not exit, and its shared memory get reused, under
+            // a copy in flight
+            if (tid == 0 && !mbar_wait(&s_bar[li & 1], (unsigned int)((li >> 1) & 1))) atomicExch(a.status, 4);
+            __syncthreads();
         }
 
         // ---- write the survivors' activations back (dead blocks write nothing)

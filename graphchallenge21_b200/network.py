@@ -35,6 +35,8 @@ class InferResult:
     infer_ms: float
     algorithmic_bytes: float
     kernel_launches: int
+    loop_launches: int = 0
+    resident_group: int = 0
 
     @property
     def edges(self) -> float:
@@ -169,7 +171,7 @@ class SpDNN:
     @staticmethod
     def _result(s: _lib.Stats) -> InferResult:
         return InferResult(s.layers, s.batch, int(s.survivors), float(s.prepare_ms), float(s.infer_ms),
-                           float(s.algorithmic_bytes), int(s.kernel_launches))
+                           float(s.algorithmic_bytes), int(s.kernel_launches), int(s.loop_launches), int(s.resident_group))
 
     def infer(self) -> InferResult:
         s = _lib.Stats()

@@ -57,6 +57,8 @@ typedef struct spdnn_stats {
     float infer_ms;             /* device time of the layer loop incl. on-device compaction (CUDA events) */
     double algorithmic_bytes;   /* sum over layers of 4N(live_in + live_out) + bytes of W_l as CSC */
     int64_t kernel_launches;    /* kernels of this library launched by the last infer (+ last set_input) */
+    int32_t loop_launches;      /* of those, launches of the layer loop (1 per layer, or 1 per chunk of layers) */
+    int32_t resident_group;     /* images per block of the shared-memory-resident kernel, 0 = per-layer kernel */
 } spdnn_stats_t;
 
 /* Replaces GpuEnv::GpuEnv(gpu_id) + the allocations of all_network.cu:283-303.

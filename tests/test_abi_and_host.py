@@ -32,8 +32,8 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_stats_struct_matches_header_size():
-    # int32, int32, int64, float, float, double, int64
-    assert C.sizeof(_lib.Stats) == 40
+    # int32, int32, int64, float, float, double, int64, int32, int32
+    assert C.sizeof(_lib.Stats) == 48
 
 
 def test_inspect_layer_without_gpu():
