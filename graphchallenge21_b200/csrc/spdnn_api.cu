@@ -26,22 +26,39 @@ using namespace spdnn_impl;
 
 namespace {
 
+// Device copy of one layer's tables for the per-layer kernel, plus the canonical host form
+// the resident kernel's tables are derived from when the whole network is known.
 struct DevLayer {
     int32_t *off = nullptr;
     float *vals = nullptr;
     int32_t *mem_ptr = nullptr;
     int32_t *mem = nullptr;
-    int32_t *rblob = nullptr;                     // tables of the resident kernel in one blob (or null)
-    int rblob_bytes = 0, o_mem_ptr = 0, o_rmem = 0, o_vals = 0;
     int classes = 0, k = 0;
     bool uniform = false, identity_members = false;
     float w = 0.0f;
     int64_t nnz = 0;
     uint64_t h1 = 0, h2 = 0;
     int device = 0;
+    std::shared_ptr<HostLayer> host;      // null when the host copy was not kept (resident kernel unavailable)
     ~DevLayer() {
         cudaSetDevice(device);
-        cudaFree(off); cudaFree(vals); cudaFree(mem_ptr); cudaFree(mem); cudaFree(rblob);
+        cudaFree(off); cudaFree(vals); cudaFree(mem_ptr); cudaFree(mem);
+    }
+};
+
+// Device copy of one layer's tables for the resident kernel.  They depend on the layer AND on
+// the classes of the layer before it (its value ids).
+struct DevRes {
+    int32_t *blob = nullptr, *rep = nullptr, *mem_ptr = nullptr, *mem = nullptr;
+    int blob_bytes = 0, o_vals = 0, classes = 0, k = 0, v_in = 0, mode = 0;
+    bool uniform = false;
+    float w = 0.0f;
+    std::vector<int32_t> class_of;        // value ids this layer hands to the next one
+    uint64_t partition_hash = 0;
+    int device = 0;
+    ~DevRes() {
+        cudaSetDevice(device);
+        cudaFree(blob); cudaFree(rep); cudaFree(mem_ptr); cudaFree(mem);
     }
 };
 
@@ -56,6 +73,9 @@ struct spdnn {
 
     std::vector<std::shared_ptr<DevLayer>> layer;
     std::unordered_map<uint64_t, std::weak_ptr<DevLayer>> shared;   // content hash -> layer
+    std::vector<std::shared_ptr<DevRes>> res;                        // per layer, built when the graph is
+    std::unordered_map<uint64_t, std::weak_ptr<DevRes>> res_shared;  // (layer, input partition) -> tables
+    size_t host_bytes = 0, host_budget = (size_t)16 << 30;           // canonical layers kept on the host
 
     long long tile_stride = 0;
     int tiles_cap = 0;
@@ -63,8 +83,9 @@ struct spdnn {
     LoopCtl *ctl = nullptr;            // one record per launch boundary (at most layers + 1)
     int32_t *died_at = nullptr;        // [layers] images that died in each layer
     ResLayer *res_table = nullptr;     // [layers] tables of the resident kernel
-    int res_ti = 0;                    // images per block of the resident kernel (0 = not usable)
-    size_t res_smem = 0;               // bytes of its two activation buffers
+    bool resident = true;              // use the shared-memory-resident kernel where a chunk fits
+    int res_ti_max = 16;               // largest group of images per block to try
+    int last_group = 0;                // group size of the last captured schedule's resident launches
     int smem_optin = 0;                // shared memory one block may opt in to
     bool stage_tables = true;          // bring the per-layer tables into shared memory with bulk copies
     int chunk_first = 4, chunk_max = 128;
@@ -211,92 +232,170 @@ int blocks_per_sm(int k, bool uniform) {
     return uniform ? blocks_per_sm_t<0, true>() : blocks_per_sm_t<0, false>();
 }
 
-template <int TI, int KT, bool UNIFORM, bool STAGED>
-int launch_resident_t(spdnn *c, const ResArgs &a, int grid) {
+template <int TI, int MODE, int KT, bool UNIFORM, bool STAGED>
+int launch_resident_t(spdnn *c, const ResArgs &a, int grid, size_t smem) {
     static bool configured[64] = {};
     if (!configured[c->device & 63]) {
-        CK(cudaFuncSetAttribute(resident_kernel<TI, KT, UNIFORM, STAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        CK(cudaFuncSetAttribute(resident_kernel<TI, MODE, KT, UNIFORM, STAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 c->smem_optin - 1024));     // the kernel also has a little static shared memory
         configured[c->device & 63] = true;
     }
-    const size_t smem = c->res_smem + 2 * (size_t)a.table_bytes;
-    resident_kernel<TI, KT, UNIFORM, STAGED><<<grid, kThreads, smem, c->stream>>>(a);
+    resident_kernel<TI, MODE, KT, UNIFORM, STAGED><<<grid, kThreads, smem, c->stream>>>(a);
     CK(cudaGetLastError());
     return SPDNN_OK;
 }
 
-template <int TI, bool STAGED>
-int launch_resident_s(spdnn *c, const ResArgs &a, int grid, bool k32, bool uniform) {
-    if (k32) return uniform ? launch_resident_t<TI, 32, true, STAGED>(c, a, grid) : launch_resident_t<TI, 32, false, STAGED>(c, a, grid);
-    return uniform ? launch_resident_t<TI, 0, true, STAGED>(c, a, grid) : launch_resident_t<TI, 0, false, STAGED>(c, a, grid);
-}
-
 template <int TI>
-int launch_resident_ti(spdnn *c, const ResArgs &a, int grid, bool k32, bool uniform) {
-    return a.table_bytes > 0 ? launch_resident_s<TI, true>(c, a, grid, k32, uniform)
-                             : launch_resident_s<TI, false>(c, a, grid, k32, uniform);
+int launch_resident_ti(spdnn *c, const ResArgs &a, int grid, size_t smem, int mode, bool k32, bool uniform) {
+    const bool staged = a.table_bytes > 0;
+    if (mode == kResAlt2) {       // always uniform
+        if (k32) return staged ? launch_resident_t<TI, kResAlt2, 32, true, true>(c, a, grid, smem)
+                               : launch_resident_t<TI, kResAlt2, 32, true, false>(c, a, grid, smem);
+        return staged ? launch_resident_t<TI, kResAlt2, 0, true, true>(c, a, grid, smem)
+                      : launch_resident_t<TI, kResAlt2, 0, true, false>(c, a, grid, smem);
+    }
+    if (k32) {
+        if (uniform) return staged ? launch_resident_t<TI, kResGeneric, 32, true, true>(c, a, grid, smem)
+                                   : launch_resident_t<TI, kResGeneric, 32, true, false>(c, a, grid, smem);
+        return staged ? launch_resident_t<TI, kResGeneric, 32, false, true>(c, a, grid, smem)
+                      : launch_resident_t<TI, kResGeneric, 32, false, false>(c, a, grid, smem);
+    }
+    if (uniform) return staged ? launch_resident_t<TI, kResGeneric, 0, true, true>(c, a, grid, smem)
+                               : launch_resident_t<TI, kResGeneric, 0, true, false>(c, a, grid, smem);
+    return staged ? launch_resident_t<TI, kResGeneric, 0, false, true>(c, a, grid, smem)
+                  : launch_resident_t<TI, kResGeneric, 0, false, false>(c, a, grid, smem);
 }
 
-int launch_resident(spdnn *c, const ResArgs &a, int grid, bool k32, bool uniform) {
-    switch (c->res_ti) {
-        case 16: return launch_resident_ti<16>(c, a, grid, k32, uniform);
-        case 8: return launch_resident_ti<8>(c, a, grid, k32, uniform);
-        default: return launch_resident_ti<4>(c, a, grid, k32, uniform);
+int launch_resident(spdnn *c, int ti, const ResArgs &a, int grid, size_t smem, int mode, bool k32, bool uniform) {
+    switch (ti) {
+        case 16: return launch_resident_ti<16>(c, a, grid, smem, mode, k32, uniform);
+        case 8: return launch_resident_ti<8>(c, a, grid, smem, mode, k32, uniform);
+        default: return launch_resident_ti<4>(c, a, grid, smem, mode, k32, uniform);
     }
 }
 
-// Uploads the resident kernel's per-layer table (outside stream capture).
-int upload_res_table(spdnn *c) {
-    if (!c->res_ti) return SPDNN_OK;
-    std::vector<ResLayer> t(c->layers);
+template <typename T>
+int upload_vec(spdnn *c, T **dst, const std::vector<T> &v) {
+    if (v.empty()) return SPDNN_OK;
+    CK(cudaMalloc(dst, sizeof(T) * v.size()));
+    CK(cudaMemcpyAsync(*dst, v.data(), sizeof(T) * v.size(), cudaMemcpyHostToDevice, c->stream));
+    return SPDNN_OK;
+}
+
+// Builds (outside stream capture) the resident kernel's tables for every layer whose
+// canonical form is on the host, walking the network front to back because a layer's tables
+// are written in the value ids the layer before it produces.
+int prepare_resident(spdnn *c) {
+    for (auto &r : c->res) r.reset();
+    if (!c->resident) return SPDNN_OK;
+    const int32_t *vid = nullptr;      // value ids of the current layer's input (null: the neurons themselves)
+    int v_in = c->n;
+    uint64_t in_hash = 0;
     for (int l = 0; l < c->layers; ++l) {
         const DevLayer &L = *c->layer[l];
-        t[l].blob = L.rblob; t[l].blob_bytes = L.rblob_bytes;
-        t[l].o_mem_ptr = L.o_mem_ptr; t[l].o_rmem = L.o_rmem; t[l].o_vals = L.o_vals;
-        t[l].classes = L.classes; t[l].k = L.k; t[l].w = L.w;
+        if (!L.host) { vid = nullptr; v_in = c->n; in_hash = 0; continue; }
+        const uint64_t key = mix64(L.h1 ^ mix64(in_hash + 0x1234567ull));
+        std::shared_ptr<DevRes> R;
+        auto it = c->res_shared.find(key);
+        if (it != c->res_shared.end()) R = it->second.lock();
+        if (!R) {
+            ResidentTables t;
+            try {
+                build_resident_tables(*L.host, vid, v_in, t);
+            } catch (const std::bad_alloc &) {
+                return fail(c, SPDNN_ERR_MEMORY, "out of host memory preparing layer %d", l);
+            }
+            R = std::make_shared<DevRes>();
+            R->device = c->device;
+            t.blob.resize((t.blob.size() + 3) / 4 * 4, 0);       // bulk copies move multiples of 16 bytes
+            R->blob_bytes = (int)(t.blob.size() * 4);
+            R->o_vals = t.o_vals; R->classes = t.classes; R->k = L.k; R->v_in = t.v_in; R->mode = t.mode;
+            R->uniform = L.uniform; R->w = L.w;
+            int rc = upload_vec(c, &R->blob, t.blob);
+            if (!rc) rc = upload_vec(c, &R->rep, t.rep);
+            if (!rc) rc = upload_vec(c, &R->mem_ptr, t.mem_ptr);
+            if (!rc) rc = upload_vec(c, &R->mem, t.mem);
+            if (rc) return rc;
+            CK(cudaStreamSynchronize(c->stream));
+            R->class_of.swap(t.class_of);
+            R->partition_hash = t.partition_hash;
+            c->res_shared[key] = R;
+        }
+        c->res[l] = R;
+        if (R->classes < c->n) { vid = R->class_of.data(); v_in = R->classes; in_hash = R->partition_hash; }
+        else { vid = nullptr; v_in = c->n; in_hash = 0; }
+    }
+    std::vector<ResLayer> t(c->layers);
+    for (int l = 0; l < c->layers; ++l) {
+        ResLayer e{};
+        if (c->res[l]) {
+            const DevRes &R = *c->res[l];
+            e.blob = R.blob; e.rep = R.rep; e.mem_ptr = R.mem_ptr; e.mem = R.mem;
+            e.blob_bytes = R.blob_bytes; e.o_vals = R.o_vals; e.classes = R.classes; e.k = R.k; e.v_in = R.v_in; e.w = R.w;
+        }
+        t[l] = e;
     }
     CK(cudaMemcpyAsync(c->res_table, t.data(), sizeof(ResLayer) * t.size(), cudaMemcpyHostToDevice, c->stream));
     CK(cudaStreamSynchronize(c->stream));
     return SPDNN_OK;
 }
 
-// Enqueues the whole network: chunks of layers through the resident kernel when a group of
-// images fits in shared memory (chunk lengths 4, 8, 16, ... up to chunk_max: short while images
-// still die, long once the survivors are stable), one launch per layer otherwise.
+// Rows one activation buffer needs for layer l inside a resident chunk.
+inline int resident_rows(const DevRes &R) { return ((std::max(R.v_in, R.classes) + 1) & ~1) + 2; }
+
+// Enqueues the whole network: chunks of layers through the resident kernel where a group of
+// images fits in shared memory (chunk lengths chunk_first, x2, ... up to chunk_max: short while
+// images still die, long once the survivors are stable), one launch per layer otherwise.
 int enqueue_layers(spdnn *c) {
-    int step = 0;
-    int l = 0;
-    int chunk = c->chunk_first;
+    int step = 0, l = 0, chunk = c->chunk_first;
+    c->last_group = 0;
     while (l < c->layers) {
         const DevLayer &L = *c->layer[l];
         const float *yin = c->y[step & 1];
         float *yout = c->y[(step & 1) ^ 1];
-        if (c->res_ti && L.rblob) {
-            // a chunk holds layers of one kernel variant (all k == 32 or not, all uniform or not)
-            const bool k32 = (L.k == 32), uniform = L.uniform;
-            int f = 1;
-            while (f < chunk && l + f < c->layers) {
-                const DevLayer &M = *c->layer[l + f];
-                if (!M.rblob || M.uniform != uniform || (k32 && M.k != 32)) break;
-                ++f;
+        // ---- try a resident chunk starting at layer l
+        int f = 0, ti = 0, rows = 0, tb = 0;
+        if (c->res[l]) {
+            const DevRes &R0 = *c->res[l];
+            const bool k32 = (R0.k == 32);
+            auto fits = [&](int t_i, int r, int table) {
+                return 2 * (size_t)r * t_i * 4 + 2 * (size_t)table + 2048 <= (size_t)c->smem_optin;
+            };
+            rows = resident_rows(R0);
+            for (int t_i : {16, 8, 4})
+                if (t_i <= c->res_ti_max && fits(t_i, rows, 0)) { ti = t_i; break; }
+            if (ti) {
+                // extend while the layers are of one kernel variant and the group still fits
+                f = 1;
+                int blob = R0.blob_bytes;
+                while (f < chunk && l + f < c->layers && c->res[l + f]) {
+                    const DevRes &M = *c->res[l + f];
+                    if (M.mode != R0.mode || M.uniform != R0.uniform || (M.k == 32) != k32) break;
+                    const int r2 = std::max(rows, resident_rows(M));
+                    if (!fits(ti, r2, 0)) break;
+                    rows = r2;
+                    blob = std::max(blob, M.blob_bytes);
+                    ++f;
+                }
+                tb = (blob + 127) / 128 * 128;
+                if (!(c->stage_tables && fits(ti, rows, tb))) tb = 0;
             }
-            bool all32 = k32;
-            for (int i = 0; i < f && all32; ++i) all32 = (c->layer[l + i]->k == 32);
+        }
+        if (f > 0) {
+            const DevRes &R0 = *c->res[l];
             ResArgs a;
             a.yin = yin; a.yout = yout; a.tile_stride = c->tile_stride;
             a.ctl_in = c->ctl + step; a.ctl_out = c->ctl + step + 1;
             a.slot = c->slot; a.mask = c->mask; a.ids0 = c->ids[0]; a.ids1 = c->ids[1];
             a.counter = c->counter; a.work = c->counter + 1; a.status = c->status;
             a.layers = c->res_table + l; a.died_at = c->died_at + l; a.nlayers = f;
-            // stage the tables in shared memory when two of the chunk's largest fit beside the activations
-            int tb = 0;
-            for (int i = 0; i < f; ++i) tb = std::max(tb, c->layer[l + i]->rblob_bytes);
-            tb = (tb + 127) / 128 * 128;
-            a.table_bytes = (c->stage_tables && c->res_smem + 2 * (size_t)tb + 2048 <= (size_t)c->smem_optin) ? tb : 0;
-            a.n = c->n; a.rows_even = (c->n + 1) & ~1; a.bias = c->bias; a.clip = c->clip;
-            const int grid = std::max(1, (c->tiles_cap * 32 + c->res_ti - 1) / c->res_ti);
-            int rc = launch_resident(c, a, grid, all32, uniform);
+            a.buf_rows = rows; a.table_bytes = tb;
+            a.n = c->n; a.bias = c->bias; a.clip = c->clip;
+            const int grid = std::max(1, (c->tiles_cap * 32 + ti - 1) / ti);
+            const size_t smem = 2 * (size_t)rows * ti * 4 + 2 * (size_t)tb;
+            int rc = launch_resident(c, ti, a, grid, smem, R0.mode, R0.k == 32, R0.uniform);
             if (rc) return rc;
+            c->last_group = ti;
             l += f;
             chunk = std::min(chunk * 2, c->chunk_max);
         } else {
@@ -337,7 +436,7 @@ int build_graph(spdnn *c) {
     if (c->graph_exec) { cudaGraphExecDestroy(c->graph_exec); c->graph_exec = nullptr; }
     cudaGraph_t g = nullptr;
     {
-        int rc0 = upload_res_table(c);
+        int rc0 = prepare_resident(c);
         if (rc0) return rc0;
     }
     CK(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
@@ -402,29 +501,20 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
     c->host_died.assign(layers, 0);
     c->host_live.assign(layers, 0);
     {
-        // resident kernel: two activation buffers of (rows_even + 2) rows x TI images must fit in
-        // the shared memory one block may opt in to
         int optin = 0;
         CK(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
         c->smem_optin = optin;
-        if (const char *e = getenv("SPDNN_STAGE_TABLES")) c->stage_tables = atoi(e) != 0;
-        const size_t rows = (size_t)((neurons + 1) & ~1) + 2;
-        for (int ti : {16, 8, 4}) {
-            const size_t need = 2 * rows * (size_t)ti * 4;
-            if (need + 1024 <= (size_t)optin) { c->res_ti = ti; c->res_smem = need; break; }
-        }
-        if (const char *e = getenv("SPDNN_RESIDENT")) if (atoi(e) == 0) c->res_ti = 0;
+        if (const char *e = getenv("SPDNN_RESIDENT")) c->resident = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_RESIDENT_TI")) {
             const int ti = atoi(e);
-            if ((ti == 16 || ti == 8 || ti == 4) && 2 * rows * (size_t)ti * 4 + 1024 <= (size_t)optin) {
-                c->res_ti = ti; c->res_smem = 2 * rows * (size_t)ti * 4;
-            }
+            if (ti == 16 || ti == 8 || ti == 4) c->res_ti_max = ti;
         }
+        if (const char *e = getenv("SPDNN_STAGE_TABLES")) c->stage_tables = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_CHUNK_FIRST")) c->chunk_first = std::max(1, atoi(e));
         if (const char *e = getenv("SPDNN_CHUNK_MAX")) c->chunk_max = std::max(1, atoi(e));
+        if (const char *e = getenv("SPDNN_HOST_BUDGET_MB")) c->host_budget = (size_t)atoll(e) << 20;
     }
-    if (const char *e = getenv("SPDNN_CLASSES_PER_ITEM")) c->cpi_override = atoi(e);
-    if (const char *e = getenv("SPDNN_GRID")) c->grid_override = atoi(e);
+    c->res.resize(layers);
     return SPDNN_OK;
 }
 
@@ -467,32 +557,34 @@ int spdnn_set_layer_csc(spdnn_t *c, int layer, const int32_t *col_ptr, const int
         int rc = spdnn_sync(c, nullptr);
         if (rc) return rc;
     }
-    PreparedLayer p;
+    auto host = std::make_shared<HostLayer>();
+    PerLayerTables p;
     std::string why;
     try {
-        why = prepare_layer(c->n, col_ptr, row_idx, val, p, c->res_ti * 4);
+        why = canonicalize_layer(c->n, col_ptr, row_idx, val, *host);
+        if (!why.empty()) return fail(c, SPDNN_ERR_ARG, "layer %d: %s", layer, why.c_str());
+        c->graph_dirty = true;
+        // equal layers share one device copy
+        auto it = c->shared.find(host->hash1);
+        if (it != c->shared.end()) {
+            if (auto sp = it->second.lock()) {
+                if (sp->h2 == host->hash2 && sp->k == host->k && sp->nnz == host->nnz) {
+                    c->layer[layer] = sp;
+                    return SPDNN_OK;
+                }
+            }
+        }
+        build_per_layer_tables(*host, p);
     } catch (const std::bad_alloc &) {
         return fail(c, SPDNN_ERR_MEMORY, "out of host memory preparing layer %d", layer);
     }
-    if (!why.empty()) return fail(c, SPDNN_ERR_ARG, "layer %d: %s", layer, why.c_str());
-    c->graph_dirty = true;
-    // equal layers share one device copy
-    auto it = c->shared.find(p.content_hash);
-    if (it != c->shared.end()) {
-        if (auto sp = it->second.lock()) {
-            if (sp->h2 == p.content_hash2 && sp->classes == p.classes && sp->k == p.k && sp->nnz == p.nnz) {
-                c->layer[layer] = sp;
-                return SPDNN_OK;
-            }
-        }
-    }
     auto L = std::make_shared<DevLayer>();
     L->device = c->device;
-    L->classes = p.classes; L->k = p.k; L->uniform = p.uniform; L->identity_members = p.identity_members;
-    L->w = p.w; L->nnz = p.nnz; L->h1 = p.content_hash; L->h2 = p.content_hash2;
+    L->classes = p.classes; L->k = host->k; L->uniform = host->uniform; L->identity_members = p.identity_members;
+    L->w = host->w; L->nnz = host->nnz; L->h1 = host->hash1; L->h2 = host->hash2;
     CK(cudaMalloc(&L->off, sizeof(int32_t) * std::max<size_t>(p.off.size(), 4)));
     CK(cudaMemcpyAsync(L->off, p.off.data(), sizeof(int32_t) * p.off.size(), cudaMemcpyHostToDevice, c->stream));
-    if (!p.uniform) {
+    if (!host->uniform) {
         CK(cudaMalloc(&L->vals, sizeof(float) * std::max<size_t>(p.vals.size(), 4)));
         CK(cudaMemcpyAsync(L->vals, p.vals.data(), sizeof(float) * p.vals.size(), cudaMemcpyHostToDevice, c->stream));
     }
@@ -500,15 +592,18 @@ int spdnn_set_layer_csc(spdnn_t *c, int layer, const int32_t *col_ptr, const int
     CK(cudaMemcpyAsync(L->mem_ptr, p.mem_ptr.data(), sizeof(int32_t) * p.mem_ptr.size(), cudaMemcpyHostToDevice, c->stream));
     CK(cudaMalloc(&L->mem, sizeof(int32_t) * std::max<size_t>(p.mem.size(), 1)));
     CK(cudaMemcpyAsync(L->mem, p.mem.data(), sizeof(int32_t) * p.mem.size(), cudaMemcpyHostToDevice, c->stream));
-    if (!p.rblob.empty()) {
-        L->rblob_bytes = (int)(sizeof(int32_t) * p.rblob.size());
-        L->o_mem_ptr = p.o_mem_ptr; L->o_rmem = p.o_rmem; L->o_vals = p.o_vals;
-        CK(cudaMalloc(&L->rblob, (size_t)L->rblob_bytes));
-        CK(cudaMemcpyAsync(L->rblob, p.rblob.data(), (size_t)L->rblob_bytes, cudaMemcpyHostToDevice, c->stream));
-    }
     CK(cudaStreamSynchronize(c->stream));     // p's host vectors die with this call
+    // the canonical form stays on the host (within a budget) for the resident kernel's tables
+    if (c->resident) {
+        if (host->uniform) std::vector<float>().swap(host->vals);
+        const size_t bytes = host->rows.size() * 4 + host->vals.size() * 4;
+        if (c->host_bytes + bytes <= c->host_budget) {
+            c->host_bytes += bytes;
+            L->host = host;
+        }
+    }
     c->layer[layer] = L;
-    c->shared[p.content_hash] = L;
+    c->shared[host->hash1] = L;
     return SPDNN_OK;
 }
 
@@ -668,7 +763,7 @@ int spdnn_sync(spdnn_t *c, spdnn_stats_t *stats) {
         s.algorithmic_bytes = bytes;
         s.kernel_launches = c->nsteps + c->prep_launches;
         s.loop_launches = c->nsteps;
-        s.resident_group = (c->nsteps < c->layers) ? c->res_ti : 0;
+        s.resident_group = c->last_group;
         c->stats = s;
         c->result_ready = true;
     }
@@ -745,15 +840,17 @@ int spdnn_get_layer_info(spdnn_t *c, int layer, int *classes, int *k, int *unifo
 
 int spdnn_inspect_layer_csc(int neurons, const int32_t *col_ptr, const int32_t *row_idx, const float *val,
                             int *classes, int *k, int *uniform) {
-    PreparedLayer p;
+    HostLayer h;
+    PerLayerTables p;
     try {
-        if (!prepare_layer(neurons, col_ptr, row_idx, val, p).empty()) return SPDNN_ERR_ARG;
+        if (!canonicalize_layer(neurons, col_ptr, row_idx, val, h).empty()) return SPDNN_ERR_ARG;
+        build_per_layer_tables(h, p);
     } catch (const std::bad_alloc &) {
         return SPDNN_ERR_MEMORY;
     }
     if (classes) *classes = p.classes;
-    if (k) *k = p.k;
-    if (uniform) *uniform = p.uniform ? 1 : 0;
+    if (k) *k = h.k;
+    if (uniform) *uniform = h.uniform ? 1 : 0;
     return SPDNN_OK;
 }
 

@@ -1,24 +1,33 @@
-// Resident kernel: several consecutive layers in ONE launch with the activations of a group
-// of images held in shared memory from the first to the last of those layers.
+// Resident kernel: a chunk of consecutive layers in ONE launch, with the activations of a
+// group of images held in shared memory from the first to the last layer of the chunk.
 //
 // Images are independent through the network, so a block that owns TI images can apply layer
-// after layer without touching global memory for Y: two activation buffers of (N + 2) x TI
-// floats ping-pong inside the block's shared memory (TI = 16 for N <= 1758, 8 or 4 for larger
-// N, as 227 KB allow), only the small per-layer index tables stream in through L1/L2.  This is
-// the idea of the reference's two-layer fusion (src/fuse/fuse.h:9-53, src/microbenchmark/fuse.cu:16-110:
-// layer-0 output kept in shared memory for layer 1) taken to a whole chunk of layers, made
-// possible by B200's shared-memory size.  HBM traffic per chunk is one read and one write of
-// the live images instead of one per layer.
+// after layer without touching global memory for Y.  This is the idea of the reference's
+// two-layer fusion (src/fuse/fuse.h:9-53, src/microbenchmark/fuse.cu:16-110: layer-0 output kept
+// in shared memory for layer 1) taken to whole chunks of layers, which B200's 227 KB of shared
+// memory per block allow.
 //
-// Thread mapping: a thread owns one class (group of identical columns) for FOUR images and
-// keeps a float4 of accumulators; every gather is one 16-byte shared-memory load, every pair
-// of adds one packed add.rn.f32x2 (sm_100 packed fp32), each element added in the same
-// ascending-input order as everywhere else, so results stay bit-identical to the per-layer
-// kernel and to the CPU loop of src/utils/cpu_spmm.h:14-43.
+// Inside a chunk the activations are stored by VALUE ID, not by neuron: all columns of a
+// class (identical inputs and weights) hold the same value, so a layer writes one row per
+// class and the next layer's tables name those rows directly (layer_inspect.h).  Two buffers
+// of rows x TI floats ping-pong; for the challenge networks that is N/16 rows instead of N.
+// At the start of a chunk one representative row per value id is read from the N-row tiles in
+// global memory, at its end every class is expanded back to all its member rows, so between
+// launches the layout is the one of the per-layer kernel.
+//
+// Thread mapping: a thread owns one class for FOUR images and keeps a float4 of accumulators;
+// a gather is one 16-byte shared-memory load, two adds are one packed add.rn.f32x2 (sm_100
+// packed fp32).  Each element is added in ascending-input order, so results are bit-identical
+// to the per-layer kernel and to the CPU loop of src/utils/cpu_spmm.h:14-43.  Two table forms:
+//   GENERIC  K row numbers per class, gathered one by one;
+//   ALT2     the K terms alternate between two rows a,b,a,b,... (what a 16-wide butterfly block
+//            looks like in value ids): two loads, then K adds in that order.
+// The per-layer tables come into shared memory by bulk asynchronous copy (TMA, cp.async.bulk
+// completing on an mbarrier), the table of layer l+1 while layer l is computed.
 //
 // Rows of the shared-memory buffers are permuted (row r sits at r ^ parity(r >> 1)) so that
-// classes whose rows all share one parity do not pile onto the same half of the banks; the
-// permutation is folded into the offset tables on the host and costs nothing here.
+// classes whose rows share one parity do not pile onto the same half of the banks; the
+// permutation is folded into the tables on the host.
 //
 // Survivors: an image dies in the layer after which all its activations are zero
 // (all_network.cu:57-59, 455-463) and stays dead; inside a chunk its activations are forced to
@@ -30,19 +39,19 @@
 
 namespace spdnn_impl {
 
+constexpr int kResGeneric = 0, kResAlt2 = 1;
+
 // Per-layer tables of the resident kernel (one entry per layer, in device memory).
-// All tables of a layer sit in one 16-byte aligned blob so that ONE bulk asynchronous copy
-// (TMA, cp.async.bulk) brings them into shared memory:
-//   int32 roff[U][K + 4]   byte offset of each input row inside an activation buffer (permuted rows);
-//                          4 ints of padding per class spread consecutive classes over the banks
-//   int32 mem_ptr[U + 1]   member ranges
-//   int32 rmem[N]          byte offsets of the member rows, grouped by class
-//   float vals[U][K + 4]   only when the weights are not one constant
 struct ResLayer {
-    const int32_t *blob;
+    const int32_t *blob;      // GENERIC: int32 t[U][k+4] (k input rows, then the output row) [+ float vals[U][k+4]]
+                              // ALT2:    int32 t[U][4] = {row a, row b, output row, 0}
+    const int32_t *rep;       // [v_in] neuron*32 carrying value id v, or nullptr (value id == neuron)
+    const int32_t *mem_ptr;   // [U+1] member ranges, or nullptr (class u == column u)
+    const int32_t *mem;       // member column*32
     int blob_bytes;           // multiple of 16
-    int o_mem_ptr, o_rmem, o_vals;   // offsets inside the blob, in 4-byte words (o_vals = 0: uniform weight)
+    int o_vals;               // word offset of the weights inside the blob (0: uniform weight)
     int classes, k;
+    int v_in;                 // rows of the input buffer
     float w;
 };
 
@@ -60,9 +69,9 @@ struct ResArgs {
     const ResLayer *layers;   // first layer of this chunk
     int32_t *died_at;         // first layer of this chunk
     int nlayers;
+    int buf_rows;             // rows of one activation buffer (largest layer of the chunk, even, + 2)
     int table_bytes;          // shared memory reserved per staged table (0 = read the tables from global memory)
     int n;                    // neurons
-    int rows_even;            // n rounded up to even: index of the zero row
     float bias, clip;
 };
 
@@ -126,14 +135,14 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned int 
     return false;
 }
 
-// Sum of one class for this thread's four images; `in` already points at the thread's 16-byte
-// column of the current activation buffer, `offs`/`vals` at the class's K entries (in shared
-// memory when STAGED, else in global memory).
-template <int KT, bool UNIFORM, bool STAGED>
-__device__ __forceinline__ float4 class_sum_resident(const int32_t *offs, const float *vals, int k, float w,
-                                                     const unsigned char *in) {
+// Sum of one class for this thread's four images, GENERIC tables.  `in` points at the thread's
+// 16-byte column of the current buffer, `rows`/`vals` at the class's K entries (in shared
+// memory when STAGED, else in global memory); a row number times RS is its byte offset.
+template <int KT, bool UNIFORM, bool STAGED, int RS>
+__device__ __forceinline__ float4 class_sum_generic(const int32_t *rows, const float *vals, int k, float w,
+                                                    const unsigned char *in) {
     float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    const int4 *o4 = reinterpret_cast<const int4 *>(offs);
+    const int4 *o4 = reinterpret_cast<const int4 *>(rows);
     const float4 *w4 = reinterpret_cast<const float4 *>(vals);
     if (KT > 0) {
         constexpr int KA = KT > 0 ? KT : 4;
@@ -141,7 +150,7 @@ __device__ __forceinline__ float4 class_sum_resident(const int32_t *offs, const 
 #pragma unroll
         for (int i = 0; i < KT / 4; ++i) {
             const int4 t = STAGED ? o4[i] : __ldg(o4 + i);
-            o[4 * i + 0] = t.x; o[4 * i + 1] = t.y; o[4 * i + 2] = t.z; o[4 * i + 3] = t.w;
+            o[4 * i + 0] = t.x * RS; o[4 * i + 1] = t.y * RS; o[4 * i + 2] = t.z * RS; o[4 * i + 3] = t.w * RS;
         }
         if (UNIFORM) {
 #pragma unroll
@@ -159,8 +168,8 @@ __device__ __forceinline__ float4 class_sum_resident(const int32_t *offs, const 
     } else {
         for (int i = 0; i < k / 4; ++i) {
             const int4 t = STAGED ? o4[i] : __ldg(o4 + i);
-            float4 a = *reinterpret_cast<const float4 *>(in + t.x), b = *reinterpret_cast<const float4 *>(in + t.y);
-            float4 c = *reinterpret_cast<const float4 *>(in + t.z), e = *reinterpret_cast<const float4 *>(in + t.w);
+            float4 a = *reinterpret_cast<const float4 *>(in + t.x * RS), b = *reinterpret_cast<const float4 *>(in + t.y * RS);
+            float4 c = *reinterpret_cast<const float4 *>(in + t.z * RS), e = *reinterpret_cast<const float4 *>(in + t.w * RS);
             if (!UNIFORM) {
                 const float4 q = STAGED ? w4[i] : __ldg(w4 + i);
                 a = mul4(a, q.x); b = mul4(b, q.y); c = mul4(c, q.z); e = mul4(e, q.w);
@@ -171,12 +180,24 @@ __device__ __forceinline__ float4 class_sum_resident(const int32_t *offs, const 
     return UNIFORM ? mul4(acc, w) : acc;
 }
 
+// ALT2: the K terms are a, b, a, b, ...
+template <int KT>
+__device__ __forceinline__ float4 class_sum_alt2(const float4 a, const float4 b, int k, float w) {
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (KT > 0) {
+#pragma unroll
+        for (int i = 0; i < KT / 2; ++i) { acc4(acc, a); acc4(acc, b); }
+    } else {
+        for (int i = 0; i < k / 2; ++i) { acc4(acc, a); acc4(acc, b); }
+    }
+    return mul4(acc, w);
+}
+
 // Grid: one block per TI live images (launched for the worst case; surplus blocks only take
-// part in the last-block ticket).  Dynamic shared memory: 2 * (rows_even + 2) * TI * 4 bytes for
-// the activations, then (STAGED) two table buffers of table_bytes each: while layer l is
-// computed from one, thread 0 has the table of layer l + 1 copied into the other.
-template <int TI, int KT, bool UNIFORM, bool STAGED>
-__global__ void __launch_bounds__(kThreads, 1) resident_kernel(const ResArgs a) {
+// part in the last-block ticket).  Dynamic shared memory: two activation buffers of
+// buf_rows * TI * 4 bytes, then (STAGED) two table buffers of table_bytes each.
+template <int TI, int MODE, int KT, bool UNIFORM, bool STAGED>
+__global__ void __launch_bounds__(kThreads) resident_kernel(const ResArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ unsigned int s_alive[3];
     __shared__ int s_last, s_fail;
@@ -189,20 +210,24 @@ __global__ void __launch_bounds__(kThreads, 1) resident_kernel(const ResArgs a) 
     const LoopCtl ctl = *a.ctl_in;
     const int live_in = ctl.live;
     const int nblk = (live_in + TI - 1) / TI;
-    const int buf_bytes = (a.rows_even + 2) * RS;
+    const int buf_bytes = a.buf_rows * RS;
 
     if ((int)blockIdx.x < nblk) {
         unsigned char *cur = smem, *nxt = smem + buf_bytes;
-        unsigned char *tbl[2] = {smem + 2 * buf_bytes, smem + 2 * buf_bytes + a.table_bytes};
+        unsigned char *const tbl0 = smem + 2 * buf_bytes;      // table buffer q sits at tbl0 + q * table_bytes
         const int j0 = blockIdx.x * TI;
-        if (STAGED && tid == 0) {
-            mbar_init(&s_bar[0], 1);
-            mbar_init(&s_bar[1], 1);
-            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (tid == 0) {
+            s_alive[0] = 0u;
             s_fail = 0;
-            bulk_load_table(tbl[0], a.layers[0].blob, (unsigned int)a.layers[0].blob_bytes, &s_bar[0]);
+            if (STAGED) {
+                mbar_init(&s_bar[0], 1);
+                mbar_init(&s_bar[1], 1);
+                asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+                bulk_load_table(tbl0, a.layers[0].blob, (unsigned int)a.layers[0].blob_bytes, &s_bar[0]);
+            }
         }
-        // ---- load the block's images (dead images were dropped: read through the work list)
+        // ---- load one row per value id of the block's images (dead images were dropped: read
+        //      through the work list)
         const float *p[4];
         unsigned int my_valid = 0;
         bool contiguous = ctl.identity != 0;
@@ -216,24 +241,26 @@ __global__ void __launch_bounds__(kThreads, 1) resident_kernel(const ResArgs a) 
             p[q] = a.yin + (size_t)(src >> 5) * a.tile_stride + (src & 31);
         }
         if (my_valid != 0xFu) contiguous = false;
-        for (int r = grp; r < a.n; r += CPI) {
-            float4 v;
-            if (contiguous) {
-                v = __ldg(reinterpret_cast<const float4 *>(p[0] + (size_t)r * 32));
-            } else {
-                v.x = (my_valid & 1u) ? __ldg(p[0] + (size_t)r * 32) : 0.0f;
-                v.y = (my_valid & 2u) ? __ldg(p[1] + (size_t)r * 32) : 0.0f;
-                v.z = (my_valid & 4u) ? __ldg(p[2] + (size_t)r * 32) : 0.0f;
-                v.w = (my_valid & 8u) ? __ldg(p[3] + (size_t)r * 32) : 0.0f;
+        {
+            const ResLayer L0 = a.layers[0];
+            for (int v = grp; v < L0.v_in; v += CPI) {
+                const size_t e = L0.rep ? (size_t)__ldg(L0.rep + v) : (size_t)v * 32;
+                float4 x;
+                if (contiguous) {
+                    x = __ldg(reinterpret_cast<const float4 *>(p[0] + e));
+                } else {
+                    x.x = (my_valid & 1u) ? __ldg(p[0] + e) : 0.0f;
+                    x.y = (my_valid & 2u) ? __ldg(p[1] + e) : 0.0f;
+                    x.z = (my_valid & 4u) ? __ldg(p[2] + e) : 0.0f;
+                    x.w = (my_valid & 8u) ? __ldg(p[3] + e) : 0.0f;
+                }
+                *reinterpret_cast<float4 *>(cur + resident_phys_row(v) * RS + sub * 16) = x;
             }
-            *reinterpret_cast<float4 *>(cur + resident_phys_row(r) * RS + sub * 16) = v;
+            // rows v_in .. even(v_in) + 1 are the zero rows padded table entries point at
+            const int ve = (L0.v_in + 1) & ~1;
+            for (int r = L0.v_in + grp; r < ve + 2; r += CPI)
+                *reinterpret_cast<float4 *>(cur + (r < ve ? resident_phys_row(r) : r) * RS + sub * 16) = make_float4(0, 0, 0, 0);
         }
-        // rows n .. rows_even + 1 of both buffers are the zero rows padded entries point at
-        for (int r = a.n + grp; r < a.rows_even + 2; r += CPI) {
-            *reinterpret_cast<float4 *>(cur + (r < a.rows_even ? resident_phys_row(r) : r) * RS + sub * 16) = make_float4(0, 0, 0, 0);
-            *reinterpret_cast<float4 *>(nxt + (r < a.rows_even ? resident_phys_row(r) : r) * RS + sub * 16) = make_float4(0, 0, 0, 0);
-        }
-        if (tid == 0) s_alive[0] = 0u;
         // LPC divides 32, so every warp holds all sub-columns: the OR over a warp is the block's
         // mask of valid images (bit i = image j0 + i), identical in every thread
         unsigned int alive_prev = __reduce_or_sync(0xffffffffu, my_valid << (sub * 4));
@@ -248,7 +275,7 @@ __global__ void __launch_bounds__(kThreads, 1) resident_kernel(const ResArgs a) 
                 // the other table buffer was last read in layer li - 1, which every thread has left
                 if (STAGED && li + 1 < a.nlayers) {
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    bulk_load_table(tbl[(li + 1) & 1], a.layers[li + 1].blob, (unsigned int)a.layers[li + 1].blob_bytes,
+                    bulk_load_table(tbl0 + ((li + 1) & 1) * a.table_bytes, a.layers[li + 1].blob, (unsigned int)a.layers[li + 1].blob_bytes,
                                     &s_bar[(li + 1) & 1]);
                 }
             }
@@ -257,16 +284,26 @@ __global__ void __launch_bounds__(kThreads, 1) resident_kernel(const ResArgs a) 
             if (STAGED) {
                 ready = mbar_wait(&s_bar[li & 1], (unsigned int)((li >> 1) & 1));
                 if (!ready) s_fail = 1;
-                T = reinterpret_cast<const int32_t *>(tbl[li & 1]);
+                T = reinterpret_cast<const int32_t *>(tbl0 + (li & 1) * a.table_bytes);
             }
-            const int kp = L.k + 4;
             unsigned int bits = 0;
             const unsigned char *in = cur + sub * 16;
             for (int u = grp; ready && u < L.classes; u += CPI) {
-                const int mb = STAGED ? T[L.o_mem_ptr + u] : __ldg(T + L.o_mem_ptr + u);
-                const int me = STAGED ? T[L.o_mem_ptr + u + 1] : __ldg(T + L.o_mem_ptr + u + 1);
-                const float4 s = class_sum_resident<KT, UNIFORM, STAGED>(
-                    T + (size_t)u * kp, reinterpret_cast<const float *>(T + L.o_vals) + (size_t)u * kp, L.k, L.w, in);
+                float4 s;
+                int out_row;
+                if (MODE == kResAlt2) {
+                    const int4 e = STAGED ? reinterpret_cast<const int4 *>(T)[u] : __ldg(reinterpret_cast<const int4 *>(T) + u);
+                    const float4 va = *reinterpret_cast<const float4 *>(in + e.x * RS);
+                    const float4 vb = *reinterpret_cast<const float4 *>(in + e.y * RS);
+                    s = class_sum_alt2<KT>(va, vb, L.k, L.w);
+                    out_row = e.z;
+                } else {
+                    const int kp = L.k + 4;
+                    const int32_t *rows = T + (size_t)u * kp;
+                    s = class_sum_generic<KT, UNIFORM, STAGED, RS>(rows, reinterpret_cast<const float *>(T + L.o_vals) + (size_t)u * kp,
+                                                                   L.k, L.w, in);
+                    out_row = STAGED ? rows[L.k] : __ldg(rows + L.k);
+                }
                 float4 y;
                 y.x = relu_clip(__fadd_rn(s.x, a.bias), a.clip);
                 y.y = relu_clip(__fadd_rn(s.y, a.bias), a.clip);
@@ -278,8 +315,13 @@ __global__ void __launch_bounds__(kThreads, 1) resident_kernel(const ResArgs a) 
                 if (!(al & 4u)) y.z = 0.0f;
                 if (!(al & 8u)) y.w = 0.0f;
                 bits |= (y.x != 0.0f ? 1u : 0u) | (y.y != 0.0f ? 2u : 0u) | (y.z != 0.0f ? 4u : 0u) | (y.w != 0.0f ? 8u : 0u);
-                for (int m = mb; m < me; ++m)
-                    *reinterpret_cast<float4 *>(nxt + (STAGED ? T[L.o_rmem + m] : __ldg(T + L.o_rmem + m)) + sub * 16) = y;
+                *reinterpret_cast<float4 *>(nxt + out_row * RS + sub * 16) = y;
+            }
+            {
+                // zero rows of the buffer just written (the next layer's padded entries point there)
+                const int ue = (L.classes + 1) & ~1;
+                for (int r = L.classes + grp; r < ue + 2; r += CPI)
+                    *reinterpret_cast<float4 *>(nxt + (r < ue ? resident_phys_row(r) : r) * RS + sub * 16) = make_float4(0, 0, 0, 0);
             }
             const unsigned int wm = __reduce_or_sync(0xffffffffu, bits << (sub * 4));
             if (lane == 0 && wm) atomicOr(&s_alive[li % 3], wm);
@@ -291,7 +333,7 @@ __global__ void __launch_bounds__(kThreads, 1) resident_kernel(const ResArgs a) 
             }
             alive_prev = alive_now;
             unsigned char *t = cur; cur = nxt; nxt = t;
-            if (STAGED && s_fail) {          // a table never arrived: report it and drop the block's images
+            if (s_fail) {                    // a table never arrived: report it and drop the block's images
                 if (tid == 0) atomicExch(a.status, 4);
                 alive_prev = 0u;
             }
@@ -305,13 +347,20 @@ __global__ void __launch_bounds__(kThreads, 1) resident_kernel(const ResArgs a) 
             __syncthreads();
         }
 
-        // ---- write the survivors' activations back (dead blocks write nothing)
+        // ---- expand the survivors' classes to all member rows (dead blocks write nothing)
         if (alive_prev != 0u) {
+            const ResLayer LL = a.layers[li - 1];
             const int tile = j0 >> 5, lane0 = j0 & 31;
             float *out = a.yout + (size_t)tile * a.tile_stride + lane0 + sub * 4;
-            for (int r = grp; r < a.n; r += CPI)
-                *reinterpret_cast<float4 *>(out + (size_t)r * 32) =
-                    *reinterpret_cast<const float4 *>(cur + resident_phys_row(r) * RS + sub * 16);
+            for (int u = grp; u < LL.classes; u += CPI) {
+                const float4 y = *reinterpret_cast<const float4 *>(cur + resident_phys_row(u) * RS + sub * 16);
+                if (LL.mem_ptr == nullptr) {
+                    *reinterpret_cast<float4 *>(out + (size_t)u * 32) = y;
+                } else {
+                    const int mb = __ldg(LL.mem_ptr + u), me = __ldg(LL.mem_ptr + u + 1);
+                    for (int m = mb; m < me; ++m) *reinterpret_cast<float4 *>(out + __ldg(LL.mem + m)) = y;
+                }
+            }
             if (tid == 0) atomicOr(a.mask + tile, alive_prev << lane0);
         }
     }
