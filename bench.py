@@ -68,7 +68,7 @@ def peaks():
 
 
 def ncu_traffic(cfg, pattern):
-    """DRAM bytes (read + write) per launch of the layer kernel on this workload, from the
+    """DRAM bytes (read + write) per LAYER of the dominant kernel on this workload, from the
     committed summary of an ncu capture (profiles/); None when no capture covers it."""
     path = os.path.join(ROOT, "profiles", "layer_kernel_traffic.json")
     if not os.path.exists(path):
@@ -76,59 +76,59 @@ def ncu_traffic(cfg, pattern):
     try:
         for rec in json.load(open(path)):
             if rec.get("neurons") == cfg["neurons"] and rec.get("pattern") == pattern:
-                return rec.get("dram_bytes_per_launch")
+                return rec.get("dram_bytes_per_layer")
     except Exception:
         return None
     return None
 
 
 class ClockSampler:
-    """nvidia-smi samples of the SM clock and throttle reasons during the timed region."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    """SM clock and throttle reasons DURING the timed region: an NVML polling thread (the
+    region lasts tens of milliseconds, shorter than one nvidia-smi interval)."""
+    REASONS = {"hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40, "sw_power_cap": 0x4}
 
     def __init__(self, index):
-        self.index, self.proc, self.path = index, None, None
+        self.index, self.samples, self.bits, self.max_mhz, self.thread, self.stop_flag = index, [], 0, None, None, False
+        self.power = []
+
+    def _run(self, nv, h):
+        while not self.stop_flag:
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                self.bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))
+                self.power.append(nv.nvmlDeviceGetPowerUsage(h) / 1000.0)
+            except Exception:
+                pass
+            time.sleep(0.001)
 
     def start(self):
         try:
-            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
-            self.path = f.name
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.index)], stdout=f, stderr=subprocess.DEVNULL)
+            import threading
+            import pynvml as nv
+            nv.nvmlInit()
+            idx = self.index
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            if vis:
+                try:
+                    idx = int(vis.split(",")[self.index])
+                except Exception:
+                    pass
+            h = nv.nvmlDeviceGetHandleByIndex(idx)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            self.thread = threading.Thread(target=self._run, args=(nv, h), daemon=True)
+            self.thread.start()
         except Exception:
-            self.proc = None
+            self.thread = None
 
     def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.proc is None:
-            return out
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        try:
-            for line in open(self.path):
-                f = [x.strip() for x in line.split(",")]
-                if len(f) < 9:
-                    continue
-                try:
-                    sm.append(float(f[1])); mx.append(float(f[2]))
-                except ValueError:
-                    continue
-                for nm, v in zip(names, f[5:9]):
-                    if v.lower().startswith("active"):
-                        reasons.add(nm)
-            os.unlink(self.path)
-        except Exception:
-            pass
-        if sm:
-            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), samples=len(sm))
-        out["reasons"] = sorted(reasons)
+        self.stop_flag = True
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+        out = {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": len(self.samples)}
+        if self.samples:
+            out["sm_mhz"] = statistics.median(self.samples)
+            out["power_w_max"] = max(self.power) if self.power else None
+        out["reasons"] = sorted(k for k, bit in self.REASONS.items() if self.bits & bit)
         return out
 
 
@@ -247,8 +247,16 @@ def main_ours(args):
         g.set_input_dense(y_dev, rank * B)
         g.infer_async()
 
-    def step_e2e():
-        g.set_input_dense(y_host, rank * B)      # H2D inside
+    # the same images as the reference's input file holds them: (img, neuron) triplets, value 1
+    img_np, neu_np = np.nonzero(y_host.numpy())
+    coo_img = torch.from_numpy(img_np.astype(np.int32)).pin_memory()
+    coo_neu = torch.from_numpy(neu_np.astype(np.int32)).pin_memory()
+
+    def step_e2e(kind="coo"):
+        if kind == "dense":
+            g.set_input_dense(y_host, rank * B)                                  # H2D of batch x N floats inside
+        else:
+            g.set_input_coo(coo_img.numpy(), coo_neu.numpy(), None, B, rank * B, index_base=0)   # H2D of the triplets inside
         g.infer_async()
         return g.categories()                    # D2H of the result (waits for the step)
 
@@ -276,21 +284,24 @@ def main_ours(args):
     survivors = r.survivors
     live = g.layer_live().copy()
     # -- e2e: host buffers in, category list out, copies inside the timed region
-    step_e2e()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(args.steps):
-        cats = step_e2e()
-    e1.record(stream)
-    barrier()
-    ms_e2e = e0.elapsed_time(e1)
+    def time_e2e(kind):
+        step_e2e(kind)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            c_ = step_e2e(kind)
+        e1.record(stream)
+        barrier()
+        return e0.elapsed_time(e1), c_
+    ms_e2e_dense, _ = time_e2e("dense")
+    ms_e2e, cats = time_e2e("coo")
     d2h = int(len(cats) * 4 + (L + 1) * 16 + 4)
     all_cats = gather_categories(np.asarray(cats).copy())
-    t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device="cuda")
+    t = torch.tensor([ms, ms_e2e, ms_e2e_dense], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, ms_e2e = float(t[0]), float(t[1])
+    ms, ms_e2e, ms_e2e_dense = float(t[0]), float(t[1]), float(t[2])
     edges_step = float(world) * B * n * 32.0 * L
     out = None
     if rank == 0:
@@ -308,8 +319,14 @@ def main_ours(args):
                        "survivors_rank0": int(survivors), "survivors_total": int(len(all_cats)),
                        "live_after_layer": {str(i): int(live[i]) for i in sorted({0, 1, 2, 4, 8, 16, 32, L - 1}) if i < L},
                        "classes_per_layer": info["classes"]},
-            "e2e": {"value": edges_step * args.steps / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": B * n * 4,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps},
+            "e2e": {"value": edges_step * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": int(coo_img.numel() * 8), "d2h_bytes_per_step": d2h,
+                    "ms_per_step": ms_e2e / args.steps,
+                    "call": "spdnn_set_input_coo (the input file's img/neuron triplets, pinned host memory) + spdnn_infer "
+                            "+ spdnn_get_categories",
+                    "dense_input": {"value": edges_step * args.steps / (ms_e2e_dense * 1e-3), "h2d_bytes_per_step": B * n * 4,
+                                    "ms_per_step": ms_e2e_dense / args.steps,
+                                    "call": "spdnn_set_input_dense (batch x N fp32, pinned host memory)"}},
             "gpu_launches": int(launches * args.steps),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind + " copy bandwidth (MEASURED_PEAKS.json hbm_gbs)", "traffic": None,
@@ -324,7 +341,8 @@ def main_ours(args):
         }
         tr = ncu_traffic(cfg, args.pattern)
         if tr is not None:
-            out["roofline"]["traffic"] = tr
+            # per launch, like `achieved`: the capture's per-layer figure times the layers of an average launch
+            out["roofline"]["traffic"] = tr * L / max(loop_launches, 1)
     g.close()
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cb = run_cpu_reference(cfg, args.pattern, args.cpu_seconds)
