@@ -254,7 +254,8 @@ struct ResidentTables {
     int v_in = 0;                   // value ids of the input: rows of the input buffer
     int mode = RES_GENERIC;
     int o_vals = 0;                 // word offset of the weights inside the blob (0: uniform)
-    // blob, all entries are (permuted) row numbers of the shared-memory buffers:
+    // blob: a 4-word header {classes, k, bits of w, 0}, then, all entries being (permuted) row
+    // numbers of the shared-memory buffers:
     //   RES_GENERIC: int32 t[U][k + 4]: the k input rows in summation order, then {output row, 0, 0, 0};
     //                followed, when the weights are not uniform, by float vals[U][k + 4]
     //   RES_ALT2:    int32 t[U][4] = {row a, row b, output row, 0}: the sum is a+b+a+b+... (k terms)
@@ -287,28 +288,32 @@ inline void build_resident_tables(const HostLayer &h, const int32_t *vid_in, int
             if (in_row(r[i]) != ((i & 1) ? b : a)) { alt2 = false; break; }
     }
     out.mode = alt2 ? RES_ALT2 : RES_GENERIC;
+    constexpr size_t H = 4;      // header words
     if (alt2) {
-        out.blob.assign((size_t)u * 4, 0);
+        out.blob.assign(H + (size_t)u * 4, 0);
         for (int cls = 0; cls < u; ++cls) {
             const int32_t *r = &h.rows[(size_t)first_col[cls] * k];
-            out.blob[(size_t)cls * 4 + 0] = in_row(r[0]);
-            out.blob[(size_t)cls * 4 + 1] = in_row(r[1]);
-            out.blob[(size_t)cls * 4 + 2] = phys_row(cls);
+            out.blob[H + (size_t)cls * 4 + 0] = in_row(r[0]);
+            out.blob[H + (size_t)cls * 4 + 1] = in_row(r[1]);
+            out.blob[H + (size_t)cls * 4 + 2] = phys_row(cls);
         }
     } else {
         const int kp = k + 4;
         const size_t words = (size_t)u * kp;
-        out.o_vals = h.uniform ? 0 : (int)words;
-        out.blob.assign(words * (h.uniform ? 1 : 2), 0);
+        out.o_vals = h.uniform ? 0 : (int)(H + words);
+        out.blob.assign(H + words * (h.uniform ? 1 : 2), 0);
         for (int cls = 0; cls < u; ++cls) {
             const int fc = first_col[cls];
             for (int i = 0; i < k; ++i) {
-                out.blob[(size_t)cls * kp + i] = in_row(h.rows[(size_t)fc * k + i]);
-                if (!h.uniform) std::memcpy(&out.blob[words + (size_t)cls * kp + i], &h.vals[(size_t)fc * k + i], 4);
+                out.blob[H + (size_t)cls * kp + i] = in_row(h.rows[(size_t)fc * k + i]);
+                if (!h.uniform) std::memcpy(&out.blob[H + words + (size_t)cls * kp + i], &h.vals[(size_t)fc * k + i], 4);
             }
-            out.blob[(size_t)cls * kp + k] = phys_row(cls);
+            out.blob[H + (size_t)cls * kp + k] = phys_row(cls);
         }
     }
+    out.blob[0] = u;
+    out.blob[1] = k;
+    std::memcpy(&out.blob[2], &h.w, 4);
     if (vid_in) {
         out.rep.assign(out.v_in, -1);
         for (int r = 0; r < n; ++r)

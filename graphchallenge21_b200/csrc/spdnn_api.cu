@@ -84,6 +84,7 @@ struct spdnn {
     int32_t *died_at = nullptr;        // [layers] images that died in each layer
     ResLayer *res_table = nullptr;     // [layers] tables of the resident kernel
     bool resident = true;              // use the shared-memory-resident kernel where a chunk fits
+    bool resident_always = false;      // ... even for a lone layer that the per-layer kernel would serve better
     int res_ti_max = 16;               // largest group of images per block to try
     int last_group = 0;                // group size of the last captured schedule's resident launches
     int smem_optin = 0;                // shared memory one block may opt in to
@@ -379,6 +380,10 @@ int enqueue_layers(spdnn *c) {
                 }
                 tb = (blob + 127) / 128 * 128;
                 if (!(c->stage_tables && fits(ti, rows, tb))) tb = 0;
+                // A lone layer that reads all N rows of every image but computes few classes from
+                // them (the first layer of a network with repeated columns) gains nothing from
+                // staging the rows in shared memory: gather straight from global memory instead.
+                if (f == 1 && R0.v_in == c->n && R0.classes * 2 <= c->n && !c->resident_always) f = 0;
             }
         }
         if (f > 0) {
@@ -504,7 +509,7 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
         int optin = 0;
         CK(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device));
         c->smem_optin = optin;
-        if (const char *e = getenv("SPDNN_RESIDENT")) c->resident = atoi(e) != 0;
+        if (const char *e = getenv("SPDNN_RESIDENT")) { c->resident = atoi(e) != 0; c->resident_always = atoi(e) > 1; }
         if (const char *e = getenv("SPDNN_RESIDENT_TI")) {
             const int ti = atoi(e);
             if (ti == 16 || ti == 8 || ti == 4) c->res_ti_max = ti;

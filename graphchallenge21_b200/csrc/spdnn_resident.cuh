@@ -43,7 +43,8 @@ constexpr int kResGeneric = 0, kResAlt2 = 1;
 
 // Per-layer tables of the resident kernel (one entry per layer, in device memory).
 struct ResLayer {
-    const int32_t *blob;      // GENERIC: int32 t[U][k+4] (k input rows, then the output row) [+ float vals[U][k+4]]
+    const int32_t *blob;      // header {classes, k, bits of w, 0}, then
+                              // GENERIC: int32 t[U][k+4] (k input rows, then the output row) [+ float vals[U][k+4]]
                               // ALT2:    int32 t[U][4] = {row a, row b, output row, 0}
     const int32_t *rep;       // [v_in] neuron*32 carrying value id v, or nullptr (value id == neuron)
     const int32_t *mem_ptr;   // [U+1] member ranges, or nullptr (class u == column u)
@@ -82,24 +83,49 @@ __host__ __device__ __forceinline__ int resident_phys_row(int r) {
     return r ^ (x & 1);
 }
 
-__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+// Two fp32 values in one 64-bit register pair, added by ONE instruction (add.rn.f32x2, sm_100):
+// each half is an ordinary IEEE round-to-nearest add, so results equal two scalar adds.
+typedef unsigned long long f32x2;
+
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+
+__device__ __forceinline__ void unpack2(f32x2 v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
 #ifndef SPDNN_NO_F32X2
-    unsigned long long ra, rb, rd;
-    float2 d;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
-    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    f32x2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 #else
-    return make_float2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y));
+    float al, ah, bl, bh;
+    unpack2(a, al, ah);
+    unpack2(b, bl, bh);
+    return pack2(__fadd_rn(al, bl), __fadd_rn(ah, bh));
 #endif
 }
 
-__device__ __forceinline__ void acc4(float4 &acc, const float4 v) {
-    const float2 lo = add2(make_float2(acc.x, acc.y), make_float2(v.x, v.y));
-    const float2 hi = add2(make_float2(acc.z, acc.w), make_float2(v.z, v.w));
-    acc = make_float4(lo.x, lo.y, hi.x, hi.y);
+// Four accumulators (one per image of the thread) as two packed pairs.
+struct Acc4 {
+    f32x2 lo, hi;
+};
+
+__device__ __forceinline__ Acc4 acc_zero() { return Acc4{pack2(0.0f, 0.0f), pack2(0.0f, 0.0f)}; }
+__device__ __forceinline__ Acc4 acc_from(const float4 v) { return Acc4{pack2(v.x, v.y), pack2(v.z, v.w)}; }
+__device__ __forceinline__ void acc_add(Acc4 &acc, const Acc4 &v) {
+    acc.lo = add2(acc.lo, v.lo);
+    acc.hi = add2(acc.hi, v.hi);
+}
+__device__ __forceinline__ float4 acc_get(const Acc4 &acc) {
+    float4 r;
+    unpack2(acc.lo, r.x, r.y);
+    unpack2(acc.hi, r.z, r.w);
+    return r;
 }
 
 __device__ __forceinline__ float4 mul4(const float4 v, float w) {
@@ -141,7 +167,7 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned int 
 template <int KT, bool UNIFORM, bool STAGED, int RS>
 __device__ __forceinline__ float4 class_sum_generic(const int32_t *rows, const float *vals, int k, float w,
                                                     const unsigned char *in) {
-    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    Acc4 acc = acc_zero();
     const int4 *o4 = reinterpret_cast<const int4 *>(rows);
     const float4 *w4 = reinterpret_cast<const float4 *>(vals);
     if (KT > 0) {
@@ -154,15 +180,15 @@ __device__ __forceinline__ float4 class_sum_generic(const int32_t *rows, const f
         }
         if (UNIFORM) {
 #pragma unroll
-            for (int i = 0; i < KT; ++i) acc4(acc, *reinterpret_cast<const float4 *>(in + o[i]));
+            for (int i = 0; i < KT; ++i) acc_add(acc, acc_from(*reinterpret_cast<const float4 *>(in + o[i])));
         } else {
 #pragma unroll
             for (int i = 0; i < KT / 4; ++i) {
                 const float4 t = STAGED ? w4[i] : __ldg(w4 + i);
-                acc4(acc, mul4(*reinterpret_cast<const float4 *>(in + o[4 * i + 0]), t.x));
-                acc4(acc, mul4(*reinterpret_cast<const float4 *>(in + o[4 * i + 1]), t.y));
-                acc4(acc, mul4(*reinterpret_cast<const float4 *>(in + o[4 * i + 2]), t.z));
-                acc4(acc, mul4(*reinterpret_cast<const float4 *>(in + o[4 * i + 3]), t.w));
+                acc_add(acc, acc_from(mul4(*reinterpret_cast<const float4 *>(in + o[4 * i + 0]), t.x)));
+                acc_add(acc, acc_from(mul4(*reinterpret_cast<const float4 *>(in + o[4 * i + 1]), t.y)));
+                acc_add(acc, acc_from(mul4(*reinterpret_cast<const float4 *>(in + o[4 * i + 2]), t.z)));
+                acc_add(acc, acc_from(mul4(*reinterpret_cast<const float4 *>(in + o[4 * i + 3]), t.w)));
             }
         }
     } else {
@@ -174,30 +200,35 @@ __device__ __forceinline__ float4 class_sum_generic(const int32_t *rows, const f
                 const float4 q = STAGED ? w4[i] : __ldg(w4 + i);
                 a = mul4(a, q.x); b = mul4(b, q.y); c = mul4(c, q.z); e = mul4(e, q.w);
             }
-            acc4(acc, a); acc4(acc, b); acc4(acc, c); acc4(acc, e);
+            acc_add(acc, acc_from(a)); acc_add(acc, acc_from(b)); acc_add(acc, acc_from(c)); acc_add(acc, acc_from(e));
         }
     }
-    return UNIFORM ? mul4(acc, w) : acc;
+    const float4 r = acc_get(acc);
+    return UNIFORM ? mul4(r, w) : r;
 }
 
 // ALT2: the K terms are a, b, a, b, ...
 template <int KT>
 __device__ __forceinline__ float4 class_sum_alt2(const float4 a, const float4 b, int k, float w) {
-    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    Acc4 acc = acc_zero();
+    const Acc4 pa = acc_from(a), pb = acc_from(b);
     if (KT > 0) {
 #pragma unroll
-        for (int i = 0; i < KT / 2; ++i) { acc4(acc, a); acc4(acc, b); }
+        for (int i = 0; i < KT / 2; ++i) { acc_add(acc, pa); acc_add(acc, pb); }
     } else {
-        for (int i = 0; i < k / 2; ++i) { acc4(acc, a); acc4(acc, b); }
+        for (int i = 0; i < k / 2; ++i) { acc_add(acc, pa); acc_add(acc, pb); }
     }
-    return mul4(acc, w);
+    return mul4(acc_get(acc), w);
 }
 
 // Grid: one block per TI live images (launched for the worst case; surplus blocks only take
 // part in the last-block ticket).  Dynamic shared memory: two activation buffers of
 // buf_rows * TI * 4 bytes, then (STAGED) two table buffers of table_bytes each.
+#ifndef SPDNN_ALT2_MIN_BLOCKS
+#define SPDNN_ALT2_MIN_BLOCKS 8      // <= 32 registers: a full set of 64 warps per SM for the light ALT2 form
+#endif
 template <int TI, int MODE, int KT, bool UNIFORM, bool STAGED>
-__global__ void __launch_bounds__(kThreads) resident_kernel(const ResArgs a) {
+__global__ void __launch_bounds__(kThreads, (MODE == kResAlt2 ? SPDNN_ALT2_MIN_BLOCKS : 1)) resident_kernel(const ResArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ unsigned int s_alive[3];
     __shared__ int s_last, s_fail;
@@ -267,42 +298,61 @@ __global__ void __launch_bounds__(kThreads) resident_kernel(const ResArgs a) {
         __syncthreads();
 
         // ---- the layers of this chunk
+        // thread 0 keeps the address of the table after next in registers, so that the copy
+        // it issues at the top of a layer does not wait for a load from global memory
+        const int32_t *nb_ptr = nullptr;
+        unsigned int nb_bytes = 0;
+        if (STAGED && tid == 0 && a.nlayers > 1) {
+            nb_ptr = a.layers[1].blob;
+            nb_bytes = (unsigned int)a.layers[1].blob_bytes;
+        }
         int li = 0;
+        int last_classes = 0;
         for (; li < a.nlayers; ++li) {
-            const ResLayer L = a.layers[li];
-            if (tid == 0) {
-                s_alive[(li + 1) % 3] = 0u;
-                // the other table buffer was last read in layer li - 1, which every thread has left
-                if (STAGED && li + 1 < a.nlayers) {
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    bulk_load_table(tbl0 + ((li + 1) & 1) * a.table_bytes, a.layers[li + 1].blob, (unsigned int)a.layers[li + 1].blob_bytes,
-                                    &s_bar[(li + 1) & 1]);
-                }
-            }
-            const int32_t *T = L.blob;
+            const int32_t *T;
             bool ready = true;
             if (STAGED) {
+                if (tid == 0) {
+                    s_alive[(li + 1) % 3] = 0u;
+                    // the other table buffer was last read in layer li - 1, which every thread has left
+                    if (li + 1 < a.nlayers) {
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        bulk_load_table(tbl0 + ((li + 1) & 1) * a.table_bytes, nb_ptr, nb_bytes, &s_bar[(li + 1) & 1]);
+                        if (li + 2 < a.nlayers) {
+                            nb_ptr = a.layers[li + 2].blob;
+                            nb_bytes = (unsigned int)a.layers[li + 2].blob_bytes;
+                        }
+                    }
+                }
                 ready = mbar_wait(&s_bar[li & 1], (unsigned int)((li >> 1) & 1));
                 if (!ready) s_fail = 1;
                 T = reinterpret_cast<const int32_t *>(tbl0 + (li & 1) * a.table_bytes);
+            } else {
+                if (tid == 0) s_alive[(li + 1) % 3] = 0u;
+                T = a.layers[li].blob;
             }
+            // per-layer scalars travel in the table's header
+            const int4 hdr = (STAGED && ready) ? *reinterpret_cast<const int4 *>(T)
+                                               : (STAGED ? make_int4(0, 4, 0, 0) : __ldg(reinterpret_cast<const int4 *>(T)));
+            const int classes = hdr.x, lk = hdr.y;
+            const float lw = __int_as_float(hdr.z);
+            last_classes = classes;
             unsigned int bits = 0;
             const unsigned char *in = cur + sub * 16;
-            for (int u = grp; ready && u < L.classes; u += CPI) {
+            for (int u = grp; u < classes; u += CPI) {
                 float4 s;
                 int out_row;
                 if (MODE == kResAlt2) {
-                    const int4 e = STAGED ? reinterpret_cast<const int4 *>(T)[u] : __ldg(reinterpret_cast<const int4 *>(T) + u);
+                    const int4 e = STAGED ? reinterpret_cast<const int4 *>(T)[1 + u] : __ldg(reinterpret_cast<const int4 *>(T) + 1 + u);
                     const float4 va = *reinterpret_cast<const float4 *>(in + e.x * RS);
                     const float4 vb = *reinterpret_cast<const float4 *>(in + e.y * RS);
-                    s = class_sum_alt2<KT>(va, vb, L.k, L.w);
+                    s = class_sum_alt2<KT>(va, vb, lk, lw);
                     out_row = e.z;
                 } else {
-                    const int kp = L.k + 4;
-                    const int32_t *rows = T + (size_t)u * kp;
-                    s = class_sum_generic<KT, UNIFORM, STAGED, RS>(rows, reinterpret_cast<const float *>(T + L.o_vals) + (size_t)u * kp,
-                                                                   L.k, L.w, in);
-                    out_row = STAGED ? rows[L.k] : __ldg(rows + L.k);
+                    const int kp = lk + 4;
+                    const int32_t *rows = T + 4 + (size_t)u * kp;
+                    s = class_sum_generic<KT, UNIFORM, STAGED, RS>(rows, reinterpret_cast<const float *>(rows) + (size_t)classes * kp, lk, lw, in);
+                    out_row = STAGED ? rows[lk] : __ldg(rows + lk);
                 }
                 float4 y;
                 y.x = relu_clip(__fadd_rn(s.x, a.bias), a.clip);
@@ -319,8 +369,8 @@ __global__ void __launch_bounds__(kThreads) resident_kernel(const ResArgs a) {
             }
             {
                 // zero rows of the buffer just written (the next layer's padded entries point there)
-                const int ue = (L.classes + 1) & ~1;
-                for (int r = L.classes + grp; r < ue + 2; r += CPI)
+                const int ue = (classes + 1) & ~1;
+                for (int r = classes + grp; r < ue + 2; r += CPI)
                     *reinterpret_cast<float4 *>(nxt + (r < ue ? resident_phys_row(r) : r) * RS + sub * 16) = make_float4(0, 0, 0, 0);
             }
             const unsigned int wm = __reduce_or_sync(0xffffffffu, bits << (sub * 4));
@@ -352,7 +402,7 @@ __global__ void __launch_bounds__(kThreads) resident_kernel(const ResArgs a) {
             const ResLayer LL = a.layers[li - 1];
             const int tile = j0 >> 5, lane0 = j0 & 31;
             float *out = a.yout + (size_t)tile * a.tile_stride + lane0 + sub * 4;
-            for (int u = grp; u < LL.classes; u += CPI) {
+            for (int u = grp; u < last_classes; u += CPI) {
                 const float4 y = *reinterpret_cast<const float4 *>(cur + resident_phys_row(u) * RS + sub * 16);
                 if (LL.mem_ptr == nullptr) {
                     *reinterpret_cast<float4 *>(out + (size_t)u * 32) = y;

@@ -60,7 +60,9 @@ def test_golden_vectors(path, how):
 
 
 @pytest.mark.parametrize("pattern,n,L,b", [("radix16", 1024, 120, 6000), ("radix16", 4096, 30, 777),
-                                           ("random", 1024, 12, 1500), ("radix16", 16384, 12, 100)])
+                                           ("random", 1024, 12, 1500), ("radix16", 16384, 12, 100),
+                                           ("radix16", 4096, 60, 2000), ("radix16", 16384, 24, 300),
+                                           ("radix16", 65536, 14, 64), ("random", 4096, 8, 300)])
 def test_against_oracle(pattern, n, L, b, oracle):
     net = SyntheticNetwork(n, L, pattern)
     y0 = synthetic_images(n, b) if pattern == "radix16" else mixed_density_images(n, b)
