@@ -47,6 +47,8 @@ def parse():
     p.add_argument("--neurons", type=int)
     p.add_argument("--layers", type=int)
     p.add_argument("--batch", type=int, help="images per GPU")
+    p.add_argument("--inputs", default="blobs", choices=["blobs", "mixed"],
+                   help="blobs: ~15%% dense discs on the pixel grid; mixed: unstructured, density 5-60%% per image")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--cpu-seconds", type=float, default=12.0, help="target CPU time of the cpu_baseline sample")
     return p.parse_args()
@@ -232,7 +234,12 @@ def main_ours(args):
     for l in range(L):
         g.set_layer_csc(l, *net.layer_csc(l))
     info = g.layer_info(min(1, L - 1))
-    y_host = torch.from_numpy(synthetic_images(n, B, first_image=rank * B)).pin_memory()
+    if args.inputs == "mixed":
+        from graphchallenge21_b200.generator import mixed_density_images
+        y_np = mixed_density_images(n, B, first_image=rank * B)
+    else:
+        y_np = synthetic_images(n, B, first_image=rank * B)
+    y_host = torch.from_numpy(y_np).pin_memory()
     y_dev = y_host.cuda()
     stream = torch.cuda.current_stream()
     g.set_stream(stream.cuda_stream)
@@ -313,7 +320,7 @@ def main_ours(args):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"N={n} L={L} batch={B} per GPU, pattern {args.pattern}", "neurons": n, "layers": L,
-                       "batch_per_gpu": B, "pattern": args.pattern, "bias": float(net.bias),
+                       "batch_per_gpu": B, "pattern": args.pattern, "inputs": args.inputs, "bias": float(net.bias),
                        "parallelism": f"batch-sharded x{world}, weights replicated",
                        "l2": "inputs larger than L2 (%.0f MB per step), no flush" % (B * n * 4 / 1e6),
                        "survivors_rank0": int(survivors), "survivors_total": int(len(all_cats)),

@@ -84,6 +84,7 @@ struct spdnn {
     int32_t *died_at = nullptr;        // [layers] images that died in each layer
     ResLayer *res_table = nullptr;     // [layers] tables of the resident kernel
     bool resident = true;              // use the shared-memory-resident kernel where a chunk fits
+    bool print_schedule = false;       // SPDNN_PRINT_SCHEDULE=1: one line per launch when the graph is built
     bool resident_always = false;      // ... even for a lone layer that the per-layer kernel would serve better
     int res_ti_max = 16;               // largest group of images per block to try
     int last_group = 0;                // group size of the last captured schedule's resident launches
@@ -401,6 +402,10 @@ int enqueue_layers(spdnn *c) {
             int rc = launch_resident(c, ti, a, grid, smem, R0.mode, R0.k == 32, R0.uniform);
             if (rc) return rc;
             c->last_group = ti;
+            if (c->print_schedule)
+                fprintf(stderr, "[spdnn] step %d: resident layers %d..%d  group %d images  %s  rows %d (v_in %d, classes %d)  smem %zu B  tables %s\n",
+                        step, l, l + f - 1, ti, R0.mode == kResAlt2 ? "ALT2" : "GENERIC", rows, R0.v_in, R0.classes, smem,
+                        tb ? "staged" : "global");
             l += f;
             chunk = std::min(chunk * 2, c->chunk_max);
         } else {
@@ -429,6 +434,8 @@ int enqueue_layers(spdnn *c) {
             int grid = c->grid_override > 0 ? c->grid_override : c->sm_count * blocks_per_sm(L.k, L.uniform);
             int rc = launch_layer(c, d, a, grid, L.uniform);
             if (rc) return rc;
+            if (c->print_schedule)
+                fprintf(stderr, "[spdnn] step %d: per-layer kernel, layer %d  classes %d  k %d  grid %d\n", step, l, L.classes, L.k, grid);
             l += 1;
         }
         ++step;
@@ -515,6 +522,7 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
             if (ti == 16 || ti == 8 || ti == 4) c->res_ti_max = ti;
         }
         if (const char *e = getenv("SPDNN_STAGE_TABLES")) c->stage_tables = atoi(e) != 0;
+        if (const char *e = getenv("SPDNN_PRINT_SCHEDULE")) c->print_schedule = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_CHUNK_FIRST")) c->chunk_first = std::max(1, atoi(e));
         if (const char *e = getenv("SPDNN_CHUNK_MAX")) c->chunk_max = std::max(1, atoi(e));
         if (const char *e = getenv("SPDNN_HOST_BUDGET_MB")) c->host_budget = (size_t)atoll(e) << 20;

@@ -218,6 +218,18 @@ def synthetic_images(neurons: int, batch: int, seed: int = 0x1A6E5, first_image:
     return out
 
 
+def mixed_density_images(neurons: int, batch: int, seed: int = 0xABCD, lo: float = 0.05, hi: float = 0.6,
+                         first_image: int = 0) -> np.ndarray:
+    """Binary float32 [batch, N] inputs without spatial structure whose per-image density is
+    spread uniformly over [lo, hi].  On networks without locality (pattern 'random') a
+    15 %-dense image dies within three layers; the dense end of this mix survives, which makes
+    it the input of the generality tests and of the 'random' benchmark runs."""
+    ids = np.arange(first_image, first_image + batch, dtype=np.uint64)
+    idx = ids[:, None] * np.uint64(neurons) + np.arange(neurons, dtype=np.uint64)[None, :]
+    dens = lo + (hi - lo) * rand_unit(seed, 3, ids)
+    return (rand_unit(seed, 4, idx) < dens[:, None]).astype(np.float32)
+
+
 def dense_to_coo_1based(dense: np.ndarray, first_image: int = 0):
     """The triplets of the reference's input file, ``img neuron val`` 1-based
     (src/network.cpp:33-54)."""

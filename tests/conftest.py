@@ -27,7 +27,5 @@ def oracle():
 def mixed_density_images(neurons, batch, seed=0xABCD, lo=0.05, hi=0.6):
     """Binary inputs whose per-image density is spread over [lo, hi]: keeps a share of the
     images alive on networks without locality (pattern 'random')."""
-    from graphchallenge21_b200.generator import rand_unit
-    idx = np.arange(batch * neurons, dtype=np.uint64).reshape(batch, neurons)
-    dens = lo + (hi - lo) * rand_unit(seed, 3, np.arange(batch, dtype=np.uint64))
-    return (rand_unit(seed, 4, idx) < dens[:, None]).astype(np.float32)
+    from graphchallenge21_b200.generator import mixed_density_images as gen
+    return gen(neurons, batch, seed, lo, hi)
