@@ -84,6 +84,7 @@ struct spdnn {
     int32_t *died_at = nullptr;        // [layers] images that died in each layer
     ResLayer *res_table = nullptr;     // [layers] tables of the resident kernel
     bool resident = true;              // use the shared-memory-resident kernel where a chunk fits
+    bool exact_shortcut = true;        // SPDNN_EXACT_SHORTCUT=0 disables the exact-sum shortcut of the ALT2 form
     bool print_schedule = false;       // SPDNN_PRINT_SCHEDULE=1: one line per launch when the graph is built
     bool resident_always = false;      // ... even for a lone layer that the per-layer kernel would serve better
     int res_ti_max = 16;               // largest group of images per block to try
@@ -397,6 +398,7 @@ int enqueue_layers(spdnn *c) {
             a.layers = c->res_table + l; a.died_at = c->died_at + l; a.nlayers = f;
             a.buf_rows = rows; a.table_bytes = tb;
             a.n = c->n; a.bias = c->bias; a.clip = c->clip;
+            a.exact_ok = (l > 0 && c->clip <= 1024.0f && c->exact_shortcut) ? 1 : 0;
             const int grid = std::max(1, (c->tiles_cap * 32 + ti - 1) / ti);
             const size_t smem = 2 * (size_t)rows * ti * 4 + 2 * (size_t)tb;
             int rc = launch_resident(c, ti, a, grid, smem, R0.mode, R0.k == 32, R0.uniform);
@@ -523,6 +525,7 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
         }
         if (const char *e = getenv("SPDNN_STAGE_TABLES")) c->stage_tables = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_PRINT_SCHEDULE")) c->print_schedule = atoi(e) != 0;
+        if (const char *e = getenv("SPDNN_EXACT_SHORTCUT")) c->exact_shortcut = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_CHUNK_FIRST")) c->chunk_first = std::max(1, atoi(e));
         if (const char *e = getenv("SPDNN_CHUNK_MAX")) c->chunk_max = std::max(1, atoi(e));
         if (const char *e = getenv("SPDNN_HOST_BUDGET_MB")) c->host_budget = (size_t)atoll(e) << 20;

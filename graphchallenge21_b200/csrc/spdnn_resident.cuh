@@ -73,6 +73,7 @@ struct ResArgs {
     int buf_rows;             // rows of one activation buffer (largest layer of the chunk, even, + 2)
     int table_bytes;          // shared memory reserved per staged table (0 = read the tables from global memory)
     int n;                    // neurons
+    int exact_ok;             // the inputs of every layer of the chunk are activations in [0, clip], clip <= 1024
     float bias, clip;
 };
 
@@ -208,10 +209,27 @@ __device__ __forceinline__ float4 class_sum_generic(const int32_t *rows, const f
 }
 
 // ALT2: the K terms are a, b, a, b, ...
+//
+// Shortcut (exact_ok: K == 32, inputs are activations of an earlier layer, clip <= 1024): when
+// all of a and b are multiples of 1/16 -- which (x + M) - M == x tests for M = 1.5 * 2^19,
+// whose ulp is 2^-4 -- every partial sum of a+b+a+b+... is a multiple of 1/16 below 2^15 and so
+// exactly representable in fp32: each of the 32 adds is exact and the sequential sum EQUALS
+// 16 (a + b), which is computed directly.  Saturated networks (activations 0 or 32, the steady
+// state of the challenge networks) take this path in every layer; the result bits are the same.
 template <int KT>
-__device__ __forceinline__ float4 class_sum_alt2(const float4 a, const float4 b, int k, float w) {
-    Acc4 acc = acc_zero();
+__device__ __forceinline__ float4 class_sum_alt2(const float4 a, const float4 b, int k, float w, bool exact_ok) {
     const Acc4 pa = acc_from(a), pb = acc_from(b);
+    if (KT == 32 && exact_ok) {
+        const f32x2 M = pack2(786432.0f, 786432.0f), NM = pack2(-786432.0f, -786432.0f);
+        const f32x2 d = (add2(add2(pa.lo, M), NM) ^ pa.lo) | (add2(add2(pa.hi, M), NM) ^ pa.hi) |
+                        (add2(add2(pb.lo, M), NM) ^ pb.lo) | (add2(add2(pb.hi, M), NM) ^ pb.hi);
+        if (d == 0ull) {
+            Acc4 s = pa;
+            acc_add(s, pb);
+            return mul4(acc_get(s), 16.0f * w);
+        }
+    }
+    Acc4 acc = acc_zero();
     if (KT > 0) {
 #pragma unroll
         for (int i = 0; i < KT / 2; ++i) { acc_add(acc, pa); acc_add(acc, pb); }
@@ -308,6 +326,7 @@ __global__ void __launch_bounds__(kThreads, (MODE == kResAlt2 ? SPDNN_ALT2_MIN_B
         }
         int li = 0;
         int last_classes = 0;
+        const bool force_dead = a.bias > 0.0f;
         for (; li < a.nlayers; ++li) {
             const int32_t *T;
             bool ready = true;
@@ -346,7 +365,7 @@ __global__ void __launch_bounds__(kThreads, (MODE == kResAlt2 ? SPDNN_ALT2_MIN_B
                     const int4 e = STAGED ? reinterpret_cast<const int4 *>(T)[1 + u] : __ldg(reinterpret_cast<const int4 *>(T) + 1 + u);
                     const float4 va = *reinterpret_cast<const float4 *>(in + e.x * RS);
                     const float4 vb = *reinterpret_cast<const float4 *>(in + e.y * RS);
-                    s = class_sum_alt2<KT>(va, vb, lk, lw);
+                    s = class_sum_alt2<KT>(va, vb, lk, lw, a.exact_ok != 0);
                     out_row = e.z;
                 } else {
                     const int kp = lk + 4;
@@ -354,20 +373,25 @@ __global__ void __launch_bounds__(kThreads, (MODE == kResAlt2 ? SPDNN_ALT2_MIN_B
                     s = class_sum_generic<KT, UNIFORM, STAGED, RS>(rows, reinterpret_cast<const float *>(rows) + (size_t)classes * kp, lk, lw, in);
                     out_row = STAGED ? rows[lk] : __ldg(rows + lk);
                 }
+                // x<0 ? 0 : x>clip ? clip : x (all_network.cu:8-10); for the finite x that occur this is
+                // min(max(x, 0), clip), two instructions instead of two compares and two selects
                 float4 y;
-                y.x = relu_clip(__fadd_rn(s.x, a.bias), a.clip);
-                y.y = relu_clip(__fadd_rn(s.y, a.bias), a.clip);
-                y.z = relu_clip(__fadd_rn(s.z, a.bias), a.clip);
-                y.w = relu_clip(__fadd_rn(s.w, a.bias), a.clip);
-                const unsigned int al = alive_prev >> (sub * 4);      // dead images stay dead
-                if (!(al & 1u)) y.x = 0.0f;
-                if (!(al & 2u)) y.y = 0.0f;
-                if (!(al & 4u)) y.z = 0.0f;
-                if (!(al & 8u)) y.w = 0.0f;
+                y.x = fminf(fmaxf(__fadd_rn(s.x, a.bias), 0.0f), a.clip);
+                y.y = fminf(fmaxf(__fadd_rn(s.y, a.bias), 0.0f), a.clip);
+                y.z = fminf(fmaxf(__fadd_rn(s.z, a.bias), 0.0f), a.clip);
+                y.w = fminf(fmaxf(__fadd_rn(s.w, a.bias), 0.0f), a.clip);
+                // dead images stay dead: with bias <= 0 an all-zero image stays all-zero by itself
+                if (force_dead) {
+                    const unsigned int al = alive_prev >> (sub * 4);
+                    if (!(al & 1u)) y.x = 0.0f;
+                    if (!(al & 2u)) y.y = 0.0f;
+                    if (!(al & 4u)) y.z = 0.0f;
+                    if (!(al & 8u)) y.w = 0.0f;
+                }
                 bits |= (y.x != 0.0f ? 1u : 0u) | (y.y != 0.0f ? 2u : 0u) | (y.z != 0.0f ? 4u : 0u) | (y.w != 0.0f ? 8u : 0u);
                 *reinterpret_cast<float4 *>(nxt + out_row * RS + sub * 16) = y;
             }
-            {
+            if (MODE == kResGeneric) {
                 // zero rows of the buffer just written (the next layer's padded entries point there)
                 const int ue = (classes + 1) & ~1;
                 for (int r = classes + grp; r < ue + 2; r += CPI)
