@@ -243,7 +243,7 @@ int launch_resident_t(spdnn *c, const ResArgs &a, int grid, size_t smem) {
                                 c->smem_optin - 1024));     // the kernel also has a little static shared memory
         configured[c->device & 63] = true;
     }
-    resident_kernel<TI, MODE, KT, UNIFORM, STAGED><<<grid, kThreads, smem, c->stream>>>(a);
+    resident_kernel<TI, MODE, KT, UNIFORM, STAGED><<<grid, ResThreads<MODE>::value, smem, c->stream>>>(a);
     CK(cudaGetLastError());
     return SPDNN_OK;
 }
@@ -867,6 +867,29 @@ int spdnn_inspect_layer_csc(int neurons, const int32_t *col_ptr, const int32_t *
     if (classes) *classes = p.classes;
     if (k) *k = h.k;
     if (uniform) *uniform = h.uniform ? 1 : 0;
+    return SPDNN_OK;
+}
+
+int spdnn_inspect_network_csc(int neurons, int layers, const int32_t *const *col_ptr, const int32_t *const *row_idx,
+                              const float *const *val, int32_t *classes, int32_t *v_in, int32_t *form) {
+    if (layers < 0 || !col_ptr || !row_idx) return SPDNN_ERR_ARG;
+    try {
+        std::vector<int32_t> vid;          // value ids of the current layer's input (empty: the neurons themselves)
+        int vin = neurons;
+        for (int l = 0; l < layers; ++l) {
+            HostLayer h;
+            if (!canonicalize_layer(neurons, col_ptr[l], row_idx[l], val ? val[l] : nullptr, h).empty()) return SPDNN_ERR_ARG;
+            ResidentTables t;
+            build_resident_tables(h, vid.empty() ? nullptr : vid.data(), vin, t);
+            if (classes) classes[l] = t.classes;
+            if (v_in) v_in[l] = t.v_in;
+            if (form) form[l] = t.mode;
+            if (t.classes < neurons) { vid.swap(t.class_of); vin = t.classes; }
+            else { vid.clear(); vin = neurons; }
+        }
+    } catch (const std::bad_alloc &) {
+        return SPDNN_ERR_MEMORY;
+    }
     return SPDNN_OK;
 }
 

@@ -125,11 +125,12 @@ __device__ __forceinline__ float class_sum(const LayerDesc &d, int u, const floa
 
 // The last block to finish turns the per-tile ballots into the next layer's work list.
 __device__ __forceinline__ void rebuild_worklist(const LayerArgs &a, int live_in, int ids_buf) {
-    __shared__ int s_warp[kWarps];
+    __shared__ int s_warp[32];          // works for any block size up to 1024 threads
     __shared__ int s_total;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int ntiles = (live_in + 31) >> 5;
-    const int per = (ntiles + kThreads - 1) / kThreads;
+    const int nthreads = blockDim.x, nwarps = nthreads >> 5;
+    const int per = (ntiles + nthreads - 1) / nthreads;
     const int t0 = min(tid * per, ntiles), t1 = min(t0 + per, ntiles);
     int cnt = 0;
     for (int t = t0; t < t1; ++t) cnt += __popc(__ldcg(a.mask + t));
@@ -143,14 +144,14 @@ __device__ __forceinline__ void rebuild_worklist(const LayerArgs &a, int live_in
     if (lane == 31) s_warp[warp] = inc;
     __syncthreads();
     if (warp == 0) {
-        int w = lane < kWarps ? s_warp[lane] : 0;
+        int w = lane < nwarps ? s_warp[lane] : 0;
 #pragma unroll
-        for (int d = 1; d < kWarps; d <<= 1) {
+        for (int d = 1; d < 32; d <<= 1) {
             const int o = __shfl_up_sync(0xffffffffu, w, d);
             if (lane >= d) w += o;
         }
-        if (lane < kWarps) s_warp[lane] = w;          // inclusive over warps
-        if (lane == kWarps - 1) s_total = w;
+        if (lane < nwarps) s_warp[lane] = w;          // inclusive over warps
+        if (lane == nwarps - 1) s_total = w;
     }
     __syncthreads();
     int base = inc - cnt + (warp ? s_warp[warp - 1] : 0);

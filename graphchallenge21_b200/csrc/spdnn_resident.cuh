@@ -245,14 +245,25 @@ __device__ __forceinline__ float4 class_sum_alt2(const float4 a, const float4 b,
 #ifndef SPDNN_ALT2_MIN_BLOCKS
 #define SPDNN_ALT2_MIN_BLOCKS 8      // <= 32 registers: a full set of 64 warps per SM for the light ALT2 form
 #endif
+// Threads per block: the GENERIC form is bound by shared-memory latency with one block per SM
+// (its buffers fill the shared memory), so it runs 16 warps; the light ALT2 form runs many
+// small blocks per SM.
+#ifndef SPDNN_GENERIC_THREADS
+#define SPDNN_GENERIC_THREADS 512
+#endif
+template <int MODE>
+struct ResThreads {
+    static constexpr int value = (MODE == kResAlt2) ? kThreads : SPDNN_GENERIC_THREADS;
+};
 template <int TI, int MODE, int KT, bool UNIFORM, bool STAGED>
-__global__ void __launch_bounds__(kThreads, (MODE == kResAlt2 ? SPDNN_ALT2_MIN_BLOCKS : 1)) resident_kernel(const ResArgs a) {
+__global__ void __launch_bounds__(ResThreads<MODE>::value, (MODE == kResAlt2 ? SPDNN_ALT2_MIN_BLOCKS : 1)) resident_kernel(const ResArgs a) {
+    constexpr int NT = ResThreads<MODE>::value;
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ unsigned int s_alive[3];
     __shared__ int s_last, s_fail;
     __shared__ __align__(8) unsigned long long s_bar[2];
     constexpr int LPC = TI / 4;                  // threads per class
-    constexpr int CPI = kThreads / LPC;          // classes per pass of the block
+    constexpr int CPI = NT / LPC;                // classes per pass of the block
     constexpr int RS = TI * 4;                   // bytes per row
     const int tid = threadIdx.x, lane = tid & 31;
     const int sub = tid % LPC, grp = tid / LPC;

@@ -207,6 +207,26 @@ class SpDNN:
         return y
 
 
+def inspect_network(neurons: int, layer_csc) -> dict:
+    """Host-only analysis of a network (no GPU): per layer the classes in value ids, the value
+    ids read and the resident kernel's table form (0 = K gathers, 1 = alternating pair).
+    ``layer_csc``: sequence of (col_ptr, row_idx, val_or_None)."""
+    lib = _lib.load()
+    keep, cps, ris, vs = [], [], [], []
+    for cp, ri, v in layer_csc:
+        cp = np.ascontiguousarray(cp, dtype=np.int32); ri = np.ascontiguousarray(ri, dtype=np.int32)
+        v = None if v is None else np.ascontiguousarray(v, dtype=np.float32)
+        keep.append((cp, ri, v))
+        cps.append(cp.ctypes.data); ris.append(ri.ctypes.data); vs.append(None if v is None else v.ctypes.data)
+    n = len(keep)
+    arr = lambda xs: (C.c_void_p * max(n, 1))(*xs)
+    classes, v_in, form = (np.zeros(max(n, 1), dtype=np.int32) for _ in range(3))
+    rc = lib.spdnn_inspect_network_csc(neurons, n, arr(cps), arr(ris), arr(vs), _ptr(classes), _ptr(v_in), _ptr(form))
+    if rc != 0:
+        raise SpDNNError(rc, "malformed layer")
+    return {"classes": classes[:n], "v_in": v_in[:n], "form": form[:n]}
+
+
 # ---- the reference's drivers ---------------------------------------------------------------
 
 def load_network_from_files(net: SpDNN, data_dir: str, log=None):

@@ -132,6 +132,16 @@ int spdnn_get_layer_info(spdnn_t *ctx, int layer, int *classes, int *k, int *uni
 int spdnn_inspect_layer_csc(int neurons, const int32_t *col_ptr, const int32_t *row_idx, const float *val,
                             int *classes, int *k, int *uniform);
 
+/* The analysis of a whole network, on the host, without a context or a GPU: for every layer the
+ * number of classes when it is expressed in the value ids of the layer before it, the number of
+ * value ids it reads (v_in[l] == classes[l-1], or `neurons` where the layer before has no
+ * repeated columns) and the table form the resident kernel would use (0 = K gathers per class,
+ * 1 = alternating pair).  Layer l is given as CSC through col_ptr[l], row_idx[l], val[l]
+ * (val or val[l] may be NULL: all weights 0.0625).  Output arrays hold `layers` entries and
+ * may be NULL. */
+int spdnn_inspect_network_csc(int neurons, int layers, const int32_t *const *col_ptr, const int32_t *const *row_idx,
+                              const float *const *val, int32_t *classes, int32_t *v_in, int32_t *form);
+
 /* One layer, for callers that cannot allocate device memory when they run it (a plugin inside
  * another runtime's memory pool, a callback where cudaMalloc's implicit synchronisation is
  * forbidden, a process whose footprint is frozen after start-up).  This entry point has no

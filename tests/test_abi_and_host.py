@@ -53,6 +53,25 @@ def test_inspect_layer_without_gpu():
     assert lib.spdnn_inspect_layer_csc(1024, cp.ctypes.data, bad.ctypes.data, None, None, None, None) == -1
 
 
+def test_network_analysis_in_value_ids():
+    """Host logic of the resident kernel's tables: value ids chain from layer to layer."""
+    n, L = 1024, 9
+    net = SyntheticNetwork(n, L, "radix16")
+    r = network.inspect_network(n, [net.layer_csc(l) for l in range(L)])
+    assert r["classes"][:5].tolist() == [64] * 5 and r["classes"].max() == 64
+    assert r["classes"][5] == 32                                 # stride N/2: columns g and g + 32 read the same rows
+    assert r["v_in"].tolist() == [n] + r["classes"][:-1].tolist()   # layer 0 reads neurons, the rest value ids
+    assert r["form"].tolist() == [0] + [1] * (L - 1)             # 16-wide butterfly blocks alternate two ids
+    net = SyntheticNetwork(n, 3, "random")
+    r = network.inspect_network(n, [net.layer_csc(l) for l in range(3)])
+    assert r["classes"].tolist() == [n] * 3 and r["v_in"].tolist() == [n] * 3 and r["form"].tolist() == [0] * 3
+    # a layer after one with repeated columns merges columns that differ only in equivalent rows
+    cp, ri, v = SyntheticNetwork(n, 2, "radix16").layer_csc(0)
+    rnd = SyntheticNetwork(n, 2, "random").layer_csc(1)
+    r = network.inspect_network(n, [(cp, ri, v), rnd])
+    assert r["classes"][0] == 64 and r["v_in"][1] == 64 and r["form"][1] == 0 and r["classes"][1] <= n
+
+
 def test_generator_is_deterministic_and_well_formed():
     for pattern in ("radix16", "random"):
         a = SyntheticNetwork(1024, 8, pattern).layer_rows(3)
