@@ -101,6 +101,27 @@ def test_positive_bias_all_zero_inputs_stay_alive(oracle):
     assert len(want[0]) == b
 
 
+def test_alternating_pairs_with_k16(oracle):
+    """The alternating-pair table form with K != 32 (runtime-K code path) and weight 1/8."""
+    from conftest import paired_group_network
+    n, L, b = 256, 6, 300
+    rows = paired_group_network(n, L)
+    vals = [np.full((n, 16), 0.125, np.float32) for _ in range(L)]
+
+    class Net:
+        neurons, layers, bias = n, L, np.float32(-0.4)
+        def layer_rows(self, l): return rows[l]
+    from graphchallenge21_b200 import network
+    csc = [((np.arange(n + 1) * 16).astype(np.int32), r.reshape(-1), v.reshape(-1)) for r, v in zip(rows, vals)]
+    info = network.inspect_network(n, csc)
+    assert info["form"].tolist() == [0] + [1] * (L - 1) and info["classes"].max() <= n // 8
+    y0 = mixed_density_images(n, b)
+    want = oracle.infer(y0, list(zip(rows, vals)), -0.4, value=0.125)
+    got = run_gpu(Net(), y0, vals=vals)
+    check(got, want)
+    assert 0 < len(want[0]) < b
+
+
 def test_general_weights_and_ragged_columns(oracle):
     n, b, L = 512, 200, 6
     rng = np.random.default_rng(11)
