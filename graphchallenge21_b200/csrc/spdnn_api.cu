@@ -87,7 +87,8 @@ struct spdnn {
     bool exact_shortcut = true;        // SPDNN_EXACT_SHORTCUT=0 disables the exact-sum shortcut of the ALT2 form
     bool print_schedule = false;       // SPDNN_PRINT_SCHEDULE=1: one line per launch when the graph is built
     bool resident_always = false;      // ... even for a lone layer that the per-layer kernel would serve better
-    int res_ti_max = 16;               // largest group of images per block to try
+    int res_ti_max = 32;               // largest group of images per block to try
+    int res_ipt_max = 8;               // most images per thread to try
     int last_group = 0;                // group size of the last captured schedule's resident launches
     int smem_optin = 0;                // shared memory one block may opt in to
     bool stage_tables = true;          // bring the per-layer tables into shared memory with bulk copies
@@ -235,45 +236,57 @@ int blocks_per_sm(int k, bool uniform) {
     return uniform ? blocks_per_sm_t<0, true>() : blocks_per_sm_t<0, false>();
 }
 
-template <int TI, int MODE, int KT, bool UNIFORM, bool STAGED>
+template <int TI, int IPT, int MODE, int KT, bool UNIFORM, bool STAGED>
 int launch_resident_t(spdnn *c, const ResArgs &a, int grid, size_t smem) {
     static bool configured[64] = {};
     if (!configured[c->device & 63]) {
-        CK(cudaFuncSetAttribute(resident_kernel<TI, MODE, KT, UNIFORM, STAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        CK(cudaFuncSetAttribute(resident_kernel<TI, IPT, MODE, KT, UNIFORM, STAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 c->smem_optin - 1024));     // the kernel also has a little static shared memory
         configured[c->device & 63] = true;
     }
-    resident_kernel<TI, MODE, KT, UNIFORM, STAGED><<<grid, ResThreads<MODE>::value, smem, c->stream>>>(a);
+    resident_kernel<TI, IPT, MODE, KT, UNIFORM, STAGED><<<grid, ResThreads<MODE>::value, smem, c->stream>>>(a);
     CK(cudaGetLastError());
     return SPDNN_OK;
 }
 
-template <int TI>
-int launch_resident_ti(spdnn *c, const ResArgs &a, int grid, size_t smem, int mode, bool k32, bool uniform) {
+// ALT2 form (always a uniform weight): group sizes 32/16 with 8 images per thread, 16/8/4 with 4.
+template <int TI, int IPT>
+int launch_alt2(spdnn *c, const ResArgs &a, int grid, size_t smem, bool k32) {
     const bool staged = a.table_bytes > 0;
-    if (mode == kResAlt2) {       // always uniform
-        if (k32) return staged ? launch_resident_t<TI, kResAlt2, 32, true, true>(c, a, grid, smem)
-                               : launch_resident_t<TI, kResAlt2, 32, true, false>(c, a, grid, smem);
-        return staged ? launch_resident_t<TI, kResAlt2, 0, true, true>(c, a, grid, smem)
-                      : launch_resident_t<TI, kResAlt2, 0, true, false>(c, a, grid, smem);
-    }
-    if (k32) {
-        if (uniform) return staged ? launch_resident_t<TI, kResGeneric, 32, true, true>(c, a, grid, smem)
-                                   : launch_resident_t<TI, kResGeneric, 32, true, false>(c, a, grid, smem);
-        return staged ? launch_resident_t<TI, kResGeneric, 32, false, true>(c, a, grid, smem)
-                      : launch_resident_t<TI, kResGeneric, 32, false, false>(c, a, grid, smem);
-    }
-    if (uniform) return staged ? launch_resident_t<TI, kResGeneric, 0, true, true>(c, a, grid, smem)
-                               : launch_resident_t<TI, kResGeneric, 0, true, false>(c, a, grid, smem);
-    return staged ? launch_resident_t<TI, kResGeneric, 0, false, true>(c, a, grid, smem)
-                  : launch_resident_t<TI, kResGeneric, 0, false, false>(c, a, grid, smem);
+    if (k32) return staged ? launch_resident_t<TI, IPT, kResAlt2, 32, true, true>(c, a, grid, smem)
+                           : launch_resident_t<TI, IPT, kResAlt2, 32, true, false>(c, a, grid, smem);
+    return staged ? launch_resident_t<TI, IPT, kResAlt2, 0, true, true>(c, a, grid, smem)
+                  : launch_resident_t<TI, IPT, kResAlt2, 0, true, false>(c, a, grid, smem);
 }
 
-int launch_resident(spdnn *c, int ti, const ResArgs &a, int grid, size_t smem, int mode, bool k32, bool uniform) {
+template <int TI>
+int launch_generic(spdnn *c, const ResArgs &a, int grid, size_t smem, bool k32, bool uniform) {
+    const bool staged = a.table_bytes > 0;
+    if (k32) {
+        if (uniform) return staged ? launch_resident_t<TI, 4, kResGeneric, 32, true, true>(c, a, grid, smem)
+                                   : launch_resident_t<TI, 4, kResGeneric, 32, true, false>(c, a, grid, smem);
+        return staged ? launch_resident_t<TI, 4, kResGeneric, 32, false, true>(c, a, grid, smem)
+                      : launch_resident_t<TI, 4, kResGeneric, 32, false, false>(c, a, grid, smem);
+    }
+    if (uniform) return staged ? launch_resident_t<TI, 4, kResGeneric, 0, true, true>(c, a, grid, smem)
+                               : launch_resident_t<TI, 4, kResGeneric, 0, true, false>(c, a, grid, smem);
+    return staged ? launch_resident_t<TI, 4, kResGeneric, 0, false, true>(c, a, grid, smem)
+                  : launch_resident_t<TI, 4, kResGeneric, 0, false, false>(c, a, grid, smem);
+}
+
+int launch_resident(spdnn *c, int ti, int ipt, const ResArgs &a, int grid, size_t smem, int mode, bool k32, bool uniform) {
+    if (mode == kResAlt2) {
+        if (ipt == 8) return ti == 32 ? launch_alt2<32, 8>(c, a, grid, smem, k32) : launch_alt2<16, 8>(c, a, grid, smem, k32);
+        switch (ti) {
+            case 16: return launch_alt2<16, 4>(c, a, grid, smem, k32);
+            case 8: return launch_alt2<8, 4>(c, a, grid, smem, k32);
+            default: return launch_alt2<4, 4>(c, a, grid, smem, k32);
+        }
+    }
     switch (ti) {
-        case 16: return launch_resident_ti<16>(c, a, grid, smem, mode, k32, uniform);
-        case 8: return launch_resident_ti<8>(c, a, grid, smem, mode, k32, uniform);
-        default: return launch_resident_ti<4>(c, a, grid, smem, mode, k32, uniform);
+        case 16: return launch_generic<16>(c, a, grid, smem, k32, uniform);
+        case 8: return launch_generic<8>(c, a, grid, smem, k32, uniform);
+        default: return launch_generic<4>(c, a, grid, smem, k32, uniform);
     }
 }
 
@@ -357,7 +370,7 @@ int enqueue_layers(spdnn *c) {
         const float *yin = c->y[step & 1];
         float *yout = c->y[(step & 1) ^ 1];
         // ---- try a resident chunk starting at layer l
-        int f = 0, ti = 0, rows = 0, tb = 0;
+        int f = 0, ti = 0, ipt = 4, rows = 0, tb = 0;
         if (c->res[l]) {
             const DevRes &R0 = *c->res[l];
             const bool k32 = (R0.k == 32);
@@ -365,8 +378,16 @@ int enqueue_layers(spdnn *c) {
                 return 2 * (size_t)r * t_i * 4 + 2 * (size_t)table + 2048 <= (size_t)c->smem_optin;
             };
             rows = resident_rows(R0);
-            for (int t_i : {16, 8, 4})
-                if (t_i <= c->res_ti_max && fits(t_i, rows, 0)) { ti = t_i; break; }
+            // (images per block, images per thread) in order of preference
+            static const int kAlt2[][2] = {{32, 8}, {16, 8}, {16, 4}, {8, 4}, {4, 4}};
+            static const int kGeneric[][2] = {{16, 4}, {8, 4}, {4, 4}};
+            const int (*cand)[2] = R0.mode == kResAlt2 ? kAlt2 : kGeneric;
+            const int ncand = R0.mode == kResAlt2 ? 5 : 3;
+            for (int q = 0; q < ncand; ++q)
+                if (cand[q][0] <= c->res_ti_max && cand[q][1] <= c->res_ipt_max && fits(cand[q][0], rows, 0)) {
+                    ti = cand[q][0]; ipt = cand[q][1];
+                    break;
+                }
             if (ti) {
                 // extend while the layers are of one kernel variant and the group still fits
                 f = 1;
@@ -401,12 +422,12 @@ int enqueue_layers(spdnn *c) {
             a.exact_ok = (l > 0 && c->clip <= 1024.0f && c->exact_shortcut) ? 1 : 0;
             const int grid = std::max(1, (c->tiles_cap * 32 + ti - 1) / ti);
             const size_t smem = 2 * (size_t)rows * ti * 4 + 2 * (size_t)tb;
-            int rc = launch_resident(c, ti, a, grid, smem, R0.mode, R0.k == 32, R0.uniform);
+            int rc = launch_resident(c, ti, ipt, a, grid, smem, R0.mode, R0.k == 32, R0.uniform);
             if (rc) return rc;
             c->last_group = ti;
             if (c->print_schedule)
-                fprintf(stderr, "[spdnn] step %d: resident layers %d..%d  group %d images  %s  rows %d (v_in %d, classes %d)  smem %zu B  tables %s\n",
-                        step, l, l + f - 1, ti, R0.mode == kResAlt2 ? "ALT2" : "GENERIC", rows, R0.v_in, R0.classes, smem,
+                fprintf(stderr, "[spdnn] step %d: resident layers %d..%d  group %d images (%d per thread)  %s  rows %d (v_in %d, classes %d)  smem %zu B  tables %s\n",
+                        step, l, l + f - 1, ti, ipt, R0.mode == kResAlt2 ? "ALT2" : "GENERIC", rows, R0.v_in, R0.classes, smem,
                         tb ? "staged" : "global");
             l += f;
             chunk = std::min(chunk * 2, c->chunk_max);
@@ -521,8 +542,9 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
         if (const char *e = getenv("SPDNN_RESIDENT")) { c->resident = atoi(e) != 0; c->resident_always = atoi(e) > 1; }
         if (const char *e = getenv("SPDNN_RESIDENT_TI")) {
             const int ti = atoi(e);
-            if (ti == 16 || ti == 8 || ti == 4) c->res_ti_max = ti;
+            if (ti == 32 || ti == 16 || ti == 8 || ti == 4) c->res_ti_max = ti;
         }
+        if (const char *e = getenv("SPDNN_RESIDENT_IPT")) c->res_ipt_max = atoi(e) >= 8 ? 8 : 4;
         if (const char *e = getenv("SPDNN_STAGE_TABLES")) c->stage_tables = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_PRINT_SCHEDULE")) c->print_schedule = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_EXACT_SHORTCUT")) c->exact_shortcut = atoi(e) != 0;

@@ -255,16 +255,23 @@ template <int MODE>
 struct ResThreads {
     static constexpr int value = (MODE == kResAlt2) ? kThreads : SPDNN_GENERIC_THREADS;
 };
-template <int TI, int MODE, int KT, bool UNIFORM, bool STAGED>
-__global__ void __launch_bounds__(ResThreads<MODE>::value, (MODE == kResAlt2 ? SPDNN_ALT2_MIN_BLOCKS : 1)) resident_kernel(const ResArgs a) {
+// IPT = images per thread (4 or 8): with 8 a thread carries two float4 halves through every
+// step, which halves the per-layer bookkeeping (barrier, table wait, loop control, addresses)
+// per image; it is used for the light ALT2 form.
+template <int TI, int IPT, int MODE, int KT, bool UNIFORM, bool STAGED>
+__global__ void __launch_bounds__(ResThreads<MODE>::value, (MODE == kResAlt2 ? (IPT == 8 ? SPDNN_ALT2_MIN_BLOCKS / 2 : SPDNN_ALT2_MIN_BLOCKS) : 1))
+resident_kernel(const ResArgs a) {
     constexpr int NT = ResThreads<MODE>::value;
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ unsigned int s_alive[3];
     __shared__ int s_last, s_fail;
     __shared__ __align__(8) unsigned long long s_bar[2];
-    constexpr int LPC = TI / 4;                  // threads per class
+    constexpr int NQ = IPT / 4;                  // float4 halves per thread
+    constexpr int LPC = TI / IPT;                // threads per class
     constexpr int CPI = NT / LPC;                // classes per pass of the block
     constexpr int RS = TI * 4;                   // bytes per row
+    constexpr int TB = IPT * 4;                  // bytes of a row one thread owns
+    constexpr unsigned int kFull = (IPT == 8) ? 0xFFu : 0xFu;
     const int tid = threadIdx.x, lane = tid & 31;
     const int sub = tid % LPC, grp = tid / LPC;
     const LoopCtl ctl = *a.ctl_in;
@@ -288,42 +295,48 @@ __global__ void __launch_bounds__(ResThreads<MODE>::value, (MODE == kResAlt2 ? S
         }
         // ---- load one row per value id of the block's images (dead images were dropped: read
         //      through the work list)
-        const float *p[4];
         unsigned int my_valid = 0;
-        bool contiguous = ctl.identity != 0;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const int j = j0 + sub * 4 + q;
-            const bool v = j < live_in;
-            my_valid |= (v ? 1u : 0u) << q;
-            const int jj = v ? j : j0;
-            const int src = ctl.identity ? jj : __ldg(a.slot + jj);
-            p[q] = a.yin + (size_t)(src >> 5) * a.tile_stride + (src & 31);
-        }
-        if (my_valid != 0xFu) contiguous = false;
         {
+            const float *p[IPT];
+            bool contiguous = ctl.identity != 0;
+#pragma unroll
+            for (int q = 0; q < IPT; ++q) {
+                const int j = j0 + sub * IPT + q;
+                const bool v = j < live_in;
+                my_valid |= (v ? 1u : 0u) << q;
+                const int jj = v ? j : j0;
+                const int src = ctl.identity ? jj : __ldg(a.slot + jj);
+                p[q] = a.yin + (size_t)(src >> 5) * a.tile_stride + (src & 31);
+            }
+            if (my_valid != kFull) contiguous = false;
             const ResLayer L0 = a.layers[0];
             for (int v = grp; v < L0.v_in; v += CPI) {
                 const size_t e = L0.rep ? (size_t)__ldg(L0.rep + v) : (size_t)v * 32;
-                float4 x;
-                if (contiguous) {
-                    x = __ldg(reinterpret_cast<const float4 *>(p[0] + e));
-                } else {
-                    x.x = (my_valid & 1u) ? __ldg(p[0] + e) : 0.0f;
-                    x.y = (my_valid & 2u) ? __ldg(p[1] + e) : 0.0f;
-                    x.z = (my_valid & 4u) ? __ldg(p[2] + e) : 0.0f;
-                    x.w = (my_valid & 8u) ? __ldg(p[3] + e) : 0.0f;
+                unsigned char *dst = cur + resident_phys_row(v) * RS + sub * TB;
+#pragma unroll
+                for (int h = 0; h < NQ; ++h) {
+                    float4 x;
+                    if (contiguous) {
+                        x = __ldg(reinterpret_cast<const float4 *>(p[0] + e) + h);
+                    } else {
+                        x.x = (my_valid >> (4 * h) & 1u) ? __ldg(p[4 * h + 0] + e) : 0.0f;
+                        x.y = (my_valid >> (4 * h) & 2u) ? __ldg(p[4 * h + 1] + e) : 0.0f;
+                        x.z = (my_valid >> (4 * h) & 4u) ? __ldg(p[4 * h + 2] + e) : 0.0f;
+                        x.w = (my_valid >> (4 * h) & 8u) ? __ldg(p[4 * h + 3] + e) : 0.0f;
+                    }
+                    *reinterpret_cast<float4 *>(dst + 16 * h) = x;
                 }
-                *reinterpret_cast<float4 *>(cur + resident_phys_row(v) * RS + sub * 16) = x;
             }
             // rows v_in .. even(v_in) + 1 are the zero rows padded table entries point at
             const int ve = (L0.v_in + 1) & ~1;
             for (int r = L0.v_in + grp; r < ve + 2; r += CPI)
-                *reinterpret_cast<float4 *>(cur + (r < ve ? resident_phys_row(r) : r) * RS + sub * 16) = make_float4(0, 0, 0, 0);
+#pragma unroll
+                for (int h = 0; h < NQ; ++h)
+                    *reinterpret_cast<float4 *>(cur + (r < ve ? resident_phys_row(r) : r) * RS + sub * TB + 16 * h) = make_float4(0, 0, 0, 0);
         }
         // LPC divides 32, so every warp holds all sub-columns: the OR over a warp is the block's
         // mask of valid images (bit i = image j0 + i), identical in every thread
-        unsigned int alive_prev = __reduce_or_sync(0xffffffffu, my_valid << (sub * 4));
+        unsigned int alive_prev = __reduce_or_sync(0xffffffffu, my_valid << (sub * IPT));
         __syncthreads();
 
         // ---- the layers of this chunk
@@ -368,47 +381,58 @@ __global__ void __launch_bounds__(ResThreads<MODE>::value, (MODE == kResAlt2 ? S
             const float lw = __int_as_float(hdr.z);
             last_classes = classes;
             unsigned int bits = 0;
-            const unsigned char *in = cur + sub * 16;
+            const unsigned char *in = cur + sub * TB;
             for (int u = grp; u < classes; u += CPI) {
-                float4 s;
+                float4 s[NQ];
                 int out_row;
                 if (MODE == kResAlt2) {
                     const int4 e = STAGED ? reinterpret_cast<const int4 *>(T)[1 + u] : __ldg(reinterpret_cast<const int4 *>(T) + 1 + u);
-                    const float4 va = *reinterpret_cast<const float4 *>(in + e.x * RS);
-                    const float4 vb = *reinterpret_cast<const float4 *>(in + e.y * RS);
-                    s = class_sum_alt2<KT>(va, vb, lk, lw, a.exact_ok != 0);
+#pragma unroll
+                    for (int h = 0; h < NQ; ++h) {
+                        const float4 va = *reinterpret_cast<const float4 *>(in + e.x * RS + 16 * h);
+                        const float4 vb = *reinterpret_cast<const float4 *>(in + e.y * RS + 16 * h);
+                        s[h] = class_sum_alt2<KT>(va, vb, lk, lw, a.exact_ok != 0);
+                    }
                     out_row = e.z;
                 } else {
                     const int kp = lk + 4;
                     const int32_t *rows = T + 4 + (size_t)u * kp;
-                    s = class_sum_generic<KT, UNIFORM, STAGED, RS>(rows, reinterpret_cast<const float *>(rows) + (size_t)classes * kp, lk, lw, in);
+#pragma unroll
+                    for (int h = 0; h < NQ; ++h)
+                        s[h] = class_sum_generic<KT, UNIFORM, STAGED, RS>(rows, reinterpret_cast<const float *>(rows) + (size_t)classes * kp,
+                                                                          lk, lw, in + 16 * h);
                     out_row = STAGED ? rows[lk] : __ldg(rows + lk);
                 }
-                // x<0 ? 0 : x>clip ? clip : x (all_network.cu:8-10); for the finite x that occur this is
-                // min(max(x, 0), clip), two instructions instead of two compares and two selects
-                float4 y;
-                y.x = fminf(fmaxf(__fadd_rn(s.x, a.bias), 0.0f), a.clip);
-                y.y = fminf(fmaxf(__fadd_rn(s.y, a.bias), 0.0f), a.clip);
-                y.z = fminf(fmaxf(__fadd_rn(s.z, a.bias), 0.0f), a.clip);
-                y.w = fminf(fmaxf(__fadd_rn(s.w, a.bias), 0.0f), a.clip);
-                // dead images stay dead: with bias <= 0 an all-zero image stays all-zero by itself
-                if (force_dead) {
-                    const unsigned int al = alive_prev >> (sub * 4);
-                    if (!(al & 1u)) y.x = 0.0f;
-                    if (!(al & 2u)) y.y = 0.0f;
-                    if (!(al & 4u)) y.z = 0.0f;
-                    if (!(al & 8u)) y.w = 0.0f;
+#pragma unroll
+                for (int h = 0; h < NQ; ++h) {
+                    // x<0 ? 0 : x>clip ? clip : x (all_network.cu:8-10); for the finite x that occur this is
+                    // min(max(x, 0), clip), two instructions instead of two compares and two selects
+                    float4 y;
+                    y.x = fminf(fmaxf(__fadd_rn(s[h].x, a.bias), 0.0f), a.clip);
+                    y.y = fminf(fmaxf(__fadd_rn(s[h].y, a.bias), 0.0f), a.clip);
+                    y.z = fminf(fmaxf(__fadd_rn(s[h].z, a.bias), 0.0f), a.clip);
+                    y.w = fminf(fmaxf(__fadd_rn(s[h].w, a.bias), 0.0f), a.clip);
+                    // dead images stay dead: with bias <= 0 an all-zero image stays all-zero by itself
+                    if (force_dead) {
+                        const unsigned int al = alive_prev >> (sub * IPT + 4 * h);
+                        if (!(al & 1u)) y.x = 0.0f;
+                        if (!(al & 2u)) y.y = 0.0f;
+                        if (!(al & 4u)) y.z = 0.0f;
+                        if (!(al & 8u)) y.w = 0.0f;
+                    }
+                    bits |= ((y.x != 0.0f ? 1u : 0u) | (y.y != 0.0f ? 2u : 0u) | (y.z != 0.0f ? 4u : 0u) | (y.w != 0.0f ? 8u : 0u)) << (4 * h);
+                    *reinterpret_cast<float4 *>(nxt + out_row * RS + sub * TB + 16 * h) = y;
                 }
-                bits |= (y.x != 0.0f ? 1u : 0u) | (y.y != 0.0f ? 2u : 0u) | (y.z != 0.0f ? 4u : 0u) | (y.w != 0.0f ? 8u : 0u);
-                *reinterpret_cast<float4 *>(nxt + out_row * RS + sub * 16) = y;
             }
             if (MODE == kResGeneric) {
                 // zero rows of the buffer just written (the next layer's padded entries point there)
                 const int ue = (classes + 1) & ~1;
                 for (int r = classes + grp; r < ue + 2; r += CPI)
-                    *reinterpret_cast<float4 *>(nxt + (r < ue ? resident_phys_row(r) : r) * RS + sub * 16) = make_float4(0, 0, 0, 0);
+#pragma unroll
+                    for (int h = 0; h < NQ; ++h)
+                        *reinterpret_cast<float4 *>(nxt + (r < ue ? resident_phys_row(r) : r) * RS + sub * TB + 16 * h) = make_float4(0, 0, 0, 0);
             }
-            const unsigned int wm = __reduce_or_sync(0xffffffffu, bits << (sub * 4));
+            const unsigned int wm = __reduce_or_sync(0xffffffffu, bits << (sub * IPT));
             if (lane == 0 && wm) atomicOr(&s_alive[li % 3], wm);
             __syncthreads();
             const unsigned int alive_now = s_alive[li % 3] & alive_prev;
@@ -436,14 +460,18 @@ __global__ void __launch_bounds__(ResThreads<MODE>::value, (MODE == kResAlt2 ? S
         if (alive_prev != 0u) {
             const ResLayer LL = a.layers[li - 1];
             const int tile = j0 >> 5, lane0 = j0 & 31;
-            float *out = a.yout + (size_t)tile * a.tile_stride + lane0 + sub * 4;
+            float *out = a.yout + (size_t)tile * a.tile_stride + lane0 + sub * IPT;
             for (int u = grp; u < last_classes; u += CPI) {
-                const float4 y = *reinterpret_cast<const float4 *>(cur + resident_phys_row(u) * RS + sub * 16);
-                if (LL.mem_ptr == nullptr) {
-                    *reinterpret_cast<float4 *>(out + (size_t)u * 32) = y;
-                } else {
-                    const int mb = __ldg(LL.mem_ptr + u), me = __ldg(LL.mem_ptr + u + 1);
-                    for (int m = mb; m < me; ++m) *reinterpret_cast<float4 *>(out + __ldg(LL.mem + m)) = y;
+                const unsigned char *src = cur + resident_phys_row(u) * RS + sub * TB;
+#pragma unroll
+                for (int h = 0; h < NQ; ++h) {
+                    const float4 y = *reinterpret_cast<const float4 *>(src + 16 * h);
+                    if (LL.mem_ptr == nullptr) {
+                        *reinterpret_cast<float4 *>(out + (size_t)u * 32 + 4 * h) = y;
+                    } else {
+                        const int mb = __ldg(LL.mem_ptr + u), me = __ldg(LL.mem_ptr + u + 1);
+                        for (int m = mb; m < me; ++m) *reinterpret_cast<float4 *>(out + __ldg(LL.mem + m) + 4 * h) = y;
+                    }
                 }
             }
             if (tid == 0) atomicOr(a.mask + tile, alive_prev << lane0);
