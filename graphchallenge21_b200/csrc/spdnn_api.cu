@@ -84,6 +84,7 @@ struct spdnn {
     int32_t *died_at = nullptr;        // [layers] images that died in each layer
     ResLayer *res_table = nullptr;     // [layers] tables of the resident kernel
     bool resident = true;              // use the shared-memory-resident kernel where a chunk fits
+    bool reps_only = true;             // SPDNN_REPS_ONLY=0: every launch writes all N rows
     bool exact_shortcut = true;        // SPDNN_EXACT_SHORTCUT=0 disables the exact-sum shortcut of the ALT2 form
     bool print_schedule = false;       // SPDNN_PRINT_SCHEDULE=1: one line per launch when the graph is built
     bool resident_always = false;      // ... even for a lone layer that the per-layer kernel would serve better
@@ -362,36 +363,42 @@ inline int resident_rows(const DevRes &R) { return ((std::max(R.v_in, R.classes)
 // Enqueues the whole network: chunks of layers through the resident kernel where a group of
 // images fits in shared memory (chunk lengths chunk_first, x2, ... up to chunk_max: short while
 // images still die, long once the survivors are stable), one launch per layer otherwise.
-int enqueue_layers(spdnn *c) {
-    int step = 0, l = 0, chunk = c->chunk_first;
-    c->last_group = 0;
+struct Step {
+    int first = 0, count = 1;      // layers [first, first + count)
+    int ti = 0, ipt = 4;           // resident chunk: images per block / per thread; ti == 0: per-layer kernel
+    int rows = 0, table = 0;       // resident chunk: rows of one activation buffer, bytes per staged table
+};
+
+// The launches of one pass, front to back.
+std::vector<Step> plan_steps(spdnn *c) {
+    std::vector<Step> plan;
+    int l = 0, chunk = c->chunk_first;
     while (l < c->layers) {
-        const DevLayer &L = *c->layer[l];
-        const float *yin = c->y[step & 1];
-        float *yout = c->y[(step & 1) ^ 1];
-        // ---- try a resident chunk starting at layer l
-        int f = 0, ti = 0, ipt = 4, rows = 0, tb = 0;
+        Step st;
+        st.first = l;
         if (c->res[l]) {
             const DevRes &R0 = *c->res[l];
             const bool k32 = (R0.k == 32);
             auto fits = [&](int t_i, int r, int table) {
                 return 2 * (size_t)r * t_i * 4 + 2 * (size_t)table + 2048 <= (size_t)c->smem_optin;
             };
-            rows = resident_rows(R0);
-            // (images per block, images per thread) in order of preference
-            static const int kAlt2[][2] = {{32, 8}, {16, 8}, {16, 4}, {8, 4}, {4, 4}};
+            int rows = resident_rows(R0), ti = 0, ipt = 4;
+            // (images per block, images per thread) in order of preference; a form that would leave
+            // most threads without a class (under half of what one pass of the block covers) is skipped
+            static const int kAlt2[][2] = {{32, 8}, {16, 4}, {16, 8}, {8, 4}, {4, 4}};
             static const int kGeneric[][2] = {{16, 4}, {8, 4}, {4, 4}};
             const int (*cand)[2] = R0.mode == kResAlt2 ? kAlt2 : kGeneric;
             const int ncand = R0.mode == kResAlt2 ? 5 : 3;
-            for (int q = 0; q < ncand; ++q)
-                if (cand[q][0] <= c->res_ti_max && cand[q][1] <= c->res_ipt_max && fits(cand[q][0], rows, 0)) {
-                    ti = cand[q][0]; ipt = cand[q][1];
-                    break;
-                }
+            for (int q = 0; q < ncand; ++q) {
+                const int t_i = cand[q][0], i_pt = cand[q][1];
+                if (t_i > c->res_ti_max || i_pt > c->res_ipt_max || !fits(t_i, rows, 0)) continue;
+                if (i_pt == 8 && R0.classes * 2 < kThreads * i_pt / t_i) continue;
+                ti = t_i; ipt = i_pt;
+                break;
+            }
             if (ti) {
                 // extend while the layers are of one kernel variant and the group still fits
-                f = 1;
-                int blob = R0.blob_bytes;
+                int f = 1, blob = R0.blob_bytes;
                 while (f < chunk && l + f < c->layers && c->res[l + f]) {
                     const DevRes &M = *c->res[l + f];
                     if (M.mode != R0.mode || M.uniform != R0.uniform || (M.k == 32) != k32) break;
@@ -401,36 +408,58 @@ int enqueue_layers(spdnn *c) {
                     blob = std::max(blob, M.blob_bytes);
                     ++f;
                 }
-                tb = (blob + 127) / 128 * 128;
+                int tb = (blob + 127) / 128 * 128;
                 if (!(c->stage_tables && fits(ti, rows, tb))) tb = 0;
                 // A lone layer that reads all N rows of every image but computes few classes from
                 // them (the first layer of a network with repeated columns) gains nothing from
                 // staging the rows in shared memory: gather straight from global memory instead.
-                if (f == 1 && R0.v_in == c->n && R0.classes * 2 <= c->n && !c->resident_always) f = 0;
+                const bool lone_wide = (f == 1 && R0.v_in == c->n && R0.classes * 2 <= c->n && !c->resident_always);
+                if (!lone_wide) { st.count = f; st.ti = ti; st.ipt = ipt; st.rows = rows; st.table = tb; }
             }
         }
-        if (f > 0) {
+        if (st.ti) chunk = std::min(chunk * 2, c->chunk_max);
+        plan.push_back(st);
+        l += st.count;
+    }
+    return plan;
+}
+
+// Enqueues the whole network: chunks of layers through the resident kernel where a group of
+// images fits in shared memory (chunk lengths chunk_first, x2, ... up to chunk_max: short while
+// images still die, long once the survivors are stable), one launch per layer otherwise.  A
+// launch that is followed by a resident chunk writes only the one row per class that chunk
+// will read.
+int enqueue_layers(spdnn *c) {
+    const std::vector<Step> plan = plan_steps(c);
+    c->last_group = 0;
+    for (size_t step = 0; step < plan.size(); ++step) {
+        const Step &st = plan[step];
+        const int l = st.first;
+        const DevLayer &L = *c->layer[l];
+        const float *yin = c->y[step & 1];
+        float *yout = c->y[(step & 1) ^ 1];
+        const bool next_resident = c->reps_only && step + 1 < plan.size() && plan[step + 1].ti != 0;
+        if (st.ti) {
             const DevRes &R0 = *c->res[l];
             ResArgs a;
             a.yin = yin; a.yout = yout; a.tile_stride = c->tile_stride;
             a.ctl_in = c->ctl + step; a.ctl_out = c->ctl + step + 1;
             a.slot = c->slot; a.mask = c->mask; a.ids0 = c->ids[0]; a.ids1 = c->ids[1];
             a.counter = c->counter; a.work = c->counter + 1; a.status = c->status;
-            a.layers = c->res_table + l; a.died_at = c->died_at + l; a.nlayers = f;
-            a.buf_rows = rows; a.table_bytes = tb;
+            a.layers = c->res_table + l; a.died_at = c->died_at + l; a.nlayers = st.count;
+            a.buf_rows = st.rows; a.table_bytes = st.table;
             a.n = c->n; a.bias = c->bias; a.clip = c->clip;
+            a.reps_only = next_resident ? 1 : 0;
             a.exact_ok = (l > 0 && c->clip <= 1024.0f && c->exact_shortcut) ? 1 : 0;
-            const int grid = std::max(1, (c->tiles_cap * 32 + ti - 1) / ti);
-            const size_t smem = 2 * (size_t)rows * ti * 4 + 2 * (size_t)tb;
-            int rc = launch_resident(c, ti, ipt, a, grid, smem, R0.mode, R0.k == 32, R0.uniform);
+            const int grid = std::max(1, (c->tiles_cap * 32 + st.ti - 1) / st.ti);
+            const size_t smem = 2 * (size_t)st.rows * st.ti * 4 + 2 * (size_t)st.table;
+            int rc = launch_resident(c, st.ti, st.ipt, a, grid, smem, R0.mode, R0.k == 32, R0.uniform);
             if (rc) return rc;
-            c->last_group = ti;
+            c->last_group = st.ti;
             if (c->print_schedule)
-                fprintf(stderr, "[spdnn] step %d: resident layers %d..%d  group %d images (%d per thread)  %s  rows %d (v_in %d, classes %d)  smem %zu B  tables %s\n",
-                        step, l, l + f - 1, ti, ipt, R0.mode == kResAlt2 ? "ALT2" : "GENERIC", rows, R0.v_in, R0.classes, smem,
-                        tb ? "staged" : "global");
-            l += f;
-            chunk = std::min(chunk * 2, c->chunk_max);
+                fprintf(stderr, "[spdnn] step %zu: resident layers %d..%d  group %d images (%d per thread)  %s  rows %d (v_in %d, classes %d)  smem %zu B  tables %s%s\n",
+                        step, l, l + st.count - 1, st.ti, st.ipt, R0.mode == kResAlt2 ? "ALT2" : "GENERIC", st.rows, R0.v_in,
+                        R0.classes, smem, st.table ? "staged" : "global", next_resident ? "  writes representatives only" : "");
         } else {
             LayerDesc d;
             d.off = L.off; d.vals = L.vals;
@@ -451,6 +480,7 @@ int enqueue_layers(spdnn *c) {
             a.slot = c->slot; a.mask = c->mask; a.ids0 = c->ids[0]; a.ids1 = c->ids[1];
             a.counter = c->counter; a.work = c->counter + 1; a.status = c->status;
             a.died_at = c->died_at + l;
+            a.first_member_only = (next_resident && !L.identity_members) ? 1 : 0;
             a.bias = c->bias; a.clip = c->clip;
             const long long ncb = (L.classes + d.classes_per_item - 1) / d.classes_per_item;
             if ((long long)c->tiles_cap * ncb >= 0xffffffffLL) return fail(c, SPDNN_ERR_LIMIT, "batch too large for one launch");
@@ -458,12 +488,11 @@ int enqueue_layers(spdnn *c) {
             int rc = launch_layer(c, d, a, grid, L.uniform);
             if (rc) return rc;
             if (c->print_schedule)
-                fprintf(stderr, "[spdnn] step %d: per-layer kernel, layer %d  classes %d  k %d  grid %d\n", step, l, L.classes, L.k, grid);
-            l += 1;
+                fprintf(stderr, "[spdnn] step %zu: per-layer kernel, layer %d  classes %d  k %d  grid %d%s\n", step, l, L.classes, L.k,
+                        grid, a.first_member_only ? "  writes representatives only" : "");
         }
-        ++step;
     }
-    c->nsteps = step;
+    c->nsteps = (int)plan.size();
     return SPDNN_OK;
 }
 
@@ -548,6 +577,7 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
         if (const char *e = getenv("SPDNN_STAGE_TABLES")) c->stage_tables = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_PRINT_SCHEDULE")) c->print_schedule = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_EXACT_SHORTCUT")) c->exact_shortcut = atoi(e) != 0;
+        if (const char *e = getenv("SPDNN_REPS_ONLY")) c->reps_only = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_CHUNK_FIRST")) c->chunk_first = std::max(1, atoi(e));
         if (const char *e = getenv("SPDNN_CHUNK_MAX")) c->chunk_max = std::max(1, atoi(e));
         if (const char *e = getenv("SPDNN_HOST_BUDGET_MB")) c->host_budget = (size_t)atoll(e) << 20;

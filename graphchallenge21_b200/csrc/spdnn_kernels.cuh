@@ -62,6 +62,7 @@ struct LayerArgs {
     unsigned int *work;        // next work item to hand out (zero on entry, zero on exit)
     int32_t *status;           // set non-zero when the kernel finds an inconsistency
     int32_t *died_at;          // where the per-layer kernel records how many images died in its layer (or nullptr)
+    int first_member_only;     // 1: the next launch reads one row per class (its first member): store only that row
     float bias, clip;
 };
 
@@ -238,7 +239,7 @@ __global__ void __launch_bounds__(kThreads, SPDNN_MIN_BLOCKS) layer_kernel(const
             const float s = class_sum<KT, UNIFORM>(d, u, yin);
             const float y = relu_clip(__fadd_rn(s, a.bias), a.clip);
             any |= (y != 0.0f);
-            const int cnt = me - mb;
+            const int cnt = a.first_member_only ? 1 : me - mb;
             if (cnt <= 32) {
                 for (int m = 0; m < cnt; ++m) yout[__shfl_sync(0xffffffffu, mreg, m)] = y;
             } else {

@@ -73,6 +73,8 @@ struct ResArgs {
     int buf_rows;             // rows of one activation buffer (largest layer of the chunk, even, + 2)
     int table_bytes;          // shared memory reserved per staged table (0 = read the tables from global memory)
     int n;                    // neurons
+    int reps_only;            // 1: the next launch is a resident chunk, which reads one row per class (the first
+                              // member): write only that row at the end of this chunk
     int exact_ok;             // the inputs of every layer of the chunk are activations in [0, clip], clip <= 1024
     float bias, clip;
 };
@@ -469,7 +471,7 @@ resident_kernel(const ResArgs a) {
                     if (LL.mem_ptr == nullptr) {
                         *reinterpret_cast<float4 *>(out + (size_t)u * 32 + 4 * h) = y;
                     } else {
-                        const int mb = __ldg(LL.mem_ptr + u), me = __ldg(LL.mem_ptr + u + 1);
+                        const int mb = __ldg(LL.mem_ptr + u), me = a.reps_only ? mb + 1 : __ldg(LL.mem_ptr + u + 1);
                         for (int m = mb; m < me; ++m) *reinterpret_cast<float4 *>(out + __ldg(LL.mem + m) + 4 * h) = y;
                     }
                 }
@@ -492,6 +494,7 @@ resident_kernel(const ResArgs a) {
     la.ctl_in = a.ctl_in; la.ctl_out = a.ctl_out; la.slot = a.slot; la.mask = a.mask;
     la.ids0 = a.ids0; la.ids1 = a.ids1; la.counter = a.counter; la.work = a.work; la.status = a.status;
     la.died_at = nullptr;
+    la.first_member_only = 0;
     la.bias = a.bias; la.clip = a.clip;
     rebuild_worklist(la, live_in, ctl.ids_buf);
 }
