@@ -100,10 +100,11 @@ class ClockSampler:
             try:
                 self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
                 self.bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))
-                self.power.append(nv.nvmlDeviceGetPowerUsage(h) / 1000.0)
+                if len(self.samples) % 8 == 1:
+                    self.power.append(nv.nvmlDeviceGetPowerUsage(h) / 1000.0)
             except Exception:
                 pass
-            time.sleep(0.001)
+            time.sleep(0.0002)
 
     def start(self):
         try:
