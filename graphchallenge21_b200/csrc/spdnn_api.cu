@@ -93,7 +93,7 @@ struct spdnn {
     int last_group = 0;                // group size of the last captured schedule's resident launches
     int smem_optin = 0;                // shared memory one block may opt in to
     bool stage_tables = true;          // bring the per-layer tables into shared memory with bulk copies
-    int chunk_first = 4, chunk_max = 128;
+    int chunk_first = 8, chunk_max = 256;
     int nsteps = 0;                    // launches of the last captured schedule
     std::vector<int32_t> host_died, host_live;
     int32_t *slot = nullptr;

@@ -124,25 +124,24 @@ __device__ __forceinline__ float class_sum(const LayerDesc &d, int u, const floa
     return UNIFORM ? __fmul_rn(acc, d.w) : acc;
 }
 
-// The last block to finish turns the per-tile ballots into the next layer's work list.
+// The last block to finish turns the per-tile ballots into the next launch's work list: every
+// warp takes a contiguous run of tiles, counts its survivors (lanes split the run, warp scan),
+// a block scan over the warps gives each run its first position, and the warp then walks its
+// tiles 32 at a time with lane b handling bit b, so that the reads of the old ids and the
+// writes of the new work list and ids are coalesced and independent from tile to tile.
 __device__ __forceinline__ void rebuild_worklist(const LayerArgs &a, int live_in, int ids_buf) {
     __shared__ int s_warp[32];          // works for any block size up to 1024 threads
     __shared__ int s_total;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int ntiles = (live_in + 31) >> 5;
-    const int nthreads = blockDim.x, nwarps = nthreads >> 5;
-    const int per = (ntiles + nthreads - 1) / nthreads;
-    const int t0 = min(tid * per, ntiles), t1 = min(t0 + per, ntiles);
+    const int nwarps = blockDim.x >> 5;
+    const int per_warp = (ntiles + nwarps - 1) / nwarps;
+    const int w0 = min(warp * per_warp, ntiles), w1 = min(w0 + per_warp, ntiles);
     int cnt = 0;
-    for (int t = t0; t < t1; ++t) cnt += __popc(__ldcg(a.mask + t));
-    // exclusive block scan of cnt
-    int inc = cnt;
+    for (int t = w0 + lane; t < w1; t += 32) cnt += __popc(__ldcg(a.mask + t));
 #pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-        const int o = __shfl_up_sync(0xffffffffu, inc, d);
-        if (lane >= d) inc += o;
-    }
-    if (lane == 31) s_warp[warp] = inc;
+    for (int d = 16; d > 0; d >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, d);      // survivors of the warp's run
+    if (lane == 0) s_warp[warp] = cnt;
     __syncthreads();
     if (warp == 0) {
         int w = lane < nwarps ? s_warp[lane] : 0;
@@ -155,26 +154,30 @@ __device__ __forceinline__ void rebuild_worklist(const LayerArgs &a, int live_in
         if (lane == nwarps - 1) s_total = w;
     }
     __syncthreads();
-    int base = inc - cnt + (warp ? s_warp[warp - 1] : 0);
     const int total = s_total;
     if (total > live_in && tid == 0) atomicExch(a.status, 2);
     const bool same = (total == live_in);      // nobody died: positions are already dense
     if (!same) {
         const int32_t *ids_old = ids_buf ? a.ids1 : a.ids0;
         int32_t *ids_new = ids_buf ? a.ids0 : a.ids1;
-        for (int t = t0; t < t1; ++t) {
-            uint32_t m = __ldcg(a.mask + t);
-            while (m) {
-                const int b = __ffs(m) - 1;
-                m &= m - 1;
-                const int pos = t * 32 + b;
-                a.slot[base] = pos;
-                ids_new[base] = ids_old[pos];
-                ++base;
+        int run = warp ? s_warp[warp - 1] : 0;         // first position of this warp's run
+        const uint32_t below = (1u << lane) - 1u;
+        for (int tb = w0; tb < w1; tb += 32) {
+            const uint32_t mine = (tb + lane < w1) ? __ldcg(a.mask + tb + lane) : 0u;    // 32 ballots per load
+            const int n = min(32, w1 - tb);
+            for (int i = 0; i < n; ++i) {
+                const uint32_t m = __shfl_sync(0xffffffffu, mine, i);
+                if ((m >> lane) & 1u) {
+                    const int pos = (tb + i) * 32 + lane;
+                    const int dst = run + __popc(m & below);
+                    a.slot[dst] = pos;
+                    ids_new[dst] = ids_old[pos];
+                }
+                run += __popc(m);
             }
         }
     }
-    for (int t = t0; t < t1; ++t) a.mask[t] = 0u;
+    for (int t = w0 + lane; t < w1; t += 32) a.mask[t] = 0u;
     if (tid == 0) {
         LoopCtl c;
         c.live = total;
