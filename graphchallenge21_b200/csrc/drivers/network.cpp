@@ -4,6 +4,7 @@
 // directory), runs the layer loop on GPU 0 through the C ABI and prints the reference's progress lines
 // ("layer l, batch = k", "Kernel Exec Time [...]", all_network.cu:508, 522-523).  In addition it writes the
 // category list the reference never emitted: neuron{N}-l{L}-categories.tsv, one 1-based image number per line.
+#include <algorithm>
 #include <cstdio>
 #include <iostream>
 #include <vector>
@@ -65,6 +66,20 @@ int main(int argc, char *argv[]) {
         fclose(f);
     }
     std::cout << "categories = " << count << " -> " << out << std::endl;
+    {
+        // the challenge's truth categories, when they were downloaded next to the data
+        // (tools/get_dataset.sh:15): 1-based image numbers, one per line
+        const std::string truth = drivers::data_dir() + "/neuron" + std::to_string(neuron) + "-l" + std::to_string(layer) + "-categories.tsv";
+        if (FILE *f = fopen(truth.c_str(), "r")) {
+            std::vector<int32_t> want;
+            double x;
+            while (fscanf(f, "%lf", &x) == 1)
+                if ((int)x <= batch) want.push_back((int32_t)x - 1);
+            fclose(f);
+            const bool same = (int)want.size() == count && std::equal(want.begin(), want.end(), cats.begin());
+            std::cout << "Challenge " << (same ? "PASSED" : "FAILED") << ": " << count << " categories, truth " << want.size() << std::endl;
+        }
+    }
     spdnn_destroy(ctx);
     std::cout << "[END]..." << std::endl;
     return 0;

@@ -804,7 +804,9 @@ int spdnn_sync(spdnn_t *c, spdnn_stats_t *stats) {
         if (st != 0) {
             cudaMemsetAsync(c->status, 0, sizeof(int32_t), c->stream);
             return fail(c, SPDNN_ERR_DEVICE, "device-side check failed (code %d: %s)", st,
-                        st == 3 ? "input triplet out of range" : "survivor count inconsistent");
+                        st == 3 ? "input triplet out of range"
+                                : st == 4 ? "a table copy into shared memory did not complete within the wait limit"
+                                          : "survivor count inconsistent");
         }
         spdnn_stats_t s{};
         s.layers = c->layers; s.batch = c->batch;

@@ -119,3 +119,22 @@ def read_input_bin(path: str, batch: int | None = None):
         keep = img <= batch
         img, neuron, val = img[keep], neuron[keep], val[keep]
     return img, neuron, val
+
+
+def truth_file_name(data_dir: str, neurons: int, layers: int) -> str:
+    """The challenge's truth file for a network, next to the data (tools/get_dataset.sh:15)."""
+    return os.path.join(data_dir, f"neuron{neurons}-l{layers}-categories.tsv")
+
+
+def compare_categories(ids_zero_based, truth_path: str, batch: int | None = None) -> dict:
+    """Compares a category list with a truth file (1-based image numbers, one per line; only
+    images <= batch count when the run used a truncated batch).  Returns the verdict and the
+    differences."""
+    truth = read_categories(truth_path)
+    if batch is not None:
+        truth = truth[truth < batch]
+    got = np.asarray(ids_zero_based, dtype=np.int64)
+    missing = np.setdiff1d(truth, got)
+    extra = np.setdiff1d(got, truth)
+    return {"passed": missing.size == 0 and extra.size == 0, "truth": int(truth.size), "got": int(got.size),
+            "missing": missing[:16].tolist(), "extra": extra[:16].tolist()}

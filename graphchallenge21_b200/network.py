@@ -11,6 +11,7 @@ image numbers that the reference does not perform.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import sys
 from dataclasses import dataclass
 
@@ -271,6 +272,10 @@ def run_network(neuron: int, batch: int, layer: int, data_dir: str = "../data", 
         cats = net.categories().copy()
     if categories_path:
         formats.write_categories(categories_path, cats)
+    truth = formats.truth_file_name(data_dir, neuron, layer)
+    if os.path.exists(truth):                     # the challenge's truth categories, when they were downloaded
+        v = formats.compare_categories(cats, truth, batch)
+        say(f"Challenge {'PASSED' if v['passed'] else 'FAILED'}: {v['got']} categories, truth {v['truth']}")
     say("[END]...")
     return cats
 

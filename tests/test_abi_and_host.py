@@ -121,6 +121,10 @@ def test_formats_round_trip(tmp_path):
     assert np.array_equal(i3, img) and np.array_equal(n3, neu)
     formats.write_categories(str(tmp_path / "c.tsv"), np.array([0, 5, 9]))
     assert formats.read_categories(str(tmp_path / "c.tsv")).tolist() == [0, 5, 9]
+    assert formats.compare_categories([0, 5, 9], str(tmp_path / "c.tsv"))["passed"]
+    v = formats.compare_categories([0, 9, 11], str(tmp_path / "c.tsv"))
+    assert not v["passed"] and v["missing"] == [5] and v["extra"] == [11]
+    assert formats.compare_categories([0, 5], str(tmp_path / "c.tsv"), batch=6)["passed"]
 
 
 def test_shard_bounds_cover_batch():

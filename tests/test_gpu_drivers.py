@@ -48,6 +48,12 @@ def test_network_driver(data, tmp_path):
     assert got == live.tolist()
     assert "[BEGIN]..." in out and "[END]..." in out and "Kernel Exec Time [20-uiuc-row-succ] = " in out
     assert np.array_equal(formats.read_categories(str(tmp_path / f"neuron{N}-l{L}-categories.tsv")), cats)
+    assert "Challenge" not in out                       # no truth file next to the data yet
+    formats.write_categories(formats.truth_file_name(d, N, L), cats)
+    assert f"Challenge PASSED: {len(cats)} categories" in run("network", [N, B, L], d, str(tmp_path))
+    formats.write_categories(formats.truth_file_name(d, N, L), cats[1:])
+    assert "Challenge FAILED" in run("network", [N, B, L], d, str(tmp_path))
+    os.remove(formats.truth_file_name(d, N, L))
     assert "Usage: exe neuron batch layer" in run("network", [N, B], d, str(tmp_path))
     # the batch argument truncates the input file like the reference's reader
     out = run("network", [N, 100, L], d, str(tmp_path))
