@@ -158,22 +158,34 @@ __device__ __forceinline__ void rebuild_worklist(const LayerArgs &a, int live_in
     if (total > live_in && tid == 0) atomicExch(a.status, 2);
     const bool same = (total == live_in);      // nobody died: positions are already dense
     if (!same) {
-        const int32_t *ids_old = ids_buf ? a.ids1 : a.ids0;
-        int32_t *ids_new = ids_buf ? a.ids0 : a.ids1;
+        const int32_t *__restrict__ ids_old = ids_buf ? a.ids1 : a.ids0;
+        int32_t *__restrict__ ids_new = ids_buf ? a.ids0 : a.ids1;
         int run = warp ? s_warp[warp - 1] : 0;         // first position of this warp's run
         const uint32_t below = (1u << lane) - 1u;
+        int32_t *__restrict__ slot = a.slot;
         for (int tb = w0; tb < w1; tb += 32) {
             const uint32_t mine = (tb + lane < w1) ? __ldcg(a.mask + tb + lane) : 0u;    // 32 ballots per load
             const int n = min(32, w1 - tb);
-            for (int i = 0; i < n; ++i) {
-                const uint32_t m = __shfl_sync(0xffffffffu, mine, i);
-                if ((m >> lane) & 1u) {
-                    const int pos = (tb + i) * 32 + lane;
-                    const int dst = run + __popc(m & below);
-                    a.slot[dst] = pos;
-                    ids_new[dst] = ids_old[pos];
+            // eight tiles at a time: their old ids are fetched together (the id array read here was
+            // written by an earlier launch), then stored, so the loads do not wait for one another
+            for (int i = 0; i < n; i += 8) {
+                int dst[8], idv[8];
+                bool on[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    uint32_t m = __shfl_sync(0xffffffffu, mine, (i + u) & 31);
+                    if (i + u >= n) m = 0u;
+                    on[u] = (m >> lane) & 1u;
+                    dst[u] = run + __popc(m & below);
+                    run += __popc(m);
+                    idv[u] = on[u] ? __ldg(ids_old + (tb + i + u) * 32 + lane) : 0;
                 }
-                run += __popc(m);
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (on[u]) {
+                        slot[dst[u]] = (tb + i + u) * 32 + lane;
+                        ids_new[dst[u]] = idv[u];
+                    }
             }
         }
     }
