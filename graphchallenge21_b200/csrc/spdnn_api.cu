@@ -493,6 +493,9 @@ int enqueue_layers(spdnn *c) {
         }
     }
     c->nsteps = (int)plan.size();
+    finalize_ids_kernel<<<std::max(1, std::min(c->tiles_cap, 4 * c->sm_count)), 256, 0, c->stream>>>(c->ctl + c->nsteps, c->slot,
+                                                                                             c->ids[0], c->ids[1]);
+    CK(cudaGetLastError());
     return SPDNN_OK;
 }
 
@@ -831,7 +834,7 @@ int spdnn_sync(spdnn_t *c, spdnn_stats_t *stats) {
             bytes += 4.0 * (c->n + 1) + 8.0 * (double)c->layer[l]->nnz;
         }
         s.algorithmic_bytes = bytes;
-        s.kernel_launches = c->nsteps + c->prep_launches;
+        s.kernel_launches = c->nsteps + 1 + c->prep_launches;      // + finalize_ids_kernel
         s.loop_launches = c->nsteps;
         s.resident_group = c->last_group;
         c->stats = s;

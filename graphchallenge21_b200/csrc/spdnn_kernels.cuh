@@ -127,8 +127,10 @@ __device__ __forceinline__ float class_sum(const LayerDesc &d, int u, const floa
 // The last block to finish turns the per-tile ballots into the next launch's work list: every
 // warp takes a contiguous run of tiles, counts its survivors (lanes split the run, warp scan),
 // a block scan over the warps gives each run its first position, and the warp then walks its
-// tiles 32 at a time with lane b handling bit b, so that the reads of the old ids and the
-// writes of the new work list and ids are coalesced and independent from tile to tile.
+// tiles 32 at a time with lane b handling bit b, so that the writes of the work list are
+// coalesced.  The global image numbers follow later and in parallel: when the order changed
+// (ids_buf flips) the blocks of the NEXT launch copy ids[ids_buf ^ 1][slot[j]] to ids[ids_buf][j]
+// for the images they own (move_id), and finalize_ids_kernel does it after the last launch.
 __device__ __forceinline__ void rebuild_worklist(const LayerArgs &a, int live_in, int ids_buf) {
     __shared__ int s_warp[32];          // works for any block size up to 1024 threads
     __shared__ int s_total;
@@ -158,34 +160,16 @@ __device__ __forceinline__ void rebuild_worklist(const LayerArgs &a, int live_in
     if (total > live_in && tid == 0) atomicExch(a.status, 2);
     const bool same = (total == live_in);      // nobody died: positions are already dense
     if (!same) {
-        const int32_t *__restrict__ ids_old = ids_buf ? a.ids1 : a.ids0;
-        int32_t *__restrict__ ids_new = ids_buf ? a.ids0 : a.ids1;
         int run = warp ? s_warp[warp - 1] : 0;         // first position of this warp's run
         const uint32_t below = (1u << lane) - 1u;
         int32_t *__restrict__ slot = a.slot;
         for (int tb = w0; tb < w1; tb += 32) {
             const uint32_t mine = (tb + lane < w1) ? __ldcg(a.mask + tb + lane) : 0u;    // 32 ballots per load
             const int n = min(32, w1 - tb);
-            // eight tiles at a time: their old ids are fetched together (the id array read here was
-            // written by an earlier launch), then stored, so the loads do not wait for one another
-            for (int i = 0; i < n; i += 8) {
-                int dst[8], idv[8];
-                bool on[8];
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    uint32_t m = __shfl_sync(0xffffffffu, mine, (i + u) & 31);
-                    if (i + u >= n) m = 0u;
-                    on[u] = (m >> lane) & 1u;
-                    dst[u] = run + __popc(m & below);
-                    run += __popc(m);
-                    idv[u] = on[u] ? __ldg(ids_old + (tb + i + u) * 32 + lane) : 0;
-                }
-#pragma unroll
-                for (int u = 0; u < 8; ++u)
-                    if (on[u]) {
-                        slot[dst[u]] = (tb + i + u) * 32 + lane;
-                        ids_new[dst[u]] = idv[u];
-                    }
+            for (int i = 0; i < n; ++i) {
+                const uint32_t m = __shfl_sync(0xffffffffu, mine, i);
+                if ((m >> lane) & 1u) slot[run + __popc(m & below)] = (tb + i) * 32 + lane;
+                run += __popc(m);
             }
         }
     }
@@ -201,6 +185,13 @@ __device__ __forceinline__ void rebuild_worklist(const LayerArgs &a, int live_in
         *a.work = 0u;
         if (a.died_at) *a.died_at = live_in - total;
     }
+}
+
+// The consumer's half of the id bookkeeping: image j of the new order came from position src.
+__device__ __forceinline__ void move_id(const LoopCtl &ctl, int32_t *ids0, int32_t *ids1, int j, int src) {
+    int32_t *to = ctl.ids_buf ? ids1 : ids0;
+    const int32_t *from = ctl.ids_buf ? ids0 : ids1;
+    to[j] = __ldg(from + src);
 }
 
 // One layer.  Grid: persistent blocks that draw work items (tile, block of classes) from an
@@ -236,6 +227,7 @@ __global__ void __launch_bounds__(kThreads, SPDNN_MIN_BLOCKS) layer_kernel(const
         const bool valid = j < live_in;
         const int jj = valid ? j : tile * 32;               // padding lanes shadow lane 0 and are masked out
         const int src = ctl.identity ? jj : __ldg(a.slot + jj);
+        if (!ctl.identity && cb == 0 && warp == 0 && valid) move_id(ctl, a.ids0, a.ids1, j, src);
         const float *__restrict__ yin = a.yin + (size_t)(src >> 5) * a.tile_stride + (src & 31);
         float *__restrict__ yout = a.yout + (size_t)tile * a.tile_stride + lane;
         bool any = false;
@@ -336,6 +328,14 @@ static __global__ void tiles_to_dense_kernel(const float *__restrict__ y, long l
         const int img = j0 + r, col = c0 + threadIdx.x;
         if (img < c.live && col < n) out[(size_t)(img - j_base) * n + col] = t[threadIdx.x][r];
     }
+}
+
+// After the last launch: the ids of the final order, if that launch changed the order.
+static __global__ void finalize_ids_kernel(const LoopCtl *ctl, const int32_t *__restrict__ slot, int32_t *ids0, int32_t *ids1) {
+    const LoopCtl c = *ctl;
+    if (c.identity) return;
+    for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < c.live; j += gridDim.x * blockDim.x)
+        move_id(c, ids0, ids1, j, __ldg(slot + j));
 }
 
 static __global__ void init_loop_kernel(LoopCtl *ctl, int32_t *ids0, int batch, int first_global_id, int32_t *died_at,

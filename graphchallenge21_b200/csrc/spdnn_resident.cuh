@@ -308,6 +308,7 @@ resident_kernel(const ResArgs a) {
                 my_valid |= (v ? 1u : 0u) << q;
                 const int jj = v ? j : j0;
                 const int src = ctl.identity ? jj : __ldg(a.slot + jj);
+                if (!ctl.identity && grp == 0 && v) move_id(ctl, a.ids0, a.ids1, j, src);
                 p[q] = a.yin + (size_t)(src >> 5) * a.tile_stride + (src & 31);
             }
             if (my_valid != kFull) contiguous = false;
