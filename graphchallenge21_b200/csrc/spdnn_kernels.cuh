@@ -66,6 +66,43 @@ struct LayerArgs {
     float bias, clip;
 };
 
+// L2 residency hints of the per-layer kernel (SPDNN_L2_HINT: 0 none, 1 input rows are read
+// with an evict-first policy, 2 output rows are also written with evict-last).  The input of
+// a layer is dead once read and its output is the next layer's input, so when both together
+// exceed the L2 but the output alone fits, keeping the output and letting go of the input
+// turns the next layer's DRAM reads into L2 hits.
+#ifndef SPDNN_L2_HINT
+#define SPDNN_L2_HINT 0
+#endif
+__device__ __forceinline__ unsigned long long l2_policy_evict_first() {
+    unsigned long long pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ unsigned long long l2_policy_evict_last() {
+    unsigned long long pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ float load_row(const float *p, unsigned long long pol) {
+#if SPDNN_L2_HINT >= 1
+    float v;
+    asm volatile("ld.global.nc.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(v) : "l"(p), "l"(pol));
+    return v;
+#else
+    (void)pol;
+    return __ldg(p);
+#endif
+}
+__device__ __forceinline__ void store_row(float *p, float v, unsigned long long pol) {
+#if SPDNN_L2_HINT >= 2
+    asm volatile("st.global.L2::cache_hint.f32 [%0], %1, %2;" ::"l"(p), "f"(v), "l"(pol) : "memory");
+#else
+    (void)pol;
+    *p = v;
+#endif
+}
+
 __device__ __forceinline__ float relu_clip(float x, float clip) {
     // x<0 ? 0 : x>clip ? clip : x   (all_network.cu:8-10)
     return x < 0.0f ? 0.0f : (x > clip ? clip : x);
@@ -74,7 +111,7 @@ __device__ __forceinline__ float relu_clip(float x, float clip) {
 // Sum of one class for this lane's image: the K inputs in ascending input order, one fp32
 // add after the other, starting from 0 -- the order of src/utils/cpu_spmm.h:14-43.
 template <int KT, bool UNIFORM>
-__device__ __forceinline__ float class_sum(const LayerDesc &d, int u, const float *__restrict__ yin) {
+__device__ __forceinline__ float class_sum(const LayerDesc &d, int u, const float *__restrict__ yin, unsigned long long pol = 0) {
     float acc = 0.0f;
     if (KT > 0) {
         constexpr int KA = KT > 0 ? KT : 4;      // array extent (the branch is dead for KT == 0)
@@ -87,7 +124,7 @@ __device__ __forceinline__ float class_sum(const LayerDesc &d, int u, const floa
         }
         float v[KA];
 #pragma unroll
-        for (int i = 0; i < KT; ++i) v[i] = __ldg(yin + o[i]);
+        for (int i = 0; i < KT; ++i) v[i] = load_row(yin + o[i], pol);
         if (UNIFORM) {
 #pragma unroll
             for (int i = 0; i < KT; ++i) acc = __fadd_rn(acc, v[i]);
@@ -108,7 +145,7 @@ __device__ __forceinline__ float class_sum(const LayerDesc &d, int u, const floa
         const float4 *w4 = UNIFORM ? nullptr : reinterpret_cast<const float4 *>(d.vals + (size_t)u * k);
         for (int i = 0; i < k / 4; ++i) {
             const int4 t = __ldg(o4 + i);
-            const float a = __ldg(yin + t.x), b = __ldg(yin + t.y), c = __ldg(yin + t.z), e = __ldg(yin + t.w);
+            const float a = load_row(yin + t.x, pol), b = load_row(yin + t.y, pol), c = load_row(yin + t.z, pol), e = load_row(yin + t.w, pol);
             if (UNIFORM) {
                 acc = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(acc, a), b), c), e);
             } else {
@@ -212,6 +249,8 @@ __global__ void __launch_bounds__(kThreads, SPDNN_MIN_BLOCKS) layer_kernel(const
     const int ncb = (d.classes + cpi - 1) / cpi;
     const unsigned int items = (unsigned int)ntiles * (unsigned int)ncb;
     const int per_warp = (cpi + kWarps - 1) / kWarps;
+    const unsigned long long pol_in = SPDNN_L2_HINT >= 1 ? l2_policy_evict_first() : 0ull;
+    const unsigned long long pol_out = SPDNN_L2_HINT >= 2 ? l2_policy_evict_last() : 0ull;
 
     for (;;) {
         if (tid == 0) {
@@ -243,14 +282,14 @@ __global__ void __launch_bounds__(kThreads, SPDNN_MIN_BLOCKS) layer_kernel(const
                 me = __ldg(d.mem_ptr + u + 1);
                 mreg = (mb + lane < me) ? __ldg(d.mem + mb + lane) : 0;
             }
-            const float s = class_sum<KT, UNIFORM>(d, u, yin);
+            const float s = class_sum<KT, UNIFORM>(d, u, yin, pol_in);
             const float y = relu_clip(__fadd_rn(s, a.bias), a.clip);
             any |= (y != 0.0f);
             const int cnt = a.first_member_only ? 1 : me - mb;
             if (cnt <= 32) {
-                for (int m = 0; m < cnt; ++m) yout[__shfl_sync(0xffffffffu, mreg, m)] = y;
+                for (int m = 0; m < cnt; ++m) store_row(yout + __shfl_sync(0xffffffffu, mreg, m), y, pol_out);
             } else {
-                for (int m = mb; m < me; ++m) yout[__ldg(d.mem + m)] = y;
+                for (int m = mb; m < me; ++m) store_row(yout + __ldg(d.mem + m), y, pol_out);
             }
         }
         const unsigned int m = __ballot_sync(0xffffffffu, any && valid);
