@@ -177,10 +177,9 @@ int begin_input(spdnn *c, int batch, int first_global_id) {
     if (batch < 0) return fail(c, SPDNN_ERR_ARG, "batch must be >= 0");
     if ((long long)first_global_id + batch > 0x7fffffffLL || first_global_id < 0)
         return fail(c, SPDNN_ERR_ARG, "global image numbers must fit in int32");
-    if (c->in_flight) {
-        int rc = spdnn_sync(c, nullptr);
-        if (rc) return rc;
-    }
+    // A pass still in flight is not waited for: the new input is ordered behind it on the stream
+    // and its results, which nobody fetched, are dropped.
+    c->in_flight = false;
     int rc = ensure_capacity(c, batch > 0 ? batch : 1);
     if (rc) return rc;
     c->batch = batch;

@@ -99,7 +99,9 @@ int spdnn_set_input_coo(spdnn_t *ctx, int64_t nnz, const int32_t *img, const int
 int spdnn_infer(spdnn_t *ctx, spdnn_stats_t *stats);
 
 /* Asynchronous form: enqueue on the context's stream and return; spdnn_sync waits and
- * fills the statistics. */
+ * fills the statistics.  A set_input call made while a pass is in flight does not wait: the
+ * new input is ordered behind that pass on the stream and the pass's unfetched results are
+ * dropped, so passes can be queued back to back and only the last one synchronised. */
 int spdnn_infer_async(spdnn_t *ctx);
 int spdnn_sync(spdnn_t *ctx, spdnn_stats_t *stats);
 

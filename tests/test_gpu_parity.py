@@ -197,6 +197,12 @@ def test_infer_is_repeatable_and_input_is_consumed():
             g.infer()
             outs.append((g.categories().copy(), g.activations()))
         assert all(np.array_equal(outs[0][0], o[0]) and np.array_equal(outs[0][1], o[1]) for o in outs)
+        # passes queued back to back without waiting in between: the last one's results are what is fetched
+        for k in range(3):
+            g.set_input_dense(y0[: b - 100 * (2 - k)])
+            g.infer_async()
+        res = g.sync()
+        assert res.batch == b and np.array_equal(g.categories(), outs[0][0]) and np.array_equal(g.activations(), outs[0][1])
         with pytest.raises(SpDNNError) as e:
             g.infer()
         assert e.value.code == -4
