@@ -258,7 +258,7 @@ struct ResidentTables {
     // numbers of the shared-memory buffers:
     //   RES_GENERIC: int32 t[U][k + 4]: the k input rows in summation order, then {output row, 0, 0, 0};
     //                followed, when the weights are not uniform, by float vals[U][k + 4]
-    //   RES_ALT2:    int32 t[U][4] = {row a, row b, output row, 0}: the sum is a+b+a+b+... (k terms)
+    //   RES_ALT2:    int32 t[U][4] = {row a, row b, output row, 0 (filled on the device: truth table)}: the sum is a+b+a+b+... (k terms)
     std::vector<int32_t> blob;
     std::vector<int32_t> rep;       // [v_in] neuron * 32 holding value id v (empty: value id == neuron)
     std::vector<int32_t> mem_ptr;   // [U+1] member ranges (empty: class u == column u)

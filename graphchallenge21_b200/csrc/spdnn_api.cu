@@ -86,6 +86,7 @@ struct spdnn {
     bool resident = true;              // use the shared-memory-resident kernel where a chunk fits
     bool reps_only = true;             // SPDNN_REPS_ONLY=0: every launch writes all N rows
     bool exact_shortcut = true;        // SPDNN_EXACT_SHORTCUT=0 disables the exact-sum shortcut of the ALT2 form
+    bool bit_form = true;              // SPDNN_BIT_FORM=0 disables the bit form of saturated activations (ALT2)
     bool print_schedule = false;       // SPDNN_PRINT_SCHEDULE=1: one line per launch when the graph is built
     bool resident_always = false;      // ... even for a lone layer that the per-layer kernel would serve better
     int res_ti_max = 32;               // largest group of images per block to try
@@ -332,6 +333,11 @@ int prepare_resident(spdnn *c) {
             if (!rc) rc = upload_vec(c, &R->mem_ptr, t.mem_ptr);
             if (!rc) rc = upload_vec(c, &R->mem, t.mem);
             if (rc) return rc;
+            if (t.mode == RES_ALT2) {
+                // the four saturated outputs of every class, evaluated by the device's own arithmetic
+                alt2_truth_kernel<<<std::max(1, std::min(64, (t.classes + 255) / 256)), 256, 0, c->stream>>>(R->blob, c->bias, c->clip);
+                CK(cudaGetLastError());
+            }
             CK(cudaStreamSynchronize(c->stream));
             R->class_of.swap(t.class_of);
             R->partition_hash = t.partition_hash;
@@ -359,6 +365,12 @@ int prepare_resident(spdnn *c) {
 // Rows one activation buffer needs for layer l inside a resident chunk.
 inline int resident_rows(const DevRes &R) { return ((std::max(R.v_in, R.classes) + 1) & ~1) + 2; }
 
+// Dynamic shared memory of a resident block: two activation buffers, two staged tables, two
+// buffers of one word per row for the bit form.
+inline size_t resident_smem_bytes(int ti, int rows, int table) {
+    return 2 * (size_t)rows * ti * 4 + 2 * (size_t)table + 2 * (size_t)rows * 4;
+}
+
 // Enqueues the whole network: chunks of layers through the resident kernel where a group of
 // images fits in shared memory (chunk lengths chunk_first, x2, ... up to chunk_max: short while
 // images still die, long once the survivors are stable), one launch per layer otherwise.
@@ -379,7 +391,7 @@ std::vector<Step> plan_steps(spdnn *c) {
             const DevRes &R0 = *c->res[l];
             const bool k32 = (R0.k == 32);
             auto fits = [&](int t_i, int r, int table) {
-                return 2 * (size_t)r * t_i * 4 + 2 * (size_t)table + 2048 <= (size_t)c->smem_optin;
+                return resident_smem_bytes(t_i, r, table) + 2048 <= (size_t)c->smem_optin;
             };
             int rows = resident_rows(R0), ti = 0, ipt = 4;
             // (images per block, images per thread) in order of preference; a form that would leave
@@ -451,7 +463,8 @@ int enqueue_layers(spdnn *c) {
             a.reps_only = next_resident ? 1 : 0;
             a.exact_ok = (l > 0 && c->clip <= 1024.0f && c->exact_shortcut) ? 1 : 0;
             const int grid = std::max(1, (c->tiles_cap * 32 + st.ti - 1) / st.ti);
-            const size_t smem = 2 * (size_t)st.rows * st.ti * 4 + 2 * (size_t)st.table;
+            const size_t smem = resident_smem_bytes(st.ti, st.rows, st.table);
+            a.bit_ok = (R0.mode == kResAlt2 && c->bit_form && c->clip > 0.0f) ? 1 : 0;
             int rc = launch_resident(c, st.ti, st.ipt, a, grid, smem, R0.mode, R0.k == 32, R0.uniform);
             if (rc) return rc;
             c->last_group = st.ti;
@@ -579,6 +592,7 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
         if (const char *e = getenv("SPDNN_STAGE_TABLES")) c->stage_tables = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_PRINT_SCHEDULE")) c->print_schedule = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_EXACT_SHORTCUT")) c->exact_shortcut = atoi(e) != 0;
+        if (const char *e = getenv("SPDNN_BIT_FORM")) c->bit_form = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_REPS_ONLY")) c->reps_only = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_CHUNK_FIRST")) c->chunk_first = std::max(1, atoi(e));
         if (const char *e = getenv("SPDNN_CHUNK_MAX")) c->chunk_max = std::max(1, atoi(e));

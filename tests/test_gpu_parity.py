@@ -16,9 +16,9 @@ GOLDEN = sorted(glob.glob(os.path.join(ROOT, "tests", "golden", "*.npz")))
 REL_TOL = 1e-5        # stated tolerance for activations; the tests below get 0 (bit-exact)
 
 
-def run_gpu(net, y0, first=0, how="dense", layers=None, vals=None):
+def run_gpu(net, y0, first=0, how="dense", layers=None, vals=None, clip=32.0):
     n, L = net.neurons, (net.layers if layers is None else layers)
-    with SpDNN(n, L, float(net.bias)) as g:
+    with SpDNN(n, L, float(net.bias), clip=clip) as g:
         for l in range(L):
             if vals is None:
                 g.set_layer_csc(l, *net.layer_csc(l))
@@ -75,6 +75,7 @@ def test_against_oracle(pattern, n, L, b, oracle):
 @pytest.mark.parametrize("env", [{"SPDNN_RESIDENT": "0"}, {"SPDNN_RESIDENT_TI": "8"}, {"SPDNN_RESIDENT_TI": "4"},
                                  {"SPDNN_CHUNK_FIRST": "1", "SPDNN_CHUNK_MAX": "3"}, {"SPDNN_CHUNK_FIRST": "64"},
                                  {"SPDNN_STAGE_TABLES": "0"}, {"SPDNN_EXACT_SHORTCUT": "0"}, {"SPDNN_RESIDENT_IPT": "4"},
+                                 {"SPDNN_BIT_FORM": "0"},
                                  {"SPDNN_RESIDENT_TI": "16"}, {"SPDNN_REPS_ONLY": "0"}])
 def test_kernel_paths_agree(env, monkeypatch, oracle):
     """The per-layer kernel, and the shared-memory-resident kernel at every group size and chunk
@@ -86,6 +87,32 @@ def test_kernel_paths_agree(env, monkeypatch, oracle):
         y0 = synthetic_images(n, b) if pattern == "radix16" else mixed_density_images(n, b)
         want = oracle.infer(y0, [(r, None) for r in rows_of(net)], float(net.bias), first_image=7)
         check(run_gpu(net, y0, first=7), want)
+
+
+_BIT_FORM_WANT = {}
+
+
+@pytest.mark.parametrize("env", [{}, {"SPDNN_BIT_FORM": "0"}, {"SPDNN_CHUNK_FIRST": "1", "SPDNN_CHUNK_MAX": "3"},
+                                 {"SPDNN_RESIDENT_TI": "8"}, {"SPDNN_STAGE_TABLES": "0"}, {"SPDNN_RESIDENT_IPT": "4"}])
+@pytest.mark.parametrize("bias,clip", [(-0.3, 32.0), (0.0, 32.0), (-32.0, 32.0), (0.01, 32.0), (-0.3, 8.0), (-1.0, 2.5)])
+def test_bit_form_of_saturated_activations(bias, clip, env, monkeypatch, oracle):
+    """Blocks whose activations are all exactly 0 or clip continue as one word per row and come
+    back to floats in the layer where an output is not saturated; the bits are those of the
+    float form for every bias and clip.  The batch holds runs of images that are saturated from
+    the start (so whole blocks start a chunk in the bit form), images scaled off the 1/16 grid,
+    all-clip images and ordinary ones."""
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    n, L, b = 1024, 70, 640
+    net = SyntheticNetwork(n, L, "radix16", bias=bias)
+    y0 = synthetic_images(n, b)
+    y0[128:320] *= np.float32(clip)
+    y0[320:400:3] *= np.float32(0.37 * clip)
+    y0[400:440] = np.float32(clip)
+    key = (bias, clip)
+    if key not in _BIT_FORM_WANT:
+        _BIT_FORM_WANT[key] = oracle.infer(y0, [(r, None) for r in rows_of(net)], bias, clip=clip)
+    check(run_gpu(net, y0, clip=clip), _BIT_FORM_WANT[key])
 
 
 def test_positive_bias_all_zero_inputs_stay_alive(oracle):
