@@ -1,0 +1,478 @@
+// alt2_kernel: the resident kernel for chunks of layers in the ALT2 table form (every class adds
+// the two rows a, b alternately: a+b+a+b+..., K terms -- a 16-wide butterfly block in value ids).
+//
+// It differs from resident_kernel (spdnn_resident.cuh), whose structure it shares -- one block
+// owns TI images for all layers of the chunk, two activation buffers of one row per value id
+// ping-pong in shared memory, dead images are dropped between launches -- in two ways.
+//
+// 1. Packed table stream.  The tables of a chunk are one contiguous array in global memory,
+//    `stride` bytes per layer: a 16-byte header {classes, K, bits of w, 0}, then per pass of 64
+//    classes 32 slots of 16 bytes; slot `lane` holds the entries of classes 64p + lane and
+//    64p + 32 + lane, 8 bytes each: {4 * row a | (4 * row b) << 16, truth table}.  The output row of
+//    class u is resident_phys_row(u) and is not stored.  One bulk asynchronous copy (TMA) brings a
+//    GROUP of up to 8 layers into shared memory, several groups ahead of the layer being computed.
+//
+// 2. Bit form of saturated activations.  Once every activation of a block's images is exactly 0
+//    or exactly clip (the steady state of the challenge networks), a row of the block is one
+//    32-bit word (bit i = image i holds clip) and a class is a boolean function of two words: its
+//    output for the four combinations (a, b) in {0, clip}^2 is a property of the class, not of the
+//    image.  alt2_pack_kernel evaluates those four outputs once per class with the same fp32 code
+//    as the float form (class_sum_alt2 + finish_output) and stores them as the truth table:
+//      bit q      (q = [a == clip] + 2 [b == clip])  output == clip
+//      bit 4 + q                                    output is neither 0 nor clip
+//    The kernel then applies a layer to all images of a block with a few logic instructions per
+//    class.  It does so a group of layers at a time, writing every layer's words to the next
+//    buffer of a small ring and checking only at the end of the group that no image met a
+//    combination whose output is not saturated and that no image died; if one did, the group is
+//    repeated from its first buffer (still intact) one layer at a time, so that the layer of a
+//    death is counted exactly and the layer with the unsaturated output is computed in the float
+//    form.  The results are therefore those of the float form, bit for bit, whatever the inputs.
+#pragma once
+
+#include "spdnn_resident.cuh"
+
+namespace spdnn_impl {
+
+// Bytes per layer of a packed stream whose largest layer has max_classes classes.
+__host__ __device__ __forceinline__ int alt2_stream_stride(int max_classes) { return 16 + ((max_classes + 63) / 64) * 512; }
+
+// Byte offset of class u's entry inside a layer's record.
+__host__ __device__ __forceinline__ int alt2_entry_offset(int u) {
+    return 16 + (u >> 6) * 512 + (u & 31) * 16 + ((u >> 5) & 1) * 8;
+}
+
+// Builds the packed stream of a chunk from the per-layer blobs (ALT2: int32 t[U][4] = {row a,
+// row b, output row, 0} behind a 4-word header).  One block per layer.
+static __global__ void alt2_pack_kernel(const ResLayer *layers, int stride, unsigned char *out, float bias, float clip) {
+    const int32_t *blob = layers[blockIdx.x].blob;
+    const int classes = blob[0], k = blob[1];
+    const float w = __int_as_float(blob[2]);
+    unsigned char *rec = out + (size_t)blockIdx.x * stride;
+    if (threadIdx.x == 0) *reinterpret_cast<int4 *>(rec) = make_int4(classes, k, blob[2], 0);
+    const int slots = (stride - 16) / 8;
+    for (int u = threadIdx.x; u < slots; u += blockDim.x) {
+        uint2 e = make_uint2(0u, 0u);        // a class past the end: rows 0, truth table 0
+        if (u < classes) {
+            const float4 s = class_sum_alt2<0>(make_float4(0.0f, clip, 0.0f, clip), make_float4(0.0f, 0.0f, clip, clip), k, w, false);
+            const float y[4] = {finish_output(s.x, bias, clip), finish_output(s.y, bias, clip), finish_output(s.z, bias, clip),
+                                finish_output(s.w, bias, clip)};
+            unsigned int tt = 0u;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                if (y[q] == clip) tt |= 1u << q;
+                else if (y[q] != 0.0f) tt |= 16u << q;
+            }
+            e.x = (unsigned int)(blob[4 + 4 * u] * 4) | ((unsigned int)(blob[4 + 4 * u + 1] * 4) << 16);
+            e.y = tt;
+        }
+        *reinterpret_cast<uint2 *>(rec + alt2_entry_offset(u)) = e;
+    }
+}
+
+// Applies a two-input truth table (4 bits of tt, index = [a] + 2 [b]) to 32 images at once.
+__device__ __forceinline__ unsigned int apply_truth(unsigned int wa, unsigned int wb, unsigned int tt) {
+    int m0, m1, m2, m3;      // bit q of tt spread over a word: bfe.s32 of one bit sign-extends it
+    asm("bfe.s32 %0, %1, 0, 1;" : "=r"(m0) : "r"(tt));
+    asm("bfe.s32 %0, %1, 1, 1;" : "=r"(m1) : "r"(tt));
+    asm("bfe.s32 %0, %1, 2, 1;" : "=r"(m2) : "r"(tt));
+    asm("bfe.s32 %0, %1, 3, 1;" : "=r"(m3) : "r"(tt));
+    const unsigned int t0 = (wa & (unsigned int)m1) | (~wa & (unsigned int)m0);
+    const unsigned int t1 = (wa & (unsigned int)m3) | (~wa & (unsigned int)m2);
+    return (wb & t1) | (~wb & t0);
+}
+
+// resident_phys_row(64 p + q) for q < 64, given pq = resident_phys_row(q): the parity of the upper
+// bits splits into the parities of p and of q >> 1.
+__device__ __forceinline__ int alt2_out_row(int p, int pq) { return (p << 6) + (pq ^ (__popc((unsigned int)p) & 1)); }
+
+#ifndef SPDNN_ALT2_MIN_BLOCKS
+#define SPDNN_ALT2_MIN_BLOCKS 4      // blocks per SM asked of the compiler: <= 64 registers, no spills
+#endif
+constexpr int kAlt2MaxTableRing = 4;
+
+// Grid: one block per TI live images (launched for the worst case; surplus blocks only take
+// part in the last-block ticket).  Dynamic shared memory: two activation buffers of
+// buf_rows * TI * 4 bytes, then (STAGED) tring buffers of (stream_stride << tgroup_shift) bytes for
+// groups of layer records, then wring buffers of rows_w words for the bit form.
+// IPT = images per thread (4 or 8): with 8 a thread carries two float4 halves through every step.
+template <int TI, int IPT, int KT, bool STAGED>
+__global__ void __launch_bounds__(kThreads, SPDNN_ALT2_MIN_BLOCKS) alt2_kernel(const ResArgs a) {
+    constexpr int NT = kThreads;
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ unsigned int s_alive[3];          // float form: images alive after layer li % 3
+    __shared__ int s_ns[3];                      // float form: layer li % 3 produced an output that is neither 0 nor clip
+    __shared__ unsigned int s_grp[2][2];         // bit form, many warps: {unsaturated, last layer's outputs} of a group
+    __shared__ int s_x[4];                       // state handed from the bit form to the block
+    __shared__ int s_last, s_fail;
+    __shared__ __align__(8) unsigned long long s_bar[kAlt2MaxTableRing];
+    constexpr int NQ = IPT / 4;                  // float4 halves per thread
+    constexpr int LPC = TI / IPT;                // threads per class
+    constexpr int CPI = NT / LPC;                // classes per pass of the block
+    constexpr int RS = TI * 4;                   // bytes per row
+    constexpr int TB = IPT * 4;                  // bytes of a row one thread owns
+    constexpr unsigned int kFull = (IPT == 8) ? 0xFFu : 0xFu;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int sub = tid % LPC, grp = tid / LPC;
+    const LoopCtl ctl = *a.ctl_in;
+    const int live_in = ctl.live;
+    const int nblk = (live_in + TI - 1) / TI;
+    const int buf_bytes = a.buf_rows * RS;
+    const int stride = a.stream_stride;
+
+    if ((int)blockIdx.x < nblk) {
+        unsigned char *cur = smem, *nxt = smem + buf_bytes;
+        unsigned char *const tbl0 = smem + 2 * buf_bytes;
+        // Staged tables: group g = layers [g << gshift, (g + 1) << gshift) lives in buffer g & (tring - 1)
+        // and completes phase g / tring of that buffer's mbarrier.
+        const int gshift = a.tgroup_shift, gmask = (1 << gshift) - 1;
+        const int tring = STAGED ? a.tring : 0, tshift = tring == 4 ? 2 : 1;
+        const int group_bytes = stride << gshift;
+        const int ngroups = STAGED ? (a.nlayers + gmask) >> gshift : 0;
+        unsigned int *const wring0 = reinterpret_cast<unsigned int *>(tbl0 + (size_t)tring * group_bytes);
+        const bool use_bits = a.bit_ok != 0;
+        const int j0 = blockIdx.x * TI;
+        int next_group = 0;          // thread 0: the next group of tables to request
+        // Thread 0 requests the groups in order.  At the top of layer li every thread has left layer
+        // li - 1, so the buffers of all groups before li's are free: groups up to (li's group) + tring - 1
+        // may be on their way.
+        auto issue_groups = [&](int li) {
+            const int lim = min((li >> gshift) + tring, ngroups);
+            while (next_group < lim) {
+                const int l0 = next_group << gshift, cnt = min(1 << gshift, a.nlayers - l0);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                bulk_load_table(tbl0 + (size_t)(next_group & (tring - 1)) * group_bytes, a.stream + (size_t)l0 * stride,
+                                (unsigned int)(cnt * stride), &s_bar[next_group & (tring - 1)]);
+                ++next_group;
+            }
+        };
+        auto wait_table = [&](int l) -> bool {        // bounded
+            const int g = l >> gshift;
+            return mbar_wait(&s_bar[g & (tring - 1)], (unsigned int)((g >> tshift) & 1));
+        };
+        auto table_of = [&](int l) -> const unsigned char * {
+            return STAGED ? tbl0 + (size_t)((l >> gshift) & (tring - 1)) * group_bytes + (size_t)(l & gmask) * stride
+                          : a.stream + (size_t)l * stride;
+        };
+        if (tid == 0) {
+            s_alive[0] = 0u;
+            s_ns[0] = 0;
+            s_grp[0][0] = s_grp[0][1] = s_grp[1][0] = s_grp[1][1] = 0u;
+            s_fail = 0;
+            if (STAGED) {
+                for (int q = 0; q < tring; ++q) mbar_init(&s_bar[q], 1);
+                asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+                issue_groups(0);         // travels while the block's activations are read
+            }
+        }
+        // ---- load one row per value id of the block's images (dead images were dropped: read
+        //      through the work list)
+        unsigned int my_valid = 0;
+        bool load_ns = false;                    // a loaded value is neither 0 nor clip
+        {
+            const float *p[IPT];
+            bool contiguous = ctl.identity != 0;
+#pragma unroll
+            for (int q = 0; q < IPT; ++q) {
+                const int j = j0 + sub * IPT + q;
+                const bool v = j < live_in;
+                my_valid |= (v ? 1u : 0u) << q;
+                const int jj = v ? j : j0;
+                const int src = ctl.identity ? jj : __ldg(a.slot + jj);
+                if (!ctl.identity && grp == 0 && v) move_id(ctl, a.ids0, a.ids1, j, src);
+                p[q] = a.yin + (size_t)(src >> 5) * a.tile_stride + (src & 31);
+            }
+            if (my_valid != kFull) contiguous = false;
+            const ResLayer L0 = a.layers[0];
+            for (int v = grp; v < L0.v_in; v += CPI) {
+                const size_t e = L0.rep ? (size_t)__ldg(L0.rep + v) : (size_t)v * 32;
+                unsigned char *dst = cur + resident_phys_row(v) * RS + sub * TB;
+#pragma unroll
+                for (int h = 0; h < NQ; ++h) {
+                    float4 x;
+                    if (contiguous) {
+                        x = __ldg(reinterpret_cast<const float4 *>(p[0] + e) + h);
+                    } else {
+                        x.x = (my_valid >> (4 * h) & 1u) ? __ldg(p[4 * h + 0] + e) : 0.0f;
+                        x.y = (my_valid >> (4 * h) & 2u) ? __ldg(p[4 * h + 1] + e) : 0.0f;
+                        x.z = (my_valid >> (4 * h) & 4u) ? __ldg(p[4 * h + 2] + e) : 0.0f;
+                        x.w = (my_valid >> (4 * h) & 8u) ? __ldg(p[4 * h + 3] + e) : 0.0f;
+                    }
+                    *reinterpret_cast<float4 *>(dst + 16 * h) = x;
+                    load_ns |= (x.x != 0.0f && x.x != a.clip) || (x.y != 0.0f && x.y != a.clip) || (x.z != 0.0f && x.z != a.clip) ||
+                               (x.w != 0.0f && x.w != a.clip);
+                }
+            }
+        }
+        // LPC divides 32, so every warp holds all sub-columns: the OR over a warp is the block's
+        // mask of valid images (bit i = image j0 + i), identical in every thread
+        unsigned int alive_prev = __reduce_or_sync(0xffffffffu, my_valid << (sub * IPT));
+        const bool start_in_bits = !__syncthreads_or(load_ns ? 1 : 0) && use_bits;
+
+        // float rows -> one word per row (bit i = image i is non-zero; called when every value is 0 or clip)
+        auto rows_to_bits = [&](const unsigned char *buf, unsigned int *w) {
+            for (int r0 = 0; r0 < a.buf_rows; r0 += CPI) {
+                const int r = r0 + grp;
+                unsigned int m = 0;
+                if (r < a.buf_rows) {
+#pragma unroll
+                    for (int h = 0; h < NQ; ++h) {
+                        const float4 v = *reinterpret_cast<const float4 *>(buf + r * RS + sub * TB + 16 * h);
+                        m |= ((v.x != 0.0f ? 1u : 0u) | (v.y != 0.0f ? 2u : 0u) | (v.z != 0.0f ? 4u : 0u) | (v.w != 0.0f ? 8u : 0u)) << (4 * h);
+                    }
+                }
+                m <<= sub * IPT;
+#pragma unroll
+                for (int s = 1; s < LPC; s <<= 1) m |= __shfl_xor_sync(0xffffffffu, m, s);
+                if (sub == 0 && r < a.buf_rows) w[r] = m;
+            }
+        };
+        // ---- the layers of this chunk
+        int li = 0;                  // layers of the chunk applied so far
+        int last_classes = 0;
+        const bool force_dead = a.bias > 0.0f;
+        const bool multi = a.bit_multi != 0;     // layers of more than one pass of 64 classes: all warps work in the bit form
+        int ws = 0;                  // bit form: the word buffer that holds the current activations
+        bool bitmode = false;
+        if (start_in_bits) {
+            rows_to_bits(cur, wring0);
+            __syncthreads();
+            bitmode = true;
+        }
+        while (li < a.nlayers) {
+            if (bitmode) {
+                // ---- bit form.  Worker warps (warp 0 alone when a layer is one pass of 64 classes, else
+                //      all warps) apply groups of layers until the chunk ends, every image is dead, or a
+                //      layer yields an output that is neither 0 nor clip (redone in the float form).
+                if (multi || tid < 32) {
+                    unsigned int alive = alive_prev;
+                    int done_classes = last_classes;
+                    int careful = 0;             // layers still to be applied one at a time
+                    int par = 0;
+                    const int pq1 = resident_phys_row(lane), pq2 = resident_phys_row(lane + 32);
+                    const int p0 = multi ? warp : 0, pstep = multi ? NT / 32 : 1;
+                    while (li < a.nlayers) {
+                        if (STAGED) {
+                            if (tid == 0) issue_groups(li);
+                            const bool arrived = wait_table(li);
+                            // one verdict for all workers, so that they leave the loop together
+                            if (!(multi ? __syncthreads_and(arrived ? 1 : 0) != 0 : __all_sync(0xffffffffu, arrived))) {
+                                s_fail = 1;
+                                break;
+                            }
+                        }
+                        int cnt = min(a.wring - 1, a.nlayers - li);
+                        if (STAGED) cnt = min(cnt, (1 << gshift) - (li & gmask));
+                        if (careful > 0) cnt = 1;
+                        const unsigned char *T = table_of(li);
+                        const unsigned int keep = force_dead ? alive : 0xffffffffu;
+                        unsigned int ns = 0u, acc = 0u;
+                        int s = ws, classes = 0;
+                        for (int g = 0; g < cnt; ++g) {
+                            const unsigned char *wc = reinterpret_cast<const unsigned char *>(wring0 + (size_t)s * a.rows_w);
+                            s = (s + 1 == a.wring) ? 0 : s + 1;
+                            unsigned int *wn = wring0 + (size_t)s * a.rows_w;
+                            const unsigned char *Tg = T + (size_t)g * stride;
+                            classes = STAGED ? *reinterpret_cast<const int *>(Tg) : __ldg(reinterpret_cast<const int *>(Tg));
+                            const int passes = (classes + 63) >> 6;
+                            acc = 0u;
+                            for (int p = p0; p < passes; p += pstep) {
+                                const uint4 *slot = reinterpret_cast<const uint4 *>(Tg + 16 + p * 512) + lane;
+                                const uint4 e = STAGED ? *slot : __ldg(slot);
+                                const unsigned int a1 = *reinterpret_cast<const unsigned int *>(wc + (e.x & 0xffffu));
+                                const unsigned int b1 = *reinterpret_cast<const unsigned int *>(wc + (e.x >> 16));
+                                const unsigned int a2 = *reinterpret_cast<const unsigned int *>(wc + (e.z & 0xffffu));
+                                const unsigned int b2 = *reinterpret_cast<const unsigned int *>(wc + (e.z >> 16));
+                                const unsigned int o1 = apply_truth(a1, b1, e.y) & keep, o2 = apply_truth(a2, b2, e.w) & keep;
+                                ns |= (apply_truth(a1, b1, e.y >> 4) | apply_truth(a2, b2, e.w >> 4)) & keep;
+                                wn[alt2_out_row(p, pq1)] = o1;       // rows past the layer's classes get 0 (empty entries)
+                                wn[alt2_out_row(p, pq2)] = o2;
+                                acc |= o1 | o2;
+                            }
+                            if (multi) __syncthreads(); else __syncwarp();
+                        }
+                        // what the group did: an unsaturated output anywhere, and who is alive after it
+                        unsigned int ns_any = __reduce_or_sync(0xffffffffu, ns), now = __reduce_or_sync(0xffffffffu, acc);
+                        if (multi) {
+                            if (lane == 0) {
+                                if (ns_any) atomicOr(&s_grp[par][0], ns_any);
+                                if (now) atomicOr(&s_grp[par][1], now);
+                            }
+                            __syncthreads();
+                            ns_any = s_grp[par][0];
+                            now = s_grp[par][1];
+                            if (tid == 0) s_grp[par ^ 1][0] = s_grp[par ^ 1][1] = 0u;
+                            par ^= 1;
+                        }
+                        now &= alive;
+                        if (ns_any != 0u || (now != alive && cnt > 1)) {
+                            if (cnt == 1) break;         // layer li has an unsaturated output: the float form applies it
+                            careful = cnt;               // repeat the group from its first buffer, layer by layer
+                            continue;
+                        }
+                        if (now != alive && tid == 0) atomicAdd(a.died_at + li, __popc(alive & ~now));     // cnt == 1
+                        alive = now;
+                        ws = s;
+                        li += cnt;
+                        done_classes = classes;
+                        if (careful > 0) --careful;
+                        if (alive == 0u) break;
+                    }
+                    if (tid == 0) {
+                        s_x[0] = li; s_x[1] = (int)alive; s_x[2] = done_classes; s_x[3] = ws;
+                        s_alive[li % 3] = 0u;        // the float form may take over at layer li
+                        s_ns[li % 3] = 0;
+                    }
+                }
+                __syncthreads();
+                li = s_x[0];
+                alive_prev = (unsigned int)s_x[1];
+                last_classes = s_x[2];
+                ws = s_x[3];
+                // back to floats: the rows the next float layer (or the expansion below) reads
+                const unsigned int *wcur = wring0 + (size_t)ws * a.rows_w;
+                for (int r = grp; r < a.buf_rows; r += CPI) {
+                    const unsigned int wv = wcur[r] >> (sub * IPT);
+#pragma unroll
+                    for (int h = 0; h < NQ; ++h) {
+                        const unsigned int q = wv >> (4 * h);
+                        *reinterpret_cast<float4 *>(cur + r * RS + sub * TB + 16 * h) =
+                            make_float4((q & 1u) ? a.clip : 0.0f, (q & 2u) ? a.clip : 0.0f, (q & 4u) ? a.clip : 0.0f, (q & 8u) ? a.clip : 0.0f);
+                    }
+                }
+                bitmode = false;
+                __syncthreads();
+                if (s_fail) {
+                    if (tid == 0) atomicExch(a.status, 4);
+                    alive_prev = 0u;
+                }
+                if (alive_prev == 0u) break;
+                continue;
+            }
+
+            // ---- float form of layer li
+            bool ready = true;
+            if (tid == 0) {
+                s_alive[(li + 1) % 3] = 0u;
+                s_ns[(li + 1) % 3] = 0;
+            }
+            if (STAGED) {
+                if (tid == 0) issue_groups(li);
+                ready = wait_table(li);
+                if (!ready) s_fail = 1;
+            }
+            const unsigned char *T = table_of(li);
+            // per-layer scalars travel in the record's header
+            const int4 hdr = (STAGED && ready) ? *reinterpret_cast<const int4 *>(T)
+                                               : (STAGED ? make_int4(0, 4, 0, 0) : __ldg(reinterpret_cast<const int4 *>(T)));
+            const int classes = hdr.x, lk = hdr.y;
+            const float lw = __int_as_float(hdr.z);
+            last_classes = classes;
+            unsigned int bits = 0;
+            bool ns = false;
+            const unsigned char *in = cur + sub * TB;
+            for (int u = grp; u < classes; u += CPI) {
+                const uint2 *ep = reinterpret_cast<const uint2 *>(T + alt2_entry_offset(u));
+                const uint2 e = STAGED ? *ep : __ldg(ep);
+                const int ao = (int)(e.x & 0xffffu) * TI, bo = (int)(e.x >> 16) * TI;      // 4 * row * TI = row * RS
+                unsigned char *out = nxt + resident_phys_row(u) * RS + sub * TB;
+#pragma unroll
+                for (int h = 0; h < NQ; ++h) {
+                    const float4 va = *reinterpret_cast<const float4 *>(in + ao + 16 * h);
+                    const float4 vb = *reinterpret_cast<const float4 *>(in + bo + 16 * h);
+                    const float4 s = class_sum_alt2<KT>(va, vb, lk, lw, a.exact_ok != 0);
+                    float4 y;
+                    y.x = finish_output(s.x, a.bias, a.clip);
+                    y.y = finish_output(s.y, a.bias, a.clip);
+                    y.z = finish_output(s.z, a.bias, a.clip);
+                    y.w = finish_output(s.w, a.bias, a.clip);
+                    // dead images stay dead: with bias <= 0 an all-zero image stays all-zero by itself
+                    if (force_dead) {
+                        const unsigned int al = alive_prev >> (sub * IPT + 4 * h);
+                        if (!(al & 1u)) y.x = 0.0f;
+                        if (!(al & 2u)) y.y = 0.0f;
+                        if (!(al & 4u)) y.z = 0.0f;
+                        if (!(al & 8u)) y.w = 0.0f;
+                    }
+                    bits |= ((y.x != 0.0f ? 1u : 0u) | (y.y != 0.0f ? 2u : 0u) | (y.z != 0.0f ? 4u : 0u) | (y.w != 0.0f ? 8u : 0u)) << (4 * h);
+                    ns |= (y.x != 0.0f && y.x != a.clip) || (y.y != 0.0f && y.y != a.clip) || (y.z != 0.0f && y.z != a.clip) ||
+                          (y.w != 0.0f && y.w != a.clip);
+                    *reinterpret_cast<float4 *>(out + 16 * h) = y;
+                }
+            }
+            const unsigned int wm = __reduce_or_sync(0xffffffffu, bits << (sub * IPT));
+            if (lane == 0 && wm) atomicOr(&s_alive[li % 3], wm);
+            if (use_bits && __any_sync(0xffffffffu, ns) && lane == 0) s_ns[li % 3] = 1;
+            __syncthreads();
+            const unsigned int alive_now = s_alive[li % 3] & alive_prev;
+            const bool saturated = use_bits && s_ns[li % 3] == 0;
+            if (tid == 0) {
+                const int died = __popc(alive_prev & ~alive_now);
+                if (died) atomicAdd(a.died_at + li, died);
+            }
+            alive_prev = alive_now;
+            unsigned char *t = cur; cur = nxt; nxt = t;
+            ++li;
+            if (s_fail) {                    // a table never arrived: report it and drop the block's images
+                if (tid == 0) atomicExch(a.status, 4);
+                alive_prev = 0u;
+            }
+            if (alive_prev == 0u) break;
+            if (saturated && li < a.nlayers) {
+                // every output of the layer is 0 or clip: continue in the bit form
+                rows_to_bits(cur, wring0);
+                ws = 0;
+                __syncthreads();
+                bitmode = true;
+            }
+        }
+        if (STAGED) {
+            // tables may still be on their way: wait for them (bounded) so that the block does not
+            // exit, and its shared memory get reused, under a copy in flight
+            if (tid == 0)
+                for (int g = min(li, a.nlayers - 1) >> gshift; g < next_group; ++g)
+                    if (!mbar_wait(&s_bar[g & (tring - 1)], (unsigned int)((g >> tshift) & 1))) atomicExch(a.status, 4);
+            __syncthreads();
+        }
+
+        // ---- expand the survivors' classes to all member rows (dead blocks write nothing)
+        if (alive_prev != 0u) {
+            const ResLayer LL = a.layers[li - 1];
+            const int tile = j0 >> 5, lane0 = j0 & 31;
+            float *out = a.yout + (size_t)tile * a.tile_stride + lane0 + sub * IPT;
+            for (int u = grp; u < last_classes; u += CPI) {
+                const unsigned char *src = cur + resident_phys_row(u) * RS + sub * TB;
+#pragma unroll
+                for (int h = 0; h < NQ; ++h) {
+                    const float4 y = *reinterpret_cast<const float4 *>(src + 16 * h);
+                    if (LL.mem_ptr == nullptr) {
+                        *reinterpret_cast<float4 *>(out + (size_t)u * 32 + 4 * h) = y;
+                    } else {
+                        const int mb = __ldg(LL.mem_ptr + u), me = a.reps_only ? mb + 1 : __ldg(LL.mem_ptr + u + 1);
+                        for (int m = mb; m < me; ++m) *reinterpret_cast<float4 *>(out + __ldg(LL.mem + m) + 4 * h) = y;
+                    }
+                }
+            }
+            if (tid == 0) atomicOr(a.mask + tile, alive_prev << lane0);
+        }
+    }
+
+    // ---- last block done: rebuild the work list
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        s_last = (atomicAdd(a.counter, 1u) == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    LayerArgs la;
+    la.yin = a.yin; la.yout = a.yout; la.tile_stride = a.tile_stride;
+    la.ctl_in = a.ctl_in; la.ctl_out = a.ctl_out; la.slot = a.slot; la.mask = a.mask;
+    la.ids0 = a.ids0; la.ids1 = a.ids1; la.counter = a.counter; la.work = a.work; la.status = a.status;
+    la.died_at = nullptr;
+    la.first_member_only = 0;
+    la.bias = a.bias; la.clip = a.clip;
+    rebuild_worklist(la, live_in, ctl.ids_buf);
+}
+
+}  // namespace spdnn_impl

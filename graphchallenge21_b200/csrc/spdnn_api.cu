@@ -20,6 +20,7 @@
 
 #include "layer_inspect.h"
 #include "spdnn_kernels.cuh"
+#include "spdnn_alt2.cuh"
 #include "spdnn_resident.cuh"
 
 using namespace spdnn_impl;
@@ -87,6 +88,9 @@ struct spdnn {
     bool reps_only = true;             // SPDNN_REPS_ONLY=0: every launch writes all N rows
     bool exact_shortcut = true;        // SPDNN_EXACT_SHORTCUT=0 disables the exact-sum shortcut of the ALT2 form
     bool bit_form = true;              // SPDNN_BIT_FORM=0 disables the bit form of saturated activations (ALT2)
+    int table_ring_max = 4;            // SPDNN_TABLE_RING=2|4: most staged groups of ALT2 tables in flight
+    int table_group_max = 8;           // SPDNN_TABLE_GROUP=1|2|4|8: most layers one bulk copy brings
+    std::vector<unsigned char *> streams;   // packed ALT2 table streams of the captured schedule (one per chunk)
     bool print_schedule = false;       // SPDNN_PRINT_SCHEDULE=1: one line per launch when the graph is built
     bool resident_always = false;      // ... even for a lone layer that the per-layer kernel would serve better
     int res_ti_max = 32;               // largest group of images per block to try
@@ -250,14 +254,24 @@ int launch_resident_t(spdnn *c, const ResArgs &a, int grid, size_t smem) {
     return SPDNN_OK;
 }
 
+template <int TI, int IPT, int KT, bool STAGED>
+int launch_alt2_t(spdnn *c, const ResArgs &a, int grid, size_t smem) {
+    static bool configured[64] = {};
+    if (!configured[c->device & 63]) {
+        CK(cudaFuncSetAttribute(alt2_kernel<TI, IPT, KT, STAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, c->smem_optin - 1024));
+        configured[c->device & 63] = true;
+    }
+    alt2_kernel<TI, IPT, KT, STAGED><<<grid, kThreads, smem, c->stream>>>(a);
+    CK(cudaGetLastError());
+    return SPDNN_OK;
+}
+
 // ALT2 form (always a uniform weight): group sizes 32/16 with 8 images per thread, 16/8/4 with 4.
 template <int TI, int IPT>
 int launch_alt2(spdnn *c, const ResArgs &a, int grid, size_t smem, bool k32) {
-    const bool staged = a.table_bytes > 0;
-    if (k32) return staged ? launch_resident_t<TI, IPT, kResAlt2, 32, true, true>(c, a, grid, smem)
-                           : launch_resident_t<TI, IPT, kResAlt2, 32, true, false>(c, a, grid, smem);
-    return staged ? launch_resident_t<TI, IPT, kResAlt2, 0, true, true>(c, a, grid, smem)
-                  : launch_resident_t<TI, IPT, kResAlt2, 0, true, false>(c, a, grid, smem);
+    const bool staged = a.tring > 0;
+    if (k32) return staged ? launch_alt2_t<TI, IPT, 32, true>(c, a, grid, smem) : launch_alt2_t<TI, IPT, 32, false>(c, a, grid, smem);
+    return staged ? launch_alt2_t<TI, IPT, 0, true>(c, a, grid, smem) : launch_alt2_t<TI, IPT, 0, false>(c, a, grid, smem);
 }
 
 template <int TI>
@@ -333,11 +347,6 @@ int prepare_resident(spdnn *c) {
             if (!rc) rc = upload_vec(c, &R->mem_ptr, t.mem_ptr);
             if (!rc) rc = upload_vec(c, &R->mem, t.mem);
             if (rc) return rc;
-            if (t.mode == RES_ALT2) {
-                // the four saturated outputs of every class, evaluated by the device's own arithmetic
-                alt2_truth_kernel<<<std::max(1, std::min(64, (t.classes + 255) / 256)), 256, 0, c->stream>>>(R->blob, c->bias, c->clip);
-                CK(cudaGetLastError());
-            }
             CK(cudaStreamSynchronize(c->stream));
             R->class_of.swap(t.class_of);
             R->partition_hash = t.partition_hash;
@@ -365,10 +374,12 @@ int prepare_resident(spdnn *c) {
 // Rows one activation buffer needs for layer l inside a resident chunk.
 inline int resident_rows(const DevRes &R) { return ((std::max(R.v_in, R.classes) + 1) & ~1) + 2; }
 
-// Dynamic shared memory of a resident block: two activation buffers, two staged tables, two
-// buffers of one word per row for the bit form.
-inline size_t resident_smem_bytes(int ti, int rows, int table) {
-    return 2 * (size_t)rows * ti * 4 + 2 * (size_t)table + 2 * (size_t)rows * 4;
+// Dynamic shared memory of a resident block.  GENERIC chunks: two activation buffers and two
+// staged tables.  ALT2 chunks: two activation buffers, `tring` groups of 1 << gshift layer records
+// of `stride` bytes, `wring` buffers of rows_w words for the bit form.
+inline size_t resident_smem_bytes(int ti, int rows, int table) { return 2 * (size_t)rows * ti * 4 + 2 * (size_t)table; }
+inline size_t alt2_smem_bytes(int ti, int rows, int stride, int gshift, int tring, int wring, int rows_w) {
+    return 2 * (size_t)rows * ti * 4 + (size_t)tring * ((size_t)stride << gshift) + (size_t)wring * rows_w * 4;
 }
 
 // Enqueues the whole network: chunks of layers through the resident kernel where a group of
@@ -378,6 +389,9 @@ struct Step {
     int first = 0, count = 1;      // layers [first, first + count)
     int ti = 0, ipt = 4;           // resident chunk: images per block / per thread; ti == 0: per-layer kernel
     int rows = 0, table = 0;       // resident chunk: rows of one activation buffer, bytes per staged table
+    // ALT2 chunk (alt2_kernel): packed table stream and its staging, word buffers of the bit form
+    int stride = 0, gshift = 0, tring = 0, wring = 2, rows_w = 0, max_classes = 0;
+    unsigned char *stream = nullptr;
 };
 
 // The launches of one pass, front to back.
@@ -409,7 +423,7 @@ std::vector<Step> plan_steps(spdnn *c) {
             }
             if (ti) {
                 // extend while the layers are of one kernel variant and the group still fits
-                int f = 1, blob = R0.blob_bytes;
+                int f = 1, blob = R0.blob_bytes, maxc = R0.classes;
                 while (f < chunk && l + f < c->layers && c->res[l + f]) {
                     const DevRes &M = *c->res[l + f];
                     if (M.mode != R0.mode || M.uniform != R0.uniform || (M.k == 32) != k32) break;
@@ -417,15 +431,38 @@ std::vector<Step> plan_steps(spdnn *c) {
                     if (!fits(ti, r2, 0)) break;
                     rows = r2;
                     blob = std::max(blob, M.blob_bytes);
+                    maxc = std::max(maxc, M.classes);
                     ++f;
                 }
                 int tb = (blob + 127) / 128 * 128;
                 if (!(c->stage_tables && fits(ti, rows, tb))) tb = 0;
+                if (R0.mode == kResAlt2) {
+                    // packed stream: groups of up to 8 layers per bulk copy, up to 4 groups in flight (the bit
+                    // form applies a layer in far less time than a copy takes to arrive), as many word buffers
+                    // as a group has layers, plus the one it starts from -- whatever of that fits
+                    st.max_classes = maxc;
+                    st.stride = alt2_stream_stride(maxc);
+                    st.rows_w = std::max(rows, (maxc + 63) / 64 * 64);
+                    auto afits = [&](int gs, int tr, int wr) {
+                        return alt2_smem_bytes(ti, rows, st.stride, gs, tr, wr, st.rows_w) + 2048 <= (size_t)c->smem_optin;
+                    };
+                    st.tring = 0; st.gshift = 0; st.wring = 2;
+                    // staging may take a quarter of the shared memory at most, so that the blocks per SM stay
+                    // what the activations allow
+                    if (c->stage_tables)
+                        for (int gs = 3; gs >= 0 && !st.tring; --gs)
+                            for (int tr = 4; tr >= 2 && !st.tring; tr /= 2)
+                                if ((1 << gs) <= c->table_group_max && tr <= c->table_ring_max && afits(gs, tr, 2) &&
+                                    (size_t)tr * ((size_t)st.stride << gs) <= (size_t)c->smem_optin / 4) { st.gshift = gs; st.tring = tr; }
+                    for (int wr = (st.tring ? (1 << st.gshift) : 8) + 1; wr > 2; --wr)
+                        if (afits(st.gshift, st.tring, wr) && (size_t)wr * st.rows_w * 4 <= (size_t)c->smem_optin / 8) { st.wring = wr; break; }
+                    if (!afits(st.gshift, st.tring, st.wring)) ti = 0;      // not even the two word buffers fit
+                }
                 // A lone layer that reads all N rows of every image but computes few classes from
                 // them (the first layer of a network with repeated columns) gains nothing from
                 // staging the rows in shared memory: gather straight from global memory instead.
                 const bool lone_wide = (f == 1 && R0.v_in == c->n && R0.classes * 2 <= c->n && !c->resident_always);
-                if (!lone_wide) { st.count = f; st.ti = ti; st.ipt = ipt; st.rows = rows; st.table = tb; }
+                if (!lone_wide && ti) { st.count = f; st.ti = ti; st.ipt = ipt; st.rows = rows; st.table = tb; }
             }
         }
         if (st.ti) chunk = std::min(chunk * 2, c->chunk_max);
@@ -440,8 +477,7 @@ std::vector<Step> plan_steps(spdnn *c) {
 // images still die, long once the survivors are stable), one launch per layer otherwise.  A
 // launch that is followed by a resident chunk writes only the one row per class that chunk
 // will read.
-int enqueue_layers(spdnn *c) {
-    const std::vector<Step> plan = plan_steps(c);
+int enqueue_layers(spdnn *c, const std::vector<Step> &plan) {
     c->last_group = 0;
     for (size_t step = 0; step < plan.size(); ++step) {
         const Step &st = plan[step];
@@ -459,19 +495,27 @@ int enqueue_layers(spdnn *c) {
             a.counter = c->counter; a.work = c->counter + 1; a.status = c->status;
             a.layers = c->res_table + l; a.died_at = c->died_at + l; a.nlayers = st.count;
             a.buf_rows = st.rows; a.table_bytes = st.table;
+            a.stream = st.stream; a.stream_stride = st.stride; a.tgroup_shift = st.gshift; a.tring = st.tring;
+            a.wring = st.wring; a.rows_w = st.rows_w; a.bit_multi = st.max_classes > 64 ? 1 : 0;
             a.n = c->n; a.bias = c->bias; a.clip = c->clip;
             a.reps_only = next_resident ? 1 : 0;
             a.exact_ok = (l > 0 && c->clip <= 1024.0f && c->exact_shortcut) ? 1 : 0;
             const int grid = std::max(1, (c->tiles_cap * 32 + st.ti - 1) / st.ti);
-            const size_t smem = resident_smem_bytes(st.ti, st.rows, st.table);
-            a.bit_ok = (R0.mode == kResAlt2 && c->bit_form && c->clip > 0.0f) ? 1 : 0;
+            const bool alt2 = (R0.mode == kResAlt2);
+            const size_t smem = alt2 ? alt2_smem_bytes(st.ti, st.rows, st.stride, st.gshift, st.tring, st.wring, st.rows_w)
+                                     : resident_smem_bytes(st.ti, st.rows, st.table);
+            a.bit_ok = (alt2 && c->bit_form && c->clip > 0.0f) ? 1 : 0;
             int rc = launch_resident(c, st.ti, st.ipt, a, grid, smem, R0.mode, R0.k == 32, R0.uniform);
             if (rc) return rc;
             c->last_group = st.ti;
+            char tables_txt[96];
+            if (alt2 && st.tring) snprintf(tables_txt, sizeof tables_txt, "staged (%d layers per copy, %d copies in flight), %d word buffers", 1 << st.gshift, st.tring, st.wring);
+            else if (alt2) snprintf(tables_txt, sizeof tables_txt, "global, %d word buffers", st.wring);
+            else snprintf(tables_txt, sizeof tables_txt, "%s", st.table ? "staged" : "global");
             if (c->print_schedule)
                 fprintf(stderr, "[spdnn] step %zu: resident layers %d..%d  group %d images (%d per thread)  %s  rows %d (v_in %d, classes %d)  smem %zu B  tables %s%s\n",
                         step, l, l + st.count - 1, st.ti, st.ipt, R0.mode == kResAlt2 ? "ALT2" : "GENERIC", st.rows, R0.v_in,
-                        R0.classes, smem, st.table ? "staged" : "global", next_resident ? "  writes representatives only" : "");
+                        R0.classes, smem, tables_txt, next_resident ? "  writes representatives only" : "");
         } else {
             LayerDesc d;
             d.off = L.off; d.vals = L.vals;
@@ -518,8 +562,21 @@ int build_graph(spdnn *c) {
         int rc0 = prepare_resident(c);
         if (rc0) return rc0;
     }
+    // the launches of a pass, and (outside the capture) the packed table stream of every ALT2 chunk
+    std::vector<Step> plan = plan_steps(c);
+    for (unsigned char *p : c->streams) cudaFree(p);
+    c->streams.clear();
+    for (Step &st : plan) {
+        if (!st.ti || c->res[st.first]->mode != kResAlt2) continue;
+        if (st.rows > 16383) return fail(c, SPDNN_ERR_LIMIT, "layer %d: %d rows do not fit a packed table entry", st.first, st.rows);
+        CK(cudaMalloc(&st.stream, (size_t)st.count * st.stride));
+        c->streams.push_back(st.stream);
+        alt2_pack_kernel<<<st.count, 256, 0, c->stream>>>(c->res_table + st.first, st.stride, st.stream, c->bias, c->clip);
+        CK(cudaGetLastError());
+    }
+    CK(cudaStreamSynchronize(c->stream));
     CK(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
-    int rc = enqueue_layers(c);
+    int rc = enqueue_layers(c, plan);
     cudaError_t e = cudaStreamEndCapture(c->stream, &g);
     if (rc) { if (g) cudaGraphDestroy(g); return rc; }
     if (e != cudaSuccess) return fail(c, SPDNN_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
@@ -593,6 +650,8 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
         if (const char *e = getenv("SPDNN_PRINT_SCHEDULE")) c->print_schedule = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_EXACT_SHORTCUT")) c->exact_shortcut = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BIT_FORM")) c->bit_form = atoi(e) != 0;
+        if (const char *e = getenv("SPDNN_TABLE_RING")) c->table_ring_max = atoi(e) >= 4 ? 4 : 2;
+        if (const char *e = getenv("SPDNN_TABLE_GROUP")) { const int v = atoi(e); c->table_group_max = v >= 8 ? 8 : (v >= 4 ? 4 : (v >= 2 ? 2 : 1)); }
         if (const char *e = getenv("SPDNN_REPS_ONLY")) c->reps_only = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_CHUNK_FIRST")) c->chunk_first = std::max(1, atoi(e));
         if (const char *e = getenv("SPDNN_CHUNK_MAX")) c->chunk_max = std::max(1, atoi(e));
@@ -610,6 +669,7 @@ void spdnn_destroy(spdnn_t *c) {
     free_buffers(c);
     cudaFree(c->ctl); cudaFree(c->counter); cudaFree(c->status); cudaFree(c->stage);
     cudaFree(c->died_at); cudaFree(c->res_table);
+    for (unsigned char *p : c->streams) cudaFree(p);
     c->layer.clear();
     if (c->ev_prep0) cudaEventDestroy(c->ev_prep0);
     if (c->ev_prep1) cudaEventDestroy(c->ev_prep1);

@@ -45,7 +45,7 @@ constexpr int kResGeneric = 0, kResAlt2 = 1;
 struct ResLayer {
     const int32_t *blob;      // header {classes, k, bits of w, 0}, then
                               // GENERIC: int32 t[U][k+4] (k input rows, then the output row) [+ float vals[U][k+4]]
-                              // ALT2:    int32 t[U][4] = {row a, row b, output row, truth table (alt2_truth_kernel)}
+                              // ALT2:    int32 t[U][4] = {row a, row b, output row, 0}
     const int32_t *rep;       // [v_in] neuron*32 carrying value id v, or nullptr (value id == neuron)
     const int32_t *mem_ptr;   // [U+1] member ranges, or nullptr (class u == column u)
     const int32_t *mem;       // member column*32
@@ -76,8 +76,16 @@ struct ResArgs {
     int reps_only;            // 1: the next launch is a resident chunk, which reads one row per class (the first
                               // member): write only that row at the end of this chunk
     int exact_ok;             // the inputs of every layer of the chunk are activations in [0, clip], clip <= 1024
-    int bit_ok;               // ALT2: word 3 of every table entry holds the class's truth table (alt2_truth_kernel)
     float bias, clip;
+    // ALT2 chunks (alt2_kernel) read their tables from one packed stream per chunk instead of the per-layer blobs
+    const unsigned char *stream;   // stream_stride bytes per layer of the chunk (alt2_pack_kernel)
+    int stream_stride;
+    int tgroup_shift;         // staged: one bulk copy brings 1 << tgroup_shift layers of the stream
+    int tring;                // staged: buffers of one such group (2 or 4); 0 = read the stream from global memory
+    int wring;                // bit form: buffers of one word per row (>= 2)
+    int rows_w;               // bit form: words per buffer (>= buf_rows, covers all 64-class passes)
+    int bit_ok;               // bit form allowed (clip > 0, not switched off)
+    int bit_multi;            // bit form: some layer of the chunk has more than 64 classes
 };
 
 __host__ __device__ __forceinline__ int resident_phys_row(int r) {
@@ -248,55 +256,9 @@ __device__ __forceinline__ float finish_output(float sum, float bias, float clip
     return fminf(fmaxf(__fadd_rn(sum, bias), 0.0f), clip);
 }
 
-// ---- bit form of saturated activations (ALT2) ---------------------------------------------------
-// Once every activation of a block's images is exactly 0 or exactly clip (the steady state of
-// the challenge networks), a row of the block is one 32-bit word (bit i = image i holds clip)
-// and an ALT2 class is a boolean function of two words: its output for the four combinations
-// (a, b) in {0, clip}^2 is a property of the class, not of the image.  alt2_truth_kernel
-// evaluates those four outputs ONCE per class with the same fp32 code as the float form
-// (class_sum_alt2 + finish_output) and stores them in word 3 of the table entry:
-//   bit q      (q = [a == clip] + 2 [b == clip])  output == clip
-//   bit 4 + q                                    output is neither 0 nor clip
-//   bit 8                                        entry evaluated
-// The resident kernel then applies a layer to all 32 images of a block with a few logic
-// instructions per class, and returns to the float form for the layer in which an image meets
-// a combination whose output is not saturated -- so the results are those of the float form,
-// bit for bit, whatever the inputs.
-static __global__ void alt2_truth_kernel(int32_t *blob, float bias, float clip) {
-    const int classes = blob[0], k = blob[1];
-    const float w = __int_as_float(blob[2]);
-    for (int u = blockIdx.x * blockDim.x + threadIdx.x; u < classes; u += gridDim.x * blockDim.x) {
-        const float4 s = class_sum_alt2<0>(make_float4(0.0f, clip, 0.0f, clip), make_float4(0.0f, 0.0f, clip, clip), k, w, false);
-        const float y[4] = {finish_output(s.x, bias, clip), finish_output(s.y, bias, clip), finish_output(s.z, bias, clip),
-                            finish_output(s.w, bias, clip)};
-        unsigned int tt = 0x100u;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            if (y[q] == clip) tt |= 1u << q;
-            else if (y[q] != 0.0f) tt |= 16u << q;
-        }
-        blob[4 + 4 * u + 3] = (int32_t)tt;
-    }
-}
-
-// Applies a two-input truth table (4 bits of tt, index = [a] + 2 [b]) to 32 images at once.
-__device__ __forceinline__ unsigned int apply_truth(unsigned int wa, unsigned int wb, unsigned int tt) {
-    int m0, m1, m2, m3;      // bit q of tt spread over a word: bfe.s32 of one bit sign-extends it
-    asm("bfe.s32 %0, %1, 0, 1;" : "=r"(m0) : "r"(tt));
-    asm("bfe.s32 %0, %1, 1, 1;" : "=r"(m1) : "r"(tt));
-    asm("bfe.s32 %0, %1, 2, 1;" : "=r"(m2) : "r"(tt));
-    asm("bfe.s32 %0, %1, 3, 1;" : "=r"(m3) : "r"(tt));
-    const unsigned int t0 = (wa & (unsigned int)m1) | (~wa & (unsigned int)m0);
-    const unsigned int t1 = (wa & (unsigned int)m3) | (~wa & (unsigned int)m2);
-    return (wb & t1) | (~wb & t0);
-}
-
 // Grid: one block per TI live images (launched for the worst case; surplus blocks only take
 // part in the last-block ticket).  Dynamic shared memory: two activation buffers of
 // buf_rows * TI * 4 bytes, then (STAGED) two table buffers of table_bytes each.
-#ifndef SPDNN_ALT2_MIN_BLOCKS
-#define SPDNN_ALT2_MIN_BLOCKS 8      // <= 32 registers: a full set of 64 warps per SM for the light ALT2 form
-#endif
 // Threads per block: the GENERIC form is bound by shared-memory latency with one block per SM
 // (its buffers fill the shared memory), so it runs 16 warps; the light ALT2 form runs many
 // small blocks per SM.
@@ -311,13 +273,11 @@ struct ResThreads {
 // step, which halves the per-layer bookkeeping (barrier, table wait, loop control, addresses)
 // per image; it is used for the light ALT2 form.
 template <int TI, int IPT, int MODE, int KT, bool UNIFORM, bool STAGED>
-__global__ void __launch_bounds__(ResThreads<MODE>::value, (MODE == kResAlt2 ? (IPT == 8 ? SPDNN_ALT2_MIN_BLOCKS / 2 : SPDNN_ALT2_MIN_BLOCKS) : 1))
+__global__ void __launch_bounds__(ResThreads<MODE>::value, 1)
 resident_kernel(const ResArgs a) {
     constexpr int NT = ResThreads<MODE>::value;
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ unsigned int s_alive[3];
-    __shared__ int s_ns[3];                      // layer li % 3 produced an output that is neither 0 nor clip
-    __shared__ int s_x[4];                       // state handed from the bit form (warp 0) to the block
     __shared__ int s_last, s_fail;
     __shared__ __align__(8) unsigned long long s_bar[2];
     constexpr int NQ = IPT / 4;                  // float4 halves per thread
@@ -326,7 +286,6 @@ resident_kernel(const ResArgs a) {
     constexpr int RS = TI * 4;                   // bytes per row
     constexpr int TB = IPT * 4;                  // bytes of a row one thread owns
     constexpr unsigned int kFull = (IPT == 8) ? 0xFFu : 0xFu;
-    constexpr bool BITS = (MODE == kResAlt2);    // the bit form of saturated activations exists for ALT2 tables
     const int tid = threadIdx.x, lane = tid & 31;
     const int sub = tid % LPC, grp = tid / LPC;
     const LoopCtl ctl = *a.ctl_in;
@@ -337,13 +296,9 @@ resident_kernel(const ResArgs a) {
     if ((int)blockIdx.x < nblk) {
         unsigned char *cur = smem, *nxt = smem + buf_bytes;
         unsigned char *const tbl0 = smem + 2 * buf_bytes;      // table buffer q sits at tbl0 + q * table_bytes
-        // two buffers of one word per row for the bit form, behind the table buffers
-        unsigned int *const wbits = reinterpret_cast<unsigned int *>(tbl0 + 2 * (size_t)a.table_bytes);
-        const bool use_bits = BITS && a.bit_ok != 0;
         const int j0 = blockIdx.x * TI;
         if (tid == 0) {
             s_alive[0] = 0u;
-            s_ns[0] = 0;
             s_fail = 0;
             if (STAGED) {
                 mbar_init(&s_bar[0], 1);
@@ -355,7 +310,6 @@ resident_kernel(const ResArgs a) {
         // ---- load one row per value id of the block's images (dead images were dropped: read
         //      through the work list)
         unsigned int my_valid = 0;
-        bool load_ns = false;                    // a loaded value is neither 0 nor clip
         {
             const float *p[IPT];
             bool contiguous = ctl.identity != 0;
@@ -386,9 +340,6 @@ resident_kernel(const ResArgs a) {
                         x.w = (my_valid >> (4 * h) & 8u) ? __ldg(p[4 * h + 3] + e) : 0.0f;
                     }
                     *reinterpret_cast<float4 *>(dst + 16 * h) = x;
-                    if (BITS)
-                        load_ns |= (x.x != 0.0f && x.x != a.clip) || (x.y != 0.0f && x.y != a.clip) || (x.z != 0.0f && x.z != a.clip) ||
-                                   (x.w != 0.0f && x.w != a.clip);
                 }
             }
             // rows v_in .. even(v_in) + 1 are the zero rows padded table entries point at
@@ -401,155 +352,41 @@ resident_kernel(const ResArgs a) {
         // LPC divides 32, so every warp holds all sub-columns: the OR over a warp is the block's
         // mask of valid images (bit i = image j0 + i), identical in every thread
         unsigned int alive_prev = __reduce_or_sync(0xffffffffu, my_valid << (sub * IPT));
-        const bool start_in_bits = !__syncthreads_or(load_ns ? 1 : 0) && use_bits;
+        __syncthreads();
 
         // ---- the layers of this chunk
-        // Thread 0 requests the tables in order; next_issue is the next table to request and
-        // (nb_ptr, nb_bytes) describe it, read from global memory one layer ahead so that the
-        // request does not wait for that load.
+        // thread 0 keeps the address of the table after next in registers, so that the copy
+        // it issues at the top of a layer does not wait for a load from global memory
         const int32_t *nb_ptr = nullptr;
         unsigned int nb_bytes = 0;
-        int next_issue = 1;
         if (STAGED && tid == 0 && a.nlayers > 1) {
             nb_ptr = a.layers[1].blob;
             nb_bytes = (unsigned int)a.layers[1].blob_bytes;
         }
-        auto issue_next_table = [&](int li) {        // thread 0, at the top of layer li: every thread has left layer li - 1
-            if (next_issue == li + 1 && next_issue < a.nlayers) {
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                bulk_load_table(tbl0 + (next_issue & 1) * a.table_bytes, nb_ptr, nb_bytes, &s_bar[next_issue & 1]);
-                ++next_issue;
-                if (next_issue < a.nlayers) {
-                    nb_ptr = a.layers[next_issue].blob;
-                    nb_bytes = (unsigned int)a.layers[next_issue].blob_bytes;
-                }
-            }
-        };
-        // float rows -> one word per row (bit i = image i is non-zero; called when every value is 0 or clip)
-        auto rows_to_bits = [&](const unsigned char *buf, unsigned int *w) {
-            for (int r0 = 0; r0 < a.buf_rows; r0 += CPI) {
-                const int r = r0 + grp;
-                unsigned int m = 0;
-                if (r < a.buf_rows) {
-#pragma unroll
-                    for (int h = 0; h < NQ; ++h) {
-                        const float4 v = *reinterpret_cast<const float4 *>(buf + r * RS + sub * TB + 16 * h);
-                        m |= ((v.x != 0.0f ? 1u : 0u) | (v.y != 0.0f ? 2u : 0u) | (v.z != 0.0f ? 4u : 0u) | (v.w != 0.0f ? 8u : 0u)) << (4 * h);
-                    }
-                }
-                m <<= sub * IPT;
-#pragma unroll
-                for (int s = 1; s < LPC; s <<= 1) m |= __shfl_xor_sync(0xffffffffu, m, s);
-                if (sub == 0 && r < a.buf_rows) w[r] = m;
-            }
-        };
-        int li = 0;                  // layers of the chunk applied so far
+        int li = 0;
         int last_classes = 0;
         const bool force_dead = a.bias > 0.0f;
-        unsigned int *wcur = wbits, *wnxt = wbits + a.buf_rows;
-        bool bitmode = false;
-        if (BITS && start_in_bits) {
-            rows_to_bits(cur, wcur);
-            __syncthreads();
-            bitmode = true;
-        }
-        while (li < a.nlayers) {
-            if (BITS && bitmode) {
-                // ---- bit form: warp 0 applies layer after layer to the block's 32 images, one word
-                //      per row, until the chunk ends, every image is dead, or a layer yields an output
-                //      that is neither 0 nor clip (that layer is then redone in the float form)
-                if (tid < 32) {
-                    unsigned int alive = alive_prev;
-                    int done_classes = last_classes;
-                    while (li < a.nlayers) {
-                        const int32_t *T;
-                        if (STAGED) {
-                            if (tid == 0) issue_next_table(li);
-                            if (!__all_sync(0xffffffffu, mbar_wait(&s_bar[li & 1], (unsigned int)((li >> 1) & 1)))) {
-                                s_fail = 1;
-                                break;
-                            }
-                            T = reinterpret_cast<const int32_t *>(tbl0 + (li & 1) * a.table_bytes);
-                        } else {
-                            T = a.layers[li].blob;
-                        }
-                        const int4 *T4 = reinterpret_cast<const int4 *>(T);
-                        const int classes = STAGED ? T[0] : __ldg(T);
-                        const unsigned int keep = force_dead ? alive : 0xffffffffu;
-                        unsigned int acc = 0u, ns = 0u;
-                        for (int u0 = 0; u0 < classes; u0 += 64) {
-                            // two classes per lane and pass, their loads in flight together; an entry of
-                            // zeros (rows 0, truth table 0) stands in for a class past the end
-                            const int u1 = u0 + lane, u2 = u1 + 32;
-                            int4 e1 = make_int4(0, 0, 0, 0), e2 = e1;
-                            if (u1 < classes) e1 = STAGED ? T4[1 + u1] : __ldg(T4 + 1 + u1);
-                            if (u2 < classes) e2 = STAGED ? T4[1 + u2] : __ldg(T4 + 1 + u2);
-                            const unsigned int a1 = wcur[e1.x], b1 = wcur[e1.y], a2 = wcur[e2.x], b2 = wcur[e2.y];
-                            const unsigned int o1 = apply_truth(a1, b1, (unsigned int)e1.w) & keep;
-                            const unsigned int o2 = apply_truth(a2, b2, (unsigned int)e2.w) & keep;
-                            ns |= (apply_truth(a1, b1, (unsigned int)e1.w >> 4) | apply_truth(a2, b2, (unsigned int)e2.w >> 4)) & keep;
-                            if (u1 < classes) wnxt[e1.z] = o1;
-                            if (u2 < classes) wnxt[e2.z] = o2;
-                            acc |= o1 | o2;
-                        }
-                        if (__any_sync(0xffffffffu, ns != 0u)) break;
-                        const unsigned int now = __reduce_or_sync(0xffffffffu, acc) & alive;
-                        if (lane == 0) {
-                            const int died = __popc(alive & ~now);
-                            if (died) atomicAdd(a.died_at + li, died);
-                        }
-                        alive = now;
-                        unsigned int *t = wcur; wcur = wnxt; wnxt = t;
-                        done_classes = classes;
-                        ++li;
-                        __syncwarp();
-                        if (alive == 0u) break;
-                    }
-                    if (lane == 0) {
-                        s_x[0] = li; s_x[1] = (int)alive; s_x[2] = done_classes; s_x[3] = (wcur == wbits) ? 0 : 1;
-                        s_alive[li % 3] = 0u;        // the float form may take over at layer li
-                        s_ns[li % 3] = 0;
-                    }
-                }
-                __syncthreads();
-                li = s_x[0];
-                alive_prev = (unsigned int)s_x[1];
-                last_classes = s_x[2];
-                wcur = wbits + (s_x[3] ? a.buf_rows : 0);
-                wnxt = wbits + (s_x[3] ? 0 : a.buf_rows);
-                // back to floats: the rows the next float layer (or the expansion below) reads
-                for (int r = grp; r < a.buf_rows; r += CPI) {
-                    const unsigned int wv = wcur[r] >> (sub * IPT);
-#pragma unroll
-                    for (int h = 0; h < NQ; ++h) {
-                        const unsigned int q = wv >> (4 * h);
-                        *reinterpret_cast<float4 *>(cur + r * RS + sub * TB + 16 * h) =
-                            make_float4((q & 1u) ? a.clip : 0.0f, (q & 2u) ? a.clip : 0.0f, (q & 4u) ? a.clip : 0.0f, (q & 8u) ? a.clip : 0.0f);
-                    }
-                }
-                bitmode = false;
-                __syncthreads();
-                if (s_fail) {
-                    if (tid == 0) atomicExch(a.status, 4);
-                    alive_prev = 0u;
-                }
-                if (alive_prev == 0u) break;
-                continue;
-            }
-
-            // ---- float form of layer li
+        for (; li < a.nlayers; ++li) {
             const int32_t *T;
             bool ready = true;
-            if (tid == 0) {
-                s_alive[(li + 1) % 3] = 0u;
-                s_ns[(li + 1) % 3] = 0;
-            }
             if (STAGED) {
-                if (tid == 0) issue_next_table(li);
+                if (tid == 0) {
+                    s_alive[(li + 1) % 3] = 0u;
+                    // the other table buffer was last read in layer li - 1, which every thread has left
+                    if (li + 1 < a.nlayers) {
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        bulk_load_table(tbl0 + ((li + 1) & 1) * a.table_bytes, nb_ptr, nb_bytes, &s_bar[(li + 1) & 1]);
+                        if (li + 2 < a.nlayers) {
+                            nb_ptr = a.layers[li + 2].blob;
+                            nb_bytes = (unsigned int)a.layers[li + 2].blob_bytes;
+                        }
+                    }
+                }
                 ready = mbar_wait(&s_bar[li & 1], (unsigned int)((li >> 1) & 1));
                 if (!ready) s_fail = 1;
                 T = reinterpret_cast<const int32_t *>(tbl0 + (li & 1) * a.table_bytes);
             } else {
+                if (tid == 0) s_alive[(li + 1) % 3] = 0u;
                 T = a.layers[li].blob;
             }
             // per-layer scalars travel in the table's header
@@ -559,7 +396,6 @@ resident_kernel(const ResArgs a) {
             const float lw = __int_as_float(hdr.z);
             last_classes = classes;
             unsigned int bits = 0;
-            bool ns = false;
             const unsigned char *in = cur + sub * TB;
             for (int u = grp; u < classes; u += CPI) {
                 float4 s[NQ];
@@ -598,9 +434,6 @@ resident_kernel(const ResArgs a) {
                         if (!(al & 8u)) y.w = 0.0f;
                     }
                     bits |= ((y.x != 0.0f ? 1u : 0u) | (y.y != 0.0f ? 2u : 0u) | (y.z != 0.0f ? 4u : 0u) | (y.w != 0.0f ? 8u : 0u)) << (4 * h);
-                    if (BITS)
-                        ns |= (y.x != 0.0f && y.x != a.clip) || (y.y != 0.0f && y.y != a.clip) || (y.z != 0.0f && y.z != a.clip) ||
-                              (y.w != 0.0f && y.w != a.clip);
                     *reinterpret_cast<float4 *>(nxt + out_row * RS + sub * TB + 16 * h) = y;
                 }
             }
@@ -614,29 +447,19 @@ resident_kernel(const ResArgs a) {
             }
             const unsigned int wm = __reduce_or_sync(0xffffffffu, bits << (sub * IPT));
             if (lane == 0 && wm) atomicOr(&s_alive[li % 3], wm);
-            if (BITS && use_bits && __any_sync(0xffffffffu, ns) && lane == 0) s_ns[li % 3] = 1;
             __syncthreads();
             const unsigned int alive_now = s_alive[li % 3] & alive_prev;
-            const bool saturated = BITS && use_bits && s_ns[li % 3] == 0;
             if (tid == 0) {
                 const int died = __popc(alive_prev & ~alive_now);
                 if (died) atomicAdd(a.died_at + li, died);
             }
             alive_prev = alive_now;
             unsigned char *t = cur; cur = nxt; nxt = t;
-            ++li;
             if (s_fail) {                    // a table never arrived: report it and drop the block's images
                 if (tid == 0) atomicExch(a.status, 4);
                 alive_prev = 0u;
             }
-            if (alive_prev == 0u) break;
-            if (saturated && li < a.nlayers) {
-                // every output of the layer is 0 or clip: continue in the bit form
-                rows_to_bits(cur, wbits);
-                wcur = wbits; wnxt = wbits + a.buf_rows;
-                __syncthreads();
-                bitmode = true;
-            }
+            if (alive_prev == 0u) { ++li; break; }
         }
         if (STAGED && li < a.nlayers) {
             // the loop was left early with the table of layer li still on its way: wait for it

@@ -93,23 +93,26 @@ _BIT_FORM_WANT = {}
 
 
 @pytest.mark.parametrize("env", [{}, {"SPDNN_BIT_FORM": "0"}, {"SPDNN_CHUNK_FIRST": "1", "SPDNN_CHUNK_MAX": "3"},
-                                 {"SPDNN_RESIDENT_TI": "8"}, {"SPDNN_STAGE_TABLES": "0"}, {"SPDNN_RESIDENT_IPT": "4"}])
-@pytest.mark.parametrize("bias,clip", [(-0.3, 32.0), (0.0, 32.0), (-32.0, 32.0), (0.01, 32.0), (-0.3, 8.0), (-1.0, 2.5)])
-def test_bit_form_of_saturated_activations(bias, clip, env, monkeypatch, oracle):
+                                 {"SPDNN_RESIDENT_TI": "8"}, {"SPDNN_STAGE_TABLES": "0"}, {"SPDNN_RESIDENT_IPT": "4"},
+                                 {"SPDNN_TABLE_GROUP": "1"}, {"SPDNN_TABLE_GROUP": "2", "SPDNN_TABLE_RING": "2"}])
+@pytest.mark.parametrize("bias,clip,n,L", [(-0.3, 32.0, 1024, 70), (0.0, 32.0, 1024, 70), (-32.0, 32.0, 1024, 70), (0.01, 32.0, 1024, 70),
+                                           (-0.3, 8.0, 1024, 70), (-1.0, 2.5, 1024, 70), (-0.35, 32.0, 4096, 50), (0.0, 16.0, 4096, 50)])
+def test_bit_form_of_saturated_activations(bias, clip, n, L, env, monkeypatch, oracle):
     """Blocks whose activations are all exactly 0 or clip continue as one word per row and come
     back to floats in the layer where an output is not saturated; the bits are those of the
     float form for every bias and clip.  The batch holds runs of images that are saturated from
     the start (so whole blocks start a chunk in the bit form), images scaled off the 1/16 grid,
-    all-clip images and ordinary ones."""
+    all-clip images and ordinary ones; N = 4096 has 256 classes per layer (all warps of a block
+    work in the bit form), N = 1024 at most 64 (one warp)."""
     for k, v in env.items():
         monkeypatch.setenv(k, v)
-    n, L, b = 1024, 70, 640
+    b = 640
     net = SyntheticNetwork(n, L, "radix16", bias=bias)
     y0 = synthetic_images(n, b)
     y0[128:320] *= np.float32(clip)
     y0[320:400:3] *= np.float32(0.37 * clip)
     y0[400:440] = np.float32(clip)
-    key = (bias, clip)
+    key = (bias, clip, n)
     if key not in _BIT_FORM_WANT:
         _BIT_FORM_WANT[key] = oracle.infer(y0, [(r, None) for r in rows_of(net)], bias, clip=clip)
     check(run_gpu(net, y0, clip=clip), _BIT_FORM_WANT[key])
