@@ -349,7 +349,7 @@ def main_ours(args):
             "gpu_launches": int(launches * args.steps),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind + " copy bandwidth (MEASURED_PEAKS.json hbm_gbs)", "traffic": None,
-                         "kernel": "resident_kernel<%d>" % group if group else "layer_kernel",
+                         "kernel": (("alt2_kernel<%d>" if args.pattern == "radix16" else "resident_kernel<%d>") % group) if group else "layer_kernel",
                          "launches_per_step": loop_launches, "avg_launch_us": loop_ms * 1e3 / max(loop_launches, 1),
                          "algorithmic_bytes_per_launch": algo_bytes / max(loop_launches, 1),
                          "us_per_layer": loop_ms * 1e3 / L, "layer_loop_ms": loop_ms,

@@ -55,7 +55,8 @@ def _sources(*names: str) -> list[str]:
 
 
 def build_library(force: bool = False) -> str:
-    deps = _sources("spdnn_api.cu", "spdnn_static.cu", "spdnn_kernels.cuh", "layer_inspect.h")
+    # every source and header of the library: a header that is not listed would leave a stale build behind
+    deps = _sources(*sorted(n for n in os.listdir(CSRC) if n.endswith((".cu", ".cuh", ".h"))))
     if force or _stale(LIB, deps):
         _run([_nvcc(), *ARCH, *_host_cxx(), "-lineinfo", "-O3", "-std=c++17", "-shared", "-Xcompiler", "-fPIC",
               "-o", LIB, os.path.join(CSRC, "spdnn_api.cu"), os.path.join(CSRC, "spdnn_static.cu")])

@@ -6,20 +6,23 @@
 // ping-pong in shared memory, dead images are dropped between launches -- in two ways.
 //
 // 1. Packed table stream.  The tables of a chunk are one contiguous array in global memory,
-//    `stride` bytes per layer: a 16-byte header {classes, K, bits of w, 0}, then per pass of 64
-//    classes 32 slots of 16 bytes; slot `lane` holds the entries of classes 64p + lane and
-//    64p + 32 + lane, 8 bytes each: {4 * row a | (4 * row b) << 16, truth table}.  The output row of
-//    class u is resident_phys_row(u) and is not stored.  One bulk asynchronous copy (TMA) brings a
-//    GROUP of up to 8 layers into shared memory, several groups ahead of the layer being computed.
+//    `stride` bytes per layer: a 16-byte header {classes, K, bits of w, truth table}, then per pass
+//    of 64 classes 32 slots of 16 bytes; slot `lane` holds the entries of classes 64p + lane and
+//    64p + 32 + lane, 8 bytes each: {4 * row a | (4 * row b) << 16} twice, first in the plain row
+//    numbers (value ids) the bit form uses, then in the permuted rows of the float buffers.  The
+//    output row of class u is u (float buffers: resident_phys_row(u)) and is not stored.  One bulk asynchronous copy (TMA) brings a GROUP of up
+//    to 8 layers into shared memory, several groups ahead of the layer being computed.
 //
 // 2. Bit form of saturated activations.  Once every activation of a block's images is exactly 0
 //    or exactly clip (the steady state of the challenge networks), a row of the block is one
-//    32-bit word (bit i = image i holds clip) and a class is a boolean function of two words: its
-//    output for the four combinations (a, b) in {0, clip}^2 is a property of the class, not of the
-//    image.  alt2_pack_kernel evaluates those four outputs once per class with the same fp32 code
-//    as the float form (class_sum_alt2 + finish_output) and stores them as the truth table:
-//      bit q      (q = [a == clip] + 2 [b == clip])  output == clip
-//      bit 4 + q                                    output is neither 0 nor clip
+//    32-bit word (bit i = image i holds clip) and a class is a boolean function of two words.  All
+//    classes of an ALT2 layer share K, the weight, the bias and the clip, so the output for the
+//    four combinations (a, b) in {0, clip}^2 is a property of the LAYER.  alt2_pack_kernel evaluates
+//    those four outputs with the same fp32 code as the float form (class_sum_alt2 + finish_output)
+//    and stores them as the truth table, one byte per combination q = [a == clip] + 2 [b == clip]:
+//      bit 7 of byte q   output == clip
+//      bit 6 of byte q   output is neither 0 nor clip
+//    (the top bit of a byte, because prmt.b32 can spread it over a word in one instruction).
 //    The kernel then applies a layer to all images of a block with a few logic instructions per
 //    class.  It does so a group of layers at a time, writing every layer's words to the next
 //    buffer of a small ring and checking only at the end of the group that no image met a
@@ -48,42 +51,58 @@ static __global__ void alt2_pack_kernel(const ResLayer *layers, int stride, unsi
     const int classes = blob[0], k = blob[1];
     const float w = __int_as_float(blob[2]);
     unsigned char *rec = out + (size_t)blockIdx.x * stride;
-    if (threadIdx.x == 0) *reinterpret_cast<int4 *>(rec) = make_int4(classes, k, blob[2], 0);
+    if (threadIdx.x == 0) {
+        const float4 s = class_sum_alt2<0>(make_float4(0.0f, clip, 0.0f, clip), make_float4(0.0f, 0.0f, clip, clip), k, w, false);
+        const float y[4] = {finish_output(s.x, bias, clip), finish_output(s.y, bias, clip), finish_output(s.z, bias, clip),
+                            finish_output(s.w, bias, clip)};
+        unsigned int tt = 0u;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (y[q] == clip) tt |= 0x80u << (8 * q);
+            else if (y[q] != 0.0f) tt |= 0x40u << (8 * q);
+        }
+        *reinterpret_cast<int4 *>(rec) = make_int4(classes, k, blob[2], (int)tt);
+    }
     const int slots = (stride - 16) / 8;
     for (int u = threadIdx.x; u < slots; u += blockDim.x) {
-        uint2 e = make_uint2(0u, 0u);        // a class past the end: rows 0, truth table 0
+        uint2 e = make_uint2(0u, 0u);        // a class past the end reads row 0 twice; its output row is never read
         if (u < classes) {
-            const float4 s = class_sum_alt2<0>(make_float4(0.0f, clip, 0.0f, clip), make_float4(0.0f, 0.0f, clip, clip), k, w, false);
-            const float y[4] = {finish_output(s.x, bias, clip), finish_output(s.y, bias, clip), finish_output(s.z, bias, clip),
-                                finish_output(s.w, bias, clip)};
-            unsigned int tt = 0u;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                if (y[q] == clip) tt |= 1u << q;
-                else if (y[q] != 0.0f) tt |= 16u << q;
-            }
-            e.x = (unsigned int)(blob[4 + 4 * u] * 4) | ((unsigned int)(blob[4 + 4 * u + 1] * 4) << 16);
-            e.y = tt;
+            // the blob names rows of the float buffers, which are permuted (resident_phys_row, an involution)
+            const int pa = blob[4 + 4 * u], pb = blob[4 + 4 * u + 1];
+            e.x = (unsigned int)(resident_phys_row(pa) * 4) | ((unsigned int)(resident_phys_row(pb) * 4) << 16);
+            e.y = (unsigned int)(pa * 4) | ((unsigned int)(pb * 4) << 16);
         }
         *reinterpret_cast<uint2 *>(rec + alt2_entry_offset(u)) = e;
     }
 }
 
-// Applies a two-input truth table (4 bits of tt, index = [a] + 2 [b]) to 32 images at once.
-__device__ __forceinline__ unsigned int apply_truth(unsigned int wa, unsigned int wb, unsigned int tt) {
-    int m0, m1, m2, m3;      // bit q of tt spread over a word: bfe.s32 of one bit sign-extends it
-    asm("bfe.s32 %0, %1, 0, 1;" : "=r"(m0) : "r"(tt));
-    asm("bfe.s32 %0, %1, 1, 1;" : "=r"(m1) : "r"(tt));
-    asm("bfe.s32 %0, %1, 2, 1;" : "=r"(m2) : "r"(tt));
-    asm("bfe.s32 %0, %1, 3, 1;" : "=r"(m3) : "r"(tt));
-    const unsigned int t0 = (wa & (unsigned int)m1) | (~wa & (unsigned int)m0);
-    const unsigned int t1 = (wa & (unsigned int)m3) | (~wa & (unsigned int)m2);
+// The truth table of a layer as eight 32-bit masks: prmt.b32 with selector nibble 8 | q copies
+// the top bit of byte q over every byte of the result, so one instruction per combination makes
+// its mask (hi[q]: output == clip; ns[q], from the table shifted left by one: output unsaturated).
+// All of this runs on the integer ALU; bit-field extract and population count go through the
+// slow special-function pipe and are avoided.
+__device__ __forceinline__ unsigned int spread_top_bit(unsigned int tt, unsigned int selector) {
+    unsigned int r;
+    asm("prmt.b32 %0, %1, %1, %2;" : "=r"(r) : "r"(tt), "r"(selector));
+    return r;
+}
+struct TruthMasks {
+    unsigned int hi[4], ns[4];
+};
+__device__ __forceinline__ TruthMasks truth_masks(unsigned int tt) {
+    TruthMasks m;
+    m.hi[0] = spread_top_bit(tt, 0x8888u); m.hi[1] = spread_top_bit(tt, 0x9999u);
+    m.hi[2] = spread_top_bit(tt, 0xAAAAu); m.hi[3] = spread_top_bit(tt, 0xBBBBu);
+    m.ns[0] = spread_top_bit(tt << 1, 0x8888u); m.ns[1] = spread_top_bit(tt << 1, 0x9999u);
+    m.ns[2] = spread_top_bit(tt << 1, 0xAAAAu); m.ns[3] = spread_top_bit(tt << 1, 0xBBBBu);
+    return m;
+}
+// 32 images at once: the mask of combination [a] + 2 [b], selected bit by bit.
+__device__ __forceinline__ unsigned int select4(unsigned int wa, unsigned int wb, const unsigned int (&m)[4]) {
+    const unsigned int t0 = (wa & m[1]) | (~wa & m[0]);
+    const unsigned int t1 = (wa & m[3]) | (~wa & m[2]);
     return (wb & t1) | (~wb & t0);
 }
-
-// resident_phys_row(64 p + q) for q < 64, given pq = resident_phys_row(q): the parity of the upper
-// bits splits into the parities of p and of q >> 1.
-__device__ __forceinline__ int alt2_out_row(int p, int pq) { return (p << 6) + (pq ^ (__popc((unsigned int)p) & 1)); }
 
 #ifndef SPDNN_ALT2_MIN_BLOCKS
 #define SPDNN_ALT2_MIN_BLOCKS 4      // blocks per SM asked of the compiler: <= 64 registers, no spills
@@ -139,7 +158,9 @@ __global__ void __launch_bounds__(kThreads, SPDNN_ALT2_MIN_BLOCKS) alt2_kernel(c
             const int lim = min((li >> gshift) + tring, ngroups);
             while (next_group < lim) {
                 const int l0 = next_group << gshift, cnt = min(1 << gshift, a.nlayers - l0);
+#ifdef SPDNN_ALT2_PROXY_FENCE
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#endif
                 bulk_load_table(tbl0 + (size_t)(next_group & (tring - 1)) * group_bytes, a.stream + (size_t)l0 * stride,
                                 (unsigned int)(cnt * stride), &s_bar[next_group & (tring - 1)]);
                 ++next_group;
@@ -223,7 +244,7 @@ __global__ void __launch_bounds__(kThreads, SPDNN_ALT2_MIN_BLOCKS) alt2_kernel(c
                 m <<= sub * IPT;
 #pragma unroll
                 for (int s = 1; s < LPC; s <<= 1) m |= __shfl_xor_sync(0xffffffffu, m, s);
-                if (sub == 0 && r < a.buf_rows) w[r] = m;
+                if (sub == 0 && r < a.buf_rows) w[resident_phys_row(r)] = m;       // words are kept by plain row number
             }
         };
         // ---- the layers of this chunk
@@ -248,10 +269,11 @@ __global__ void __launch_bounds__(kThreads, SPDNN_ALT2_MIN_BLOCKS) alt2_kernel(c
                     int done_classes = last_classes;
                     int careful = 0;             // layers still to be applied one at a time
                     int par = 0;
-                    const int pq1 = resident_phys_row(lane), pq2 = resident_phys_row(lane + 32);
-                    const int p0 = multi ? warp : 0, pstep = multi ? NT / 32 : 1;
+                    int waited_group = -1;                   // the group of tables these threads have seen arrive
+                    unsigned int tt_cur = 0xffffffffu;       // no truth table has this value
+                    TruthMasks tm = truth_masks(0u);
                     while (li < a.nlayers) {
-                        if (STAGED) {
+                        if (STAGED && (li >> gshift) != waited_group) {
                             if (tid == 0) issue_groups(li);
                             const bool arrived = wait_table(li);
                             // one verdict for all workers, so that they leave the loop together
@@ -259,37 +281,97 @@ __global__ void __launch_bounds__(kThreads, SPDNN_ALT2_MIN_BLOCKS) alt2_kernel(c
                                 s_fail = 1;
                                 break;
                             }
+                            waited_group = li >> gshift;
                         }
                         int cnt = min(a.wring - 1, a.nlayers - li);
                         if (STAGED) cnt = min(cnt, (1 << gshift) - (li & gmask));
                         if (careful > 0) cnt = 1;
                         const unsigned char *T = table_of(li);
+                        // The layers of a group are applied with one truth table: lane g looks at layer g's, and
+                        // a group whose layers differ (another K or weight) is cut down to its first layer.
+                        {
+                            const unsigned char *hp = T + (size_t)(lane < cnt ? lane : 0) * stride + 12;
+                            const unsigned int tl = STAGED ? *reinterpret_cast<const unsigned int *>(hp) : __ldg(reinterpret_cast<const unsigned int *>(hp));
+                            const unsigned int t0 = __shfl_sync(0xffffffffu, tl, 0);
+                            const bool same = multi ? __syncthreads_and(tl == t0 ? 1 : 0) != 0 : __all_sync(0xffffffffu, tl == t0);
+                            if (!same) cnt = 1;
+                            if (t0 != tt_cur) {
+                                tt_cur = t0;
+                                tm = truth_masks(t0);
+                            }
+                        }
                         const unsigned int keep = force_dead ? alive : 0xffffffffu;
                         unsigned int ns = 0u, acc = 0u;
-                        int s = ws, classes = 0;
-                        for (int g = 0; g < cnt; ++g) {
-                            const unsigned char *wc = reinterpret_cast<const unsigned char *>(wring0 + (size_t)s * a.rows_w);
-                            s = (s + 1 == a.wring) ? 0 : s + 1;
-                            unsigned int *wn = wring0 + (size_t)s * a.rows_w;
-                            const unsigned char *Tg = T + (size_t)g * stride;
-                            classes = STAGED ? *reinterpret_cast<const int *>(Tg) : __ldg(reinterpret_cast<const int *>(Tg));
-                            const int passes = (classes + 63) >> 6;
-                            acc = 0u;
-                            for (int p = p0; p < passes; p += pstep) {
-                                const uint4 *slot = reinterpret_cast<const uint4 *>(Tg + 16 + p * 512) + lane;
-                                const uint4 e = STAGED ? *slot : __ldg(slot);
+                        int s = ws;
+                        const int wbytes = a.rows_w * 4;
+                        unsigned char *const wbase = reinterpret_cast<unsigned char *>(wring0);
+                        unsigned char *const wend = wbase + (size_t)a.wring * wbytes;
+                        const unsigned char *wc = wbase + (size_t)s * wbytes;
+                        unsigned int o1 = 0u, o2 = 0u;
+                        if (!multi) {
+                            // one pass of 64 classes: lane owns classes lane and lane + 32, whose words sit at
+                            // lane * 4 and lane * 4 + 128 of a buffer (plain row numbers, see rows_to_bits).
+                            // A slot past the layer's classes reads row 0 twice and writes a row nobody reads;
+                            // its bits can only add to `ns` (a needless return to the float form, never a
+                            // wrong one) -- an image with all-zero rows gets 0 there like everywhere else.
+                            const uint4 *slot = reinterpret_cast<const uint4 *>(T + 16) + lane;
+                            uint4 e = STAGED ? *slot : __ldg(slot);
+                            for (int g = 0; g < cnt; ++g) {
+                                slot = reinterpret_cast<const uint4 *>(reinterpret_cast<const unsigned char *>(slot) + stride);
+                                uint4 en = e;
+                                if (g + 1 < cnt) en = STAGED ? *slot : __ldg(slot);      // next layer's entries, early
                                 const unsigned int a1 = *reinterpret_cast<const unsigned int *>(wc + (e.x & 0xffffu));
                                 const unsigned int b1 = *reinterpret_cast<const unsigned int *>(wc + (e.x >> 16));
                                 const unsigned int a2 = *reinterpret_cast<const unsigned int *>(wc + (e.z & 0xffffu));
                                 const unsigned int b2 = *reinterpret_cast<const unsigned int *>(wc + (e.z >> 16));
-                                const unsigned int o1 = apply_truth(a1, b1, e.y) & keep, o2 = apply_truth(a2, b2, e.w) & keep;
-                                ns |= (apply_truth(a1, b1, e.y >> 4) | apply_truth(a2, b2, e.w >> 4)) & keep;
-                                wn[alt2_out_row(p, pq1)] = o1;       // rows past the layer's classes get 0 (empty entries)
-                                wn[alt2_out_row(p, pq2)] = o2;
-                                acc |= o1 | o2;
+                                unsigned char *wn = const_cast<unsigned char *>(wc) + wbytes;
+                                if (wn == wend) wn = wbase;
+                                o1 = select4(a1, b1, tm.hi) & keep;
+                                o2 = select4(a2, b2, tm.hi) & keep;
+                                ns |= (select4(a1, b1, tm.ns) | select4(a2, b2, tm.ns)) & keep;
+                                reinterpret_cast<unsigned int *>(wn)[lane] = o1;
+                                reinterpret_cast<unsigned int *>(wn)[lane + 32] = o2;
+                                wc = wn;
+                                e = en;
+                                __syncwarp();
                             }
-                            if (multi) __syncthreads(); else __syncwarp();
+                            s += cnt;
+                            if (s >= a.wring) s -= a.wring;
+                        } else {
+                            const unsigned char *Tg = T;
+                            for (int g = 0; g < cnt; ++g) {
+                                const int classes = STAGED ? *reinterpret_cast<const int *>(Tg) : __ldg(reinterpret_cast<const int *>(Tg));
+                                const int passes = (classes + 63) >> 6;
+                                unsigned char *wn = const_cast<unsigned char *>(wc) + wbytes;
+                                if (wn == wend) wn = wbase;
+                                o1 = 0u; o2 = 0u;
+                                for (int p = warp; p < passes; p += NT / 32) {
+                                    const uint4 *slot = reinterpret_cast<const uint4 *>(Tg + 16 + p * 512) + lane;
+                                    const uint4 e = STAGED ? *slot : __ldg(slot);
+                                    const unsigned int a1 = *reinterpret_cast<const unsigned int *>(wc + (e.x & 0xffffu));
+                                    const unsigned int b1 = *reinterpret_cast<const unsigned int *>(wc + (e.x >> 16));
+                                    const unsigned int a2 = *reinterpret_cast<const unsigned int *>(wc + (e.z & 0xffffu));
+                                    const unsigned int b2 = *reinterpret_cast<const unsigned int *>(wc + (e.z >> 16));
+                                    const unsigned int x1 = select4(a1, b1, tm.hi) & keep, x2 = select4(a2, b2, tm.hi) & keep;
+                                    ns |= (select4(a1, b1, tm.ns) | select4(a2, b2, tm.ns)) & keep;
+                                    reinterpret_cast<unsigned int *>(wn)[p * 64 + lane] = x1;
+                                    reinterpret_cast<unsigned int *>(wn)[p * 64 + 32 + lane] = x2;
+                                    o1 |= p * 64 + lane < classes ? x1 : 0u;         // a slot past the classes does not count
+                                    o2 |= p * 64 + 32 + lane < classes ? x2 : 0u;
+                                }
+                                wc = wn;
+                                Tg += stride;
+                                __syncthreads();
+                            }
+                            s += cnt;
+                            if (s >= a.wring) s -= a.wring;
                         }
+                        const unsigned char *hl = T + (size_t)(cnt - 1) * stride;      // classes of the group's last layer
+                        const int classes = STAGED ? *reinterpret_cast<const int *>(hl) : __ldg(reinterpret_cast<const int *>(hl));
+                        // outputs of the group's last layer; here a slot past the classes must not count, or an
+                        // image whose real outputs are all zero could pass for alive one layer longer
+                        if (!multi) acc = (lane < classes ? o1 : 0u) | (lane + 32 < classes ? o2 : 0u);
+                        else acc = o1 | o2;
                         // what the group did: an unsaturated output anywhere, and who is alive after it
                         unsigned int ns_any = __reduce_or_sync(0xffffffffu, ns), now = __reduce_or_sync(0xffffffffu, acc);
                         if (multi) {
@@ -331,7 +413,7 @@ __global__ void __launch_bounds__(kThreads, SPDNN_ALT2_MIN_BLOCKS) alt2_kernel(c
                 // back to floats: the rows the next float layer (or the expansion below) reads
                 const unsigned int *wcur = wring0 + (size_t)ws * a.rows_w;
                 for (int r = grp; r < a.buf_rows; r += CPI) {
-                    const unsigned int wv = wcur[r] >> (sub * IPT);
+                    const unsigned int wv = wcur[resident_phys_row(r)] >> (sub * IPT);
 #pragma unroll
                     for (int h = 0; h < NQ; ++h) {
                         const unsigned int q = wv >> (4 * h);
@@ -371,9 +453,9 @@ __global__ void __launch_bounds__(kThreads, SPDNN_ALT2_MIN_BLOCKS) alt2_kernel(c
             bool ns = false;
             const unsigned char *in = cur + sub * TB;
             for (int u = grp; u < classes; u += CPI) {
-                const uint2 *ep = reinterpret_cast<const uint2 *>(T + alt2_entry_offset(u));
-                const uint2 e = STAGED ? *ep : __ldg(ep);
-                const int ao = (int)(e.x & 0xffffu) * TI, bo = (int)(e.x >> 16) * TI;      // 4 * row * TI = row * RS
+                const unsigned int *ep = reinterpret_cast<const unsigned int *>(T + alt2_entry_offset(u) + 4);
+                const unsigned int e = STAGED ? *ep : __ldg(ep);
+                const int ao = (int)(e & 0xffffu) * TI, bo = (int)(e >> 16) * TI;      // 4 * row * TI = row * RS
                 unsigned char *out = nxt + resident_phys_row(u) * RS + sub * TB;
 #pragma unroll
                 for (int h = 0; h < NQ; ++h) {

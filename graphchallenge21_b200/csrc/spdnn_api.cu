@@ -88,8 +88,9 @@ struct spdnn {
     bool reps_only = true;             // SPDNN_REPS_ONLY=0: every launch writes all N rows
     bool exact_shortcut = true;        // SPDNN_EXACT_SHORTCUT=0 disables the exact-sum shortcut of the ALT2 form
     bool bit_form = true;              // SPDNN_BIT_FORM=0 disables the bit form of saturated activations (ALT2)
-    int table_ring_max = 4;            // SPDNN_TABLE_RING=2|4: most staged groups of ALT2 tables in flight
-    int table_group_max = 8;           // SPDNN_TABLE_GROUP=1|2|4|8: most layers one bulk copy brings
+    int table_ring_max = 2;            // SPDNN_TABLE_RING=2|4: most staged groups of ALT2 tables in flight or in use
+    int word_ring_max = 33;            // SPDNN_WORD_RING: most word buffers of the bit form (layers per group + 1)
+    int table_group_max = 32;          // SPDNN_TABLE_GROUP=1..32: most layers one bulk copy brings
     std::vector<unsigned char *> streams;   // packed ALT2 table streams of the captured schedule (one per chunk)
     bool print_schedule = false;       // SPDNN_PRINT_SCHEDULE=1: one line per launch when the graph is built
     bool resident_always = false;      // ... even for a lone layer that the per-layer kernel would serve better
@@ -98,7 +99,7 @@ struct spdnn {
     int last_group = 0;                // group size of the last captured schedule's resident launches
     int smem_optin = 0;                // shared memory one block may opt in to
     bool stage_tables = true;          // bring the per-layer tables into shared memory with bulk copies
-    int chunk_first = 8, chunk_max = 256;
+    int chunk_first = 8, chunk_max = 1024;
     int nsteps = 0;                    // launches of the last captured schedule
     std::vector<int32_t> host_died, host_live;
     int32_t *slot = nullptr;
@@ -437,9 +438,10 @@ std::vector<Step> plan_steps(spdnn *c) {
                 int tb = (blob + 127) / 128 * 128;
                 if (!(c->stage_tables && fits(ti, rows, tb))) tb = 0;
                 if (R0.mode == kResAlt2) {
-                    // packed stream: groups of up to 8 layers per bulk copy, up to 4 groups in flight (the bit
-                    // form applies a layer in far less time than a copy takes to arrive), as many word buffers
-                    // as a group has layers, plus the one it starts from -- whatever of that fits
+                    // packed stream: groups of up to 32 layers per bulk copy (what a group costs besides its
+                    // layers -- waiting for the copy, checking the result -- is spread over them), the next group
+                    // on its way while one is applied, as many word buffers as a group has layers plus the one
+                    // it starts from -- whatever of that fits
                     st.max_classes = maxc;
                     st.stride = alt2_stream_stride(maxc);
                     st.rows_w = std::max(rows, (maxc + 63) / 64 * 64);
@@ -450,11 +452,11 @@ std::vector<Step> plan_steps(spdnn *c) {
                     // staging may take a quarter of the shared memory at most, so that the blocks per SM stay
                     // what the activations allow
                     if (c->stage_tables)
-                        for (int gs = 3; gs >= 0 && !st.tring; --gs)
+                        for (int gs = 5; gs >= 0 && !st.tring; --gs)
                             for (int tr = 4; tr >= 2 && !st.tring; tr /= 2)
                                 if ((1 << gs) <= c->table_group_max && tr <= c->table_ring_max && afits(gs, tr, 2) &&
                                     (size_t)tr * ((size_t)st.stride << gs) <= (size_t)c->smem_optin / 4) { st.gshift = gs; st.tring = tr; }
-                    for (int wr = (st.tring ? (1 << st.gshift) : 8) + 1; wr > 2; --wr)
+                    for (int wr = std::min(c->word_ring_max, (st.tring ? (1 << st.gshift) : 8) + 1); wr > 2; --wr)
                         if (afits(st.gshift, st.tring, wr) && (size_t)wr * st.rows_w * 4 <= (size_t)c->smem_optin / 8) { st.wring = wr; break; }
                     if (!afits(st.gshift, st.tring, st.wring)) ti = 0;      // not even the two word buffers fit
                 }
@@ -651,7 +653,8 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
         if (const char *e = getenv("SPDNN_EXACT_SHORTCUT")) c->exact_shortcut = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BIT_FORM")) c->bit_form = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_TABLE_RING")) c->table_ring_max = atoi(e) >= 4 ? 4 : 2;
-        if (const char *e = getenv("SPDNN_TABLE_GROUP")) { const int v = atoi(e); c->table_group_max = v >= 8 ? 8 : (v >= 4 ? 4 : (v >= 2 ? 2 : 1)); }
+        if (const char *e = getenv("SPDNN_WORD_RING")) c->word_ring_max = std::max(2, std::min(33, atoi(e)));
+        if (const char *e = getenv("SPDNN_TABLE_GROUP")) c->table_group_max = std::max(1, std::min(32, atoi(e)));
         if (const char *e = getenv("SPDNN_REPS_ONLY")) c->reps_only = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_CHUNK_FIRST")) c->chunk_first = std::max(1, atoi(e));
         if (const char *e = getenv("SPDNN_CHUNK_MAX")) c->chunk_max = std::max(1, atoi(e));

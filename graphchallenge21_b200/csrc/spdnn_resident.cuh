@@ -158,13 +158,16 @@ __device__ __forceinline__ void bulk_load_table(void *dst, const void *src, unsi
                  : "memory");
 }
 
+#ifndef SPDNN_MBAR_POLL
+#define SPDNN_MBAR_POLL "try_wait"      // "test_wait": poll without the hardware's suspend
+#endif
 // Bounded wait: returns false when the copy has not landed after kMbarSpinLimit polls.
 constexpr int kMbarSpinLimit = 1 << 22;
 __device__ __forceinline__ bool mbar_wait(unsigned long long *bar, unsigned int parity) {
     for (int i = 0; i < kMbarSpinLimit; ++i) {
         unsigned int done;
         asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            "{\n\t.reg .pred p;\n\tmbarrier." SPDNN_MBAR_POLL ".parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(done)
             : "r"(smem_u32(bar)), "r"(parity)
             : "memory");
