@@ -191,7 +191,8 @@ __global__ void __launch_bounds__(kThreads, SPDNN_ALT2_MIN_BLOCKS) alt2_kernel(c
         bool load_ns = false;                    // a loaded value is neither 0 nor clip
         {
             const float *p[IPT];
-            bool contiguous = ctl.identity != 0;
+            const float *const dense = a.dense_in ? *a.dense_in : nullptr;
+            bool contiguous = ctl.identity != 0 && !dense;
 #pragma unroll
             for (int q = 0; q < IPT; ++q) {
                 const int j = j0 + sub * IPT + q;
@@ -200,12 +201,14 @@ __global__ void __launch_bounds__(kThreads, SPDNN_ALT2_MIN_BLOCKS) alt2_kernel(c
                 const int jj = v ? j : j0;
                 const int src = ctl.identity ? jj : __ldg(a.slot + jj);
                 if (!ctl.identity && grp == 0 && v) move_id(ctl, a.ids0, a.ids1, j, src);
-                p[q] = a.yin + (size_t)(src >> 5) * a.tile_stride + (src & 31);
+                p[q] = dense ? dense + (size_t)src * a.n : a.yin + (size_t)(src >> 5) * a.tile_stride + (src & 31);
             }
             if (my_valid != kFull) contiguous = false;
             const ResLayer L0 = a.layers[0];
             for (int v = grp; v < L0.v_in; v += CPI) {
-                const size_t e = L0.rep ? (size_t)__ldg(L0.rep + v) : (size_t)v * 32;
+                // element of row r: r * 32 floats into a tile's column, r floats into a row-major image
+                size_t e = L0.rep ? (size_t)__ldg(L0.rep + v) : (size_t)v * 32;
+                if (dense) e >>= 5;
                 unsigned char *dst = cur + resident_phys_row(v) * RS + sub * TB;
 #pragma unroll
                 for (int h = 0; h < NQ; ++h) {

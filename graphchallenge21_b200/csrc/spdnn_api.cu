@@ -113,8 +113,15 @@ struct spdnn {
 
     int batch = 0, first_id = 0;
     bool input_ready = false, result_ready = false, in_flight = false, prep_timed = false;
-    cudaGraphExec_t graph_exec = nullptr;
+    // One captured pass per kind of input: [0] the input is in tiles (y[0]); [1] the first launch reads the
+    // caller's row-major matrix in place (only when that launch is a resident chunk; else null).
+    cudaGraphExec_t graph_exec[2] = {nullptr, nullptr};
+    int graph_steps[2] = {0, 0}, graph_group[2] = {0, 0};
     bool graph_dirty = true;
+    bool dense_direct = true;          // SPDNN_DENSE_DIRECT=0: always convert a dense input to tiles first
+    const float **dense_cell = nullptr;     // device: address of the row-major input of the pass being set up
+    const float *dense_src = nullptr;       // ... as set by the last spdnn_set_input_dense* (null: converted to tiles)
+    int input_kind = 0;
     int cpi_override = 0, grid_override = 0;
 
     std::vector<LoopCtl> host_ctl;
@@ -193,13 +200,15 @@ int begin_input(spdnn *c, int batch, int first_global_id) {
     c->input_ready = false;
     c->result_ready = false;
     c->prep_launches = 0;
+    c->dense_src = nullptr;
+    c->input_kind = 0;
     CK(cudaEventRecord(c->ev_prep0, c->stream));
     return SPDNN_OK;
 }
 
 int end_input(spdnn *c) {
     init_loop_kernel<<<std::max(1, std::min(1024, (c->batch + 255) / 256)), 256, 0, c->stream>>>(
-        c->ctl, c->ids[0], c->batch, c->first_id, c->died_at, c->layers);
+        c->ctl, c->ids[0], c->batch, c->first_id, c->died_at, c->layers, c->dense_cell, c->dense_src);
     CK(cudaGetLastError());
     c->prep_launches += 1;
     CK(cudaEventRecord(c->ev_prep1, c->stream));
@@ -393,10 +402,14 @@ struct Step {
     // ALT2 chunk (alt2_kernel): packed table stream and its staging, word buffers of the bit form
     int stride = 0, gshift = 0, tring = 0, wring = 2, rows_w = 0, max_classes = 0;
     unsigned char *stream = nullptr;
+    bool dense = false;            // resident chunk that reads the caller's row-major input in place
 };
 
 // The launches of one pass, front to back.
-std::vector<Step> plan_steps(spdnn *c) {
+// dense_first: the pass starts from the caller's row-major input; its first launch is then a resident
+// chunk wherever one fits (Step::dense), because loading the rows into shared memory also does the change
+// of layout.
+std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
     std::vector<Step> plan;
     int l = 0, chunk = c->chunk_first;
     while (l < c->layers) {
@@ -415,13 +428,20 @@ std::vector<Step> plan_steps(spdnn *c) {
             static const int kGeneric[][2] = {{16, 4}, {8, 4}, {4, 4}};
             const int (*cand)[2] = R0.mode == kResAlt2 ? kAlt2 : kGeneric;
             const int ncand = R0.mode == kResAlt2 ? 5 : 3;
-            for (int q = 0; q < ncand; ++q) {
-                const int t_i = cand[q][0], i_pt = cand[q][1];
-                if (t_i > c->res_ti_max || i_pt > c->res_ipt_max || !fits(t_i, rows, 0)) continue;
-                if (i_pt == 8 && R0.classes * 2 < kThreads * i_pt / t_i) continue;
-                ti = t_i; ipt = i_pt;
-                break;
-            }
+            // Reading the input in place pays only with several blocks of at least 8 images per SM, so
+            // that one block's loads overlap another's arithmetic: the first launch of such a pass takes the
+            // largest group that leaves room for three blocks, and if there is none the pass is not built.
+            bool dense_here = false;
+            for (int pass = (l == 0 && dense_first) ? 0 : 1; pass < 2 && !ti; ++pass)
+                for (int q = 0; q < ncand; ++q) {
+                    const int t_i = cand[q][0], i_pt = cand[q][1];
+                    if (t_i > c->res_ti_max || i_pt > c->res_ipt_max || !fits(t_i, rows, 0)) continue;
+                    if (i_pt == 8 && R0.classes * 2 < kThreads * i_pt / t_i) continue;
+                    if (pass == 0 && (t_i < 8 || resident_smem_bytes(t_i, rows, 0) * 3 > (size_t)c->smem_optin)) continue;
+                    ti = t_i; ipt = i_pt;
+                    dense_here = (pass == 0);
+                    break;
+                }
             if (ti) {
                 // extend while the layers are of one kernel variant and the group still fits
                 int f = 1, blob = R0.blob_bytes, maxc = R0.classes;
@@ -454,7 +474,7 @@ std::vector<Step> plan_steps(spdnn *c) {
                     if (c->stage_tables)
                         for (int gs = 5; gs >= 0 && !st.tring; --gs)
                             for (int tr = 4; tr >= 2 && !st.tring; tr /= 2)
-                                if ((1 << gs) <= c->table_group_max && tr <= c->table_ring_max && afits(gs, tr, 2) &&
+                                if ((1 << gs) <= c->table_group_max && ((1 << gs) < 2 * f || gs == 0) && tr <= c->table_ring_max && afits(gs, tr, 2) &&
                                     (size_t)tr * ((size_t)st.stride << gs) <= (size_t)c->smem_optin / 4) { st.gshift = gs; st.tring = tr; }
                     for (int wr = std::min(c->word_ring_max, (st.tring ? (1 << st.gshift) : 8) + 1); wr > 2; --wr)
                         if (afits(st.gshift, st.tring, wr) && (size_t)wr * st.rows_w * 4 <= (size_t)c->smem_optin / 8) { st.wring = wr; break; }
@@ -463,8 +483,11 @@ std::vector<Step> plan_steps(spdnn *c) {
                 // A lone layer that reads all N rows of every image but computes few classes from
                 // them (the first layer of a network with repeated columns) gains nothing from
                 // staging the rows in shared memory: gather straight from global memory instead.
-                const bool lone_wide = (f == 1 && R0.v_in == c->n && R0.classes * 2 <= c->n && !c->resident_always);
-                if (!lone_wide && ti) { st.count = f; st.ti = ti; st.ipt = ipt; st.rows = rows; st.table = tb; }
+                const bool lone_wide = (f == 1 && R0.v_in == c->n && R0.classes * 2 <= c->n && !c->resident_always) && !dense_here;
+                if (!lone_wide && ti) {
+                    st.count = f; st.ti = ti; st.ipt = ipt; st.rows = rows; st.table = tb;
+                    st.dense = dense_here;
+                }
             }
         }
         if (st.ti) chunk = std::min(chunk * 2, c->chunk_max);
@@ -497,6 +520,7 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan) {
             a.counter = c->counter; a.work = c->counter + 1; a.status = c->status;
             a.layers = c->res_table + l; a.died_at = c->died_at + l; a.nlayers = st.count;
             a.buf_rows = st.rows; a.table_bytes = st.table;
+            a.dense_in = st.dense ? c->dense_cell : nullptr;
             a.stream = st.stream; a.stream_stride = st.stride; a.tgroup_shift = st.gshift; a.tring = st.tring;
             a.wring = st.wring; a.rows_w = st.rows_w; a.bit_multi = st.max_classes > 64 ? 1 : 0;
             a.n = c->n; a.bias = c->bias; a.clip = c->clip;
@@ -518,6 +542,7 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan) {
                 fprintf(stderr, "[spdnn] step %zu: resident layers %d..%d  group %d images (%d per thread)  %s  rows %d (v_in %d, classes %d)  smem %zu B  tables %s%s\n",
                         step, l, l + st.count - 1, st.ti, st.ipt, R0.mode == kResAlt2 ? "ALT2" : "GENERIC", st.rows, R0.v_in,
                         R0.classes, smem, tables_txt, next_resident ? "  writes representatives only" : "");
+            if (c->print_schedule && st.dense) fprintf(stderr, "[spdnn]         reads the row-major input in place\n");
         } else {
             LayerDesc d;
             d.off = L.off; d.vals = L.vals;
@@ -557,17 +582,11 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan) {
     return SPDNN_OK;
 }
 
-int build_graph(spdnn *c) {
-    if (c->graph_exec) { cudaGraphExecDestroy(c->graph_exec); c->graph_exec = nullptr; }
-    cudaGraph_t g = nullptr;
-    {
-        int rc0 = prepare_resident(c);
-        if (rc0) return rc0;
-    }
-    // the launches of a pass, and (outside the capture) the packed table stream of every ALT2 chunk
-    std::vector<Step> plan = plan_steps(c);
-    for (unsigned char *p : c->streams) cudaFree(p);
-    c->streams.clear();
+// Captures the launches of one pass for one kind of input (0: tiles, 1: row-major read in place).
+int build_graph_kind(spdnn *c, int kind) {
+    std::vector<Step> plan = plan_steps(c, kind == 1);
+    if (kind == 1 && !(plan[0].ti && plan[0].dense)) return SPDNN_OK;      // no resident first launch: kind 0 serves
+    // outside the capture: the packed table stream of every ALT2 chunk
     for (Step &st : plan) {
         if (!st.ti || c->res[st.first]->mode != kResAlt2) continue;
         if (st.rows > 16383) return fail(c, SPDNN_ERR_LIMIT, "layer %d: %d rows do not fit a packed table entry", st.first, st.rows);
@@ -577,16 +596,43 @@ int build_graph(spdnn *c) {
         CK(cudaGetLastError());
     }
     CK(cudaStreamSynchronize(c->stream));
+    cudaGraph_t g = nullptr;
     CK(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
     int rc = enqueue_layers(c, plan);
     cudaError_t e = cudaStreamEndCapture(c->stream, &g);
     if (rc) { if (g) cudaGraphDestroy(g); return rc; }
     if (e != cudaSuccess) return fail(c, SPDNN_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
-    e = cudaGraphInstantiate(&c->graph_exec, g, 0);
+    e = cudaGraphInstantiate(&c->graph_exec[kind], g, 0);
     cudaGraphDestroy(g);
     if (e != cudaSuccess) return fail(c, SPDNN_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
+    c->graph_steps[kind] = c->nsteps;
+    c->graph_group[kind] = c->last_group;
+    return SPDNN_OK;
+}
+
+int build_graph(spdnn *c) {
+    for (int kind = 0; kind < 2; ++kind)
+        if (c->graph_exec[kind]) { cudaGraphExecDestroy(c->graph_exec[kind]); c->graph_exec[kind] = nullptr; }
+    for (unsigned char *p : c->streams) cudaFree(p);
+    c->streams.clear();
+    int rc = prepare_resident(c);
+    if (rc) return rc;
+    rc = build_graph_kind(c, 0);
+    if (rc) return rc;
+    if (c->dense_direct && c->resident) {
+        rc = build_graph_kind(c, 1);
+        if (rc) return rc;
+    }
     c->graph_dirty = false;
     return SPDNN_OK;
+}
+
+// Builds the graphs if every layer has been set; returns false (without an error) when it cannot yet.
+bool graphs_ready(spdnn *c) {
+    if (!c->graph_dirty) return true;
+    for (int l = 0; l < c->layers; ++l)
+        if (!c->layer[l]) return false;
+    return build_graph(c) == SPDNN_OK;
 }
 
 struct DeviceGuard {
@@ -631,6 +677,8 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
     CK(cudaMalloc(&c->counter, 2 * sizeof(unsigned int)));
     CK(cudaMemset(c->counter, 0, 2 * sizeof(unsigned int)));
     CK(cudaMalloc(&c->status, sizeof(int32_t)));
+    CK(cudaMalloc(&c->dense_cell, sizeof(const float *)));
+    CK(cudaMemset(c->dense_cell, 0, sizeof(const float *)));
     CK(cudaMemset(c->status, 0, sizeof(int32_t)));
     CK(cudaMalloc(&c->died_at, sizeof(int32_t) * (size_t)layers));
     CK(cudaMemset(c->died_at, 0, sizeof(int32_t) * (size_t)layers));
@@ -652,6 +700,7 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
         if (const char *e = getenv("SPDNN_PRINT_SCHEDULE")) c->print_schedule = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_EXACT_SHORTCUT")) c->exact_shortcut = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BIT_FORM")) c->bit_form = atoi(e) != 0;
+        if (const char *e = getenv("SPDNN_DENSE_DIRECT")) c->dense_direct = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_TABLE_RING")) c->table_ring_max = atoi(e) >= 4 ? 4 : 2;
         if (const char *e = getenv("SPDNN_WORD_RING")) c->word_ring_max = std::max(2, std::min(33, atoi(e)));
         if (const char *e = getenv("SPDNN_TABLE_GROUP")) c->table_group_max = std::max(1, std::min(32, atoi(e)));
@@ -668,7 +717,9 @@ void spdnn_destroy(spdnn_t *c) {
     if (!c) return;
     DeviceGuard guard(c->device);
     if (c->stream) cudaStreamSynchronize(c->stream);
-    if (c->graph_exec) cudaGraphExecDestroy(c->graph_exec);
+    for (int kind = 0; kind < 2; ++kind)
+        if (c->graph_exec[kind]) cudaGraphExecDestroy(c->graph_exec[kind]);
+    cudaFree(c->dense_cell);
     free_buffers(c);
     cudaFree(c->ctl); cudaFree(c->counter); cudaFree(c->status); cudaFree(c->stage);
     cudaFree(c->died_at); cudaFree(c->res_table);
@@ -790,6 +841,11 @@ int spdnn_set_input_dense_device(spdnn_t *c, const float *y0_dev, int batch, int
     DeviceGuard guard(c->device);
     int rc = begin_input(c, batch, first_global_id);
     if (rc) return rc;
+    if (batch > 0 && graphs_ready(c) && c->graph_exec[1]) {
+        c->dense_src = y0_dev;       // read in place by the first launch of the pass
+        c->input_kind = 1;
+        return end_input(c);
+    }
     rc = convert_dense_device(c, y0_dev, batch, 0);
     if (rc) return rc;
     return end_input(c);
@@ -801,8 +857,17 @@ int spdnn_set_input_dense(spdnn_t *c, const float *y0, int batch, int first_glob
     DeviceGuard guard(c->device);
     int rc = begin_input(c, batch, first_global_id);
     if (rc) return rc;
-    // staged through a device buffer in chunks of whole tiles
     const size_t row_bytes = sizeof(float) * (size_t)c->n;
+    if (batch > 0 && (size_t)batch * row_bytes <= ((size_t)1 << 30) && graphs_ready(c) && c->graph_exec[1]) {
+        // one copy into the staging buffer, which the first launch of the pass reads in place
+        rc = ensure_stage(c, (size_t)batch * row_bytes);
+        if (rc) return rc;
+        CK(cudaMemcpyAsync(c->stage, y0, (size_t)batch * row_bytes, cudaMemcpyHostToDevice, c->stream));
+        c->dense_src = (const float *)c->stage;
+        c->input_kind = 1;
+        return end_input(c);
+    }
+    // staged through a device buffer in chunks of whole tiles
     size_t chunk_rows = std::max<size_t>(32, ((size_t)512 << 20) / row_bytes / 32 * 32);
     chunk_rows = std::min<size_t>(chunk_rows, (size_t)(batch + 31) / 32 * 32);
     if (batch > 0) {
@@ -861,7 +926,11 @@ int spdnn_infer_async(spdnn_t *c) {
         if (rc) return rc;
     }
     CK(cudaEventRecord(c->ev_inf0, c->stream));
-    CK(cudaGraphLaunch(c->graph_exec, c->stream));
+    if (c->input_kind == 1 && !c->graph_exec[1])
+        return fail(c, SPDNN_ERR_STATE, "the network changed after the input was set: set the input again");
+    c->nsteps = c->graph_steps[c->input_kind];
+    c->last_group = c->graph_group[c->input_kind];
+    CK(cudaGraphLaunch(c->graph_exec[c->input_kind], c->stream));
     CK(cudaEventRecord(c->ev_inf1, c->stream));
     c->input_ready = false;
     c->in_flight = true;

@@ -377,8 +377,10 @@ static __global__ void finalize_ids_kernel(const LoopCtl *ctl, const int32_t *__
         move_id(c, ids0, ids1, j, __ldg(slot + j));
 }
 
+// dense_cell: where the first launch of a pass finds the caller's row-major input when that launch
+// reads it in place (dense_src, may be null: the input was converted to tiles).
 static __global__ void init_loop_kernel(LoopCtl *ctl, int32_t *ids0, int batch, int first_global_id, int32_t *died_at,
-                                        int layers) {
+                                        int layers, const float **dense_cell, const float *dense_src) {
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < batch; i += gridDim.x * blockDim.x)
         ids0[i] = first_global_id + i;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < layers; i += gridDim.x * blockDim.x) died_at[i] = 0;
@@ -386,6 +388,7 @@ static __global__ void init_loop_kernel(LoopCtl *ctl, int32_t *ids0, int batch, 
         LoopCtl c;
         c.live = batch; c.identity = 1; c.ids_buf = 0; c.reserved = 0;
         *ctl = c;
+        *dense_cell = dense_src;
     }
 }
 

@@ -86,6 +86,10 @@ struct ResArgs {
     int rows_w;               // bit form: words per buffer (>= buf_rows, covers all 64-class passes)
     int bit_ok;               // bit form allowed (clip > 0, not switched off)
     int bit_multi;            // bit form: some layer of the chunk has more than 64 classes
+    // First launch of a pass that reads the caller's row-major input (batch x n floats) in place: the cell
+    // that holds its address (init_loop_kernel), else nullptr (the input is in yin, in tiles).  Loading the
+    // block's rows into shared memory does the change of layout that dense_to_tiles_kernel would do.
+    const float *const *dense_in;
 };
 
 __host__ __device__ __forceinline__ int resident_phys_row(int r) {
@@ -268,6 +272,9 @@ __device__ __forceinline__ float finish_output(float sum, float bias, float clip
 #ifndef SPDNN_GENERIC_THREADS
 #define SPDNN_GENERIC_THREADS 512
 #endif
+#ifndef SPDNN_GENERIC_MIN_BLOCKS
+#define SPDNN_GENERIC_MIN_BLOCKS 2      // <= 64 registers: two blocks of 16 warps per SM where the shared memory allows
+#endif
 template <int MODE>
 struct ResThreads {
     static constexpr int value = (MODE == kResAlt2) ? kThreads : SPDNN_GENERIC_THREADS;
@@ -276,7 +283,7 @@ struct ResThreads {
 // step, which halves the per-layer bookkeeping (barrier, table wait, loop control, addresses)
 // per image; it is used for the light ALT2 form.
 template <int TI, int IPT, int MODE, int KT, bool UNIFORM, bool STAGED>
-__global__ void __launch_bounds__(ResThreads<MODE>::value, 1)
+__global__ void __launch_bounds__(ResThreads<MODE>::value, SPDNN_GENERIC_MIN_BLOCKS)
 resident_kernel(const ResArgs a) {
     constexpr int NT = ResThreads<MODE>::value;
     extern __shared__ __align__(16) unsigned char smem[];
@@ -315,7 +322,8 @@ resident_kernel(const ResArgs a) {
         unsigned int my_valid = 0;
         {
             const float *p[IPT];
-            bool contiguous = ctl.identity != 0;
+            const float *const dense = a.dense_in ? *a.dense_in : nullptr;
+            bool contiguous = ctl.identity != 0 && !dense;
 #pragma unroll
             for (int q = 0; q < IPT; ++q) {
                 const int j = j0 + sub * IPT + q;
@@ -324,12 +332,14 @@ resident_kernel(const ResArgs a) {
                 const int jj = v ? j : j0;
                 const int src = ctl.identity ? jj : __ldg(a.slot + jj);
                 if (!ctl.identity && grp == 0 && v) move_id(ctl, a.ids0, a.ids1, j, src);
-                p[q] = a.yin + (size_t)(src >> 5) * a.tile_stride + (src & 31);
+                p[q] = dense ? dense + (size_t)src * a.n : a.yin + (size_t)(src >> 5) * a.tile_stride + (src & 31);
             }
             if (my_valid != kFull) contiguous = false;
             const ResLayer L0 = a.layers[0];
             for (int v = grp; v < L0.v_in; v += CPI) {
-                const size_t e = L0.rep ? (size_t)__ldg(L0.rep + v) : (size_t)v * 32;
+                // element of row r: r * 32 floats into a tile's column, r floats into a row-major image
+                size_t e = L0.rep ? (size_t)__ldg(L0.rep + v) : (size_t)v * 32;
+                if (dense) e >>= 5;
                 unsigned char *dst = cur + resident_phys_row(v) * RS + sub * TB;
 #pragma unroll
                 for (int h = 0; h < NQ; ++h) {
