@@ -428,18 +428,22 @@ std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
             static const int kGeneric[][2] = {{16, 4}, {8, 4}, {4, 4}};
             const int (*cand)[2] = R0.mode == kResAlt2 ? kAlt2 : kGeneric;
             const int ncand = R0.mode == kResAlt2 ? 5 : 3;
-            // Reading the input in place pays only with several blocks of at least 8 images per SM, so
-            // that one block's loads overlap another's arithmetic: the first launch of such a pass takes the
-            // largest group that leaves room for three blocks, and if there is none the pass is not built.
+            // First launch of a pass that reads the input in place.  A layer that reads all N rows to compute
+            // few classes is mostly loading: it pays only with several blocks of at least 8 images per SM, so
+            // that one block's loads overlap another's arithmetic -- it takes the largest group that leaves
+            // room for three blocks, and if there is none this kind of pass is not built.  Any other first
+            // chunk keeps the group size that suits its arithmetic.
+            const bool dense_wanted = (l == 0 && dense_first);
+            const bool wide_few = (R0.v_in == c->n && R0.classes * 2 <= c->n);
             bool dense_here = false;
-            for (int pass = (l == 0 && dense_first) ? 0 : 1; pass < 2 && !ti; ++pass)
+            for (int pass = (dense_wanted && wide_few) ? 0 : 1; pass < 2 && !ti; ++pass)
                 for (int q = 0; q < ncand; ++q) {
                     const int t_i = cand[q][0], i_pt = cand[q][1];
                     if (t_i > c->res_ti_max || i_pt > c->res_ipt_max || !fits(t_i, rows, 0)) continue;
                     if (i_pt == 8 && R0.classes * 2 < kThreads * i_pt / t_i) continue;
                     if (pass == 0 && (t_i < 8 || resident_smem_bytes(t_i, rows, 0) * 3 > (size_t)c->smem_optin)) continue;
                     ti = t_i; ipt = i_pt;
-                    dense_here = (pass == 0);
+                    dense_here = dense_wanted && (pass == 0 || !wide_few);
                     break;
                 }
             if (ti) {

@@ -263,6 +263,49 @@ __device__ __forceinline__ float finish_output(float sum, float bias, float clip
     return fminf(fmaxf(__fadd_rn(sum, bias), 0.0f), clip);
 }
 
+// Load phase of a first launch that reads the caller's row-major input in place, for layers whose
+// value ids are the neurons themselves: image j0 + i, rows [0, rows) -> cur[phys_row(r)][i].
+// A warp covers 32 / TI groups of four consecutive rows for each of the TI images with one 16-byte
+// load per lane (4 * 32 / TI lanes read 16 * 32 / TI contiguous bytes of an image), all loads of a
+// thread in flight before its stores; the scattered 4-byte stores are the change of layout.
+// Requires n % 4 == 0 and a 16-byte aligned base.  Returns whether any loaded value is neither 0
+// nor clip.
+template <int TI, int NT>
+__device__ __forceinline__ bool load_dense_rows(const float *dense, int n, int j0, int live_in, int rows, unsigned char *cur,
+                                                float clip) {
+    constexpr int RS = TI * 4;
+    constexpr int GPW = 32 / TI;                 // groups of four rows per warp and step
+    constexpr int STEP = (NT / 32) * GPW * 4;    // rows the block covers per step
+    constexpr int UNR = 4;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int i = lane % TI, g = lane / TI;
+    const bool valid = j0 + i < live_in;
+    const float *src = dense + (size_t)(valid ? j0 + i : j0) * n;
+    bool ns = false;
+    for (int r0 = (warp * GPW + g) * 4; r0 < rows; r0 += STEP * UNR) {
+        float4 x[UNR];
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            const int r = r0 + u * STEP;
+            x[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (valid && r < rows) x[u] = __ldg(reinterpret_cast<const float4 *>(src + r));
+        }
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            const int r = r0 + u * STEP;
+            if (r < rows) {
+                *reinterpret_cast<float *>(cur + resident_phys_row(r + 0) * RS + i * 4) = x[u].x;
+                *reinterpret_cast<float *>(cur + resident_phys_row(r + 1) * RS + i * 4) = x[u].y;
+                *reinterpret_cast<float *>(cur + resident_phys_row(r + 2) * RS + i * 4) = x[u].z;
+                *reinterpret_cast<float *>(cur + resident_phys_row(r + 3) * RS + i * 4) = x[u].w;
+                ns |= (x[u].x != 0.0f && x[u].x != clip) || (x[u].y != 0.0f && x[u].y != clip) || (x[u].z != 0.0f && x[u].z != clip) ||
+                      (x[u].w != 0.0f && x[u].w != clip);
+            }
+        }
+    }
+    return ns;
+}
+
 // Grid: one block per TI live images (launched for the worst case; surplus blocks only take
 // part in the last-block ticket).  Dynamic shared memory: two activation buffers of
 // buf_rows * TI * 4 bytes, then (STAGED) two table buffers of table_bytes each.
@@ -336,7 +379,9 @@ resident_kernel(const ResArgs a) {
             }
             if (my_valid != kFull) contiguous = false;
             const ResLayer L0 = a.layers[0];
-            for (int v = grp; v < L0.v_in; v += CPI) {
+            const bool fast_dense = dense && !L0.rep && L0.v_in == a.n && (a.n & 3) == 0 && (reinterpret_cast<size_t>(dense) & 15) == 0;
+            if (fast_dense) load_dense_rows<TI, NT>(dense, a.n, j0, live_in, L0.v_in, cur, a.clip);
+            for (int v = grp; v < L0.v_in && !fast_dense; v += CPI) {
                 // element of row r: r * 32 floats into a tile's column, r floats into a row-major image
                 size_t e = L0.rep ? (size_t)__ldg(L0.rep + v) : (size_t)v * 32;
                 if (dense) e >>= 5;

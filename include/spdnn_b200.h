@@ -84,7 +84,11 @@ int spdnn_set_layer_coo(spdnn_t *ctx, int layer, int64_t nnz, const int32_t *in_
  * first_global_id + i.  Replaces the H2D upload of A_d. */
 int spdnn_set_input_dense(spdnn_t *ctx, const float *y0, int batch, int first_global_id);
 
-/* Same, from a DEVICE buffer on the context's GPU (inputs already resident in HBM). */
+/* Same, from a DEVICE buffer on the context's GPU (inputs already resident in HBM).  The buffer
+ * may be read in place by the inference pass that follows (when its first launch can take a
+ * row-major matrix; otherwise it is converted to the internal layout here): keep it unchanged
+ * until that pass has finished (spdnn_infer returned, or spdnn_sync after spdnn_infer_async).
+ * It is never written. */
 int spdnn_set_input_dense_device(spdnn_t *ctx, const float *y0_dev, int batch, int first_global_id);
 
 /* Input images as the triplets of the reference's input file: `img neuron val`

@@ -89,6 +89,35 @@ def test_kernel_paths_agree(env, monkeypatch, oracle):
         check(run_gpu(net, y0, first=7), want)
 
 
+def test_dense_input_read_in_place(oracle):
+    """A dense input is read in place by the first launch (16-byte loads when the matrix is
+    aligned, 4-byte loads when it is not); a caller's device buffer is not modified, and the
+    same context then takes triplets (the other captured pass) with the same result."""
+    import torch
+    n, L, b = 1024, 30, 1000
+    net = SyntheticNetwork(n, L, "radix16")
+    y0 = synthetic_images(n, b)
+    want = oracle.infer(y0, [(r, None) for r in rows_of(net)], float(net.bias), first_image=3)
+    buf = torch.zeros(b * n + 8, dtype=torch.float32, device="cuda")
+    with SpDNN(n, L, float(net.bias)) as g:
+        for l in range(L):
+            g.set_layer_csc(l, *net.layer_csc(l))
+        for shift in (0, 1, 4):
+            view = buf[shift:shift + b * n].view(b, n)
+            view.copy_(torch.from_numpy(y0))
+            g.set_input_dense(view, 3)
+            res = g.infer()
+            check((g.categories().copy(), g.activations(), g.layer_live().copy(), res), want)
+            assert torch.equal(view.cpu(), torch.from_numpy(y0))
+        img, neu, val = generator.dense_to_coo_1based(y0)
+        g.set_input_coo(img, neu, val, b, 3, index_base=1)
+        res = g.infer()
+        check((g.categories().copy(), g.activations(), g.layer_live().copy(), res), want)
+        g.set_input_dense(y0, 3)                       # host matrix: staged, then read in place
+        res = g.infer()
+        check((g.categories().copy(), g.activations(), g.layer_live().copy(), res), want)
+
+
 _BIT_FORM_WANT = {}
 
 
