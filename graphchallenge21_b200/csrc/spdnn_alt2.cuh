@@ -206,7 +206,7 @@ __global__ void __launch_bounds__(kThreads, SPDNN_ALT2_MIN_BLOCKS) alt2_kernel(c
             if (my_valid != kFull) contiguous = false;
             const ResLayer L0 = a.layers[0];
             const bool fast_dense = dense && !L0.rep && L0.v_in == a.n && (a.n & 3) == 0 && (reinterpret_cast<size_t>(dense) & 15) == 0;
-            if (fast_dense) load_ns |= load_dense_rows<TI, NT>(dense, a.n, j0, live_in, L0.v_in, cur, a.clip);
+            if (fast_dense) load_ns |= load_dense_rows<TI, NT, true>(dense, a.n, j0, live_in, L0.v_in, cur, a.clip);
             for (int v = grp; v < L0.v_in && !fast_dense; v += CPI) {
                 // element of row r: r * 32 floats into a tile's column, r floats into a row-major image
                 size_t e = L0.rep ? (size_t)__ldg(L0.rep + v) : (size_t)v * 32;

@@ -118,7 +118,8 @@ struct spdnn {
     cudaGraphExec_t graph_exec[2] = {nullptr, nullptr};
     int graph_steps[2] = {0, 0}, graph_group[2] = {0, 0};
     bool graph_dirty = true;
-    bool dense_direct = true;          // SPDNN_DENSE_DIRECT=0: always convert a dense input to tiles first
+    bool dense_direct = false;         // SPDNN_DENSE_DIRECT=1: let the first launch read a dense input in place where
+                                       // it can (measured slower than the layout pass + per-layer kernel at N = 1024)
     const float **dense_cell = nullptr;     // device: address of the row-major input of the pass being set up
     const float *dense_src = nullptr;       // ... as set by the last spdnn_set_input_dense* (null: converted to tiles)
     int input_kind = 0;
@@ -219,7 +220,7 @@ int end_input(spdnn *c) {
 
 int convert_dense_device(spdnn *c, const float *dev_rows, int rows, int first_tile) {
     // rows is a multiple of 32 except for the last chunk
-    const dim3 block(32, 8), grid((rows + 31) / 32, (c->n + 31) / 32);
+    const dim3 block(32, 8), grid((rows + 31) / 32, (c->n + kLayoutCols - 1) / kLayoutCols);
     if (rows <= 0) return SPDNN_OK;
     dense_to_tiles_kernel<<<grid, block, 0, c->stream>>>(dev_rows, c->y[0], c->n, rows, c->tile_stride, first_tile);
     CK(cudaGetLastError());

@@ -312,21 +312,33 @@ __global__ void __launch_bounds__(kThreads, SPDNN_MIN_BLOCKS) layer_kernel(const
 
 // ---- layout conversion and bookkeeping kernels -------------------------------------------
 
-// Row-major [batch][N] -> tiles.  Block (32, 8), grid (ceil(batch/32), ceil(N/32)).
+// Row-major [batch][N] -> tiles.  Block (32, 8), grid (ceil(batch/32), ceil(N/kLayoutCols)): a block
+// moves 32 images x kLayoutCols neurons, 512 contiguous bytes of every image's row, so that the reads
+// stay within few DRAM pages; all of a thread's 16 loads are in flight before the first store.
+constexpr int kLayoutCols = 128;
 static __global__ void dense_to_tiles_kernel(const float *__restrict__ in, float *__restrict__ out, int n, int batch,
                                       long long tile_stride, int first_tile) {
-    __shared__ float t[32][33];
-    const int c0 = blockIdx.y * 32, tile = blockIdx.x;
+    __shared__ float t[32][kLayoutCols + 1];
+    const int c0 = blockIdx.y * kLayoutCols, tile = blockIdx.x;
     const int img0 = tile * 32;
+    float v[4][kLayoutCols / 32];
 #pragma unroll
-    for (int r = threadIdx.y; r < 32; r += 8) {
-        const int img = img0 + r, c = c0 + threadIdx.x;
-        t[r][threadIdx.x] = (img < batch && c < n) ? in[(size_t)img * n + c] : 0.0f;
+    for (int q = 0; q < 4; ++q) {
+        const int img = img0 + threadIdx.y + 8 * q;
+#pragma unroll
+        for (int k = 0; k < kLayoutCols / 32; ++k) {
+            const int c = c0 + 32 * k + threadIdx.x;
+            v[q][k] = (img < batch && c < n) ? __ldg(in + (size_t)img * n + c) : 0.0f;
+        }
     }
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int k = 0; k < kLayoutCols / 32; ++k) t[threadIdx.y + 8 * q][32 * k + threadIdx.x] = v[q][k];
     __syncthreads();
     float *o = out + (size_t)(first_tile + tile) * tile_stride;
 #pragma unroll
-    for (int r = threadIdx.y; r < 32; r += 8) {
+    for (int r = threadIdx.y; r < kLayoutCols; r += 8) {
         const int c = c0 + r;
         if (c < n) o[(size_t)c * 32 + threadIdx.x] = t[threadIdx.x][r];
     }

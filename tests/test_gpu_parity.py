@@ -75,7 +75,7 @@ def test_against_oracle(pattern, n, L, b, oracle):
 @pytest.mark.parametrize("env", [{"SPDNN_RESIDENT": "0"}, {"SPDNN_RESIDENT_TI": "8"}, {"SPDNN_RESIDENT_TI": "4"},
                                  {"SPDNN_CHUNK_FIRST": "1", "SPDNN_CHUNK_MAX": "3"}, {"SPDNN_CHUNK_FIRST": "64"},
                                  {"SPDNN_STAGE_TABLES": "0"}, {"SPDNN_EXACT_SHORTCUT": "0"}, {"SPDNN_RESIDENT_IPT": "4"},
-                                 {"SPDNN_BIT_FORM": "0"}, {"SPDNN_DENSE_DIRECT": "0"},
+                                 {"SPDNN_BIT_FORM": "0"}, {"SPDNN_DENSE_DIRECT": "1"},
                                  {"SPDNN_RESIDENT_TI": "16"}, {"SPDNN_REPS_ONLY": "0"}])
 def test_kernel_paths_agree(env, monkeypatch, oracle):
     """The per-layer kernel, and the shared-memory-resident kernel at every group size and chunk
@@ -89,11 +89,13 @@ def test_kernel_paths_agree(env, monkeypatch, oracle):
         check(run_gpu(net, y0, first=7), want)
 
 
-def test_dense_input_read_in_place(oracle):
-    """A dense input is read in place by the first launch (16-byte loads when the matrix is
-    aligned, 4-byte loads when it is not); a caller's device buffer is not modified, and the
-    same context then takes triplets (the other captured pass) with the same result."""
+def test_dense_input_read_in_place(oracle, monkeypatch):
+    """With SPDNN_DENSE_DIRECT=1 a dense input is read in place by the first launch (16-byte
+    loads when the matrix is aligned, 4-byte loads when it is not); a caller's device buffer is
+    not modified, and the same context then takes triplets (the other captured pass) with the
+    same result."""
     import torch
+    monkeypatch.setenv("SPDNN_DENSE_DIRECT", "1")
     n, L, b = 1024, 30, 1000
     net = SyntheticNetwork(n, L, "radix16")
     y0 = synthetic_images(n, b)
