@@ -104,11 +104,11 @@ class ClockSampler:
                     self.power.append(nv.nvmlDeviceGetPowerUsage(h) / 1000.0)
             except Exception:
                 pass
-            time.sleep(0.0002)
+            time.sleep(0)            # yield; the region may last only a few milliseconds
 
-    def start(self):
+    def prepare(self):
+        """NVML set-up (milliseconds): done before the timed region, so that start() only spawns the thread."""
         try:
-            import threading
             import pynvml as nv
             nv.nvmlInit()
             idx = self.index
@@ -120,10 +120,19 @@ class ClockSampler:
                     pass
             h = nv.nvmlDeviceGetHandleByIndex(idx)
             self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
-            self.thread = threading.Thread(target=self._run, args=(nv, h), daemon=True)
-            self.thread.start()
+            nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)          # first call pays for lazy set-up inside NVML
+            self.nv, self.handle = nv, h
         except Exception:
-            self.thread = None
+            self.nv = self.handle = None
+
+    def start(self):
+        if getattr(self, "nv", None) is None:
+            self.prepare()
+        if self.nv is None:
+            return
+        import threading
+        self.thread = threading.Thread(target=self._run, args=(self.nv, self.handle), daemon=True)
+        self.thread.start()
 
     def stop(self):
         self.stop_flag = True
@@ -281,6 +290,8 @@ def main_ours(args):
         g.sync()
     # -- value: inputs resident in HBM, device-timed
     sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.prepare()
     barrier()
     if rank == 0:
         sampler.start()
