@@ -52,6 +52,8 @@ def parse():
     p.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                    help="weak: every GPU runs --batch images; strong: --batch images are split over the GPUs")
     p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--no-per-layer-line", action="store_true",
+                   help="skip the extra line that times the per-layer kernel alone (SPDNN_RESIDENT=0) against the HBM roofline")
     p.add_argument("--cpu-seconds", type=float, default=12.0, help="target CPU time of the cpu_baseline sample")
     return p.parse_args()
 
@@ -93,12 +95,13 @@ class ClockSampler:
 
     def __init__(self, index):
         self.index, self.samples, self.bits, self.max_mhz, self.thread, self.stop_flag = index, [], 0, None, None, False
-        self.power = []
+        self.power, self.stamps, self.windows = [], [], []
 
     def _run(self, nv, h):
         while not self.stop_flag:
             try:
                 self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                self.stamps.append(time.perf_counter())
                 self.bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))
                 if len(self.samples) % 8 == 1:
                     self.power.append(nv.nvmlDeviceGetPowerUsage(h) / 1000.0)
@@ -134,13 +137,22 @@ class ClockSampler:
         self.thread = threading.Thread(target=self._run, args=(self.nv, self.handle), daemon=True)
         self.thread.start()
 
+    def window(self, t0, t1):
+        """A timed region (host clock, bracketed by synchronisations): only samples inside count."""
+        self.windows.append((t0, t1))
+
     def stop(self):
         self.stop_flag = True
         if self.thread is not None:
             self.thread.join(timeout=2)
-        out = {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": len(self.samples)}
-        if self.samples:
-            out["sm_mhz"] = statistics.median(self.samples)
+        inside = [m for m, t in zip(self.samples, self.stamps) if any(a <= t <= b for a, b in self.windows)] if self.windows \
+            else list(self.samples)
+        first = self.windows[0] if self.windows else None
+        out = {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": len(inside),
+               "samples_in_value_region": sum(1 for t in self.stamps if first and first[0] <= t <= first[1]),
+               "regions": "value + e2e timed regions"}
+        if inside:
+            out["sm_mhz"] = statistics.median(inside)
             out["power_w_max"] = max(self.power) if self.power else None
         out["reasons"] = sorted(k for k, bit in self.REASONS.items() if self.bits & bit)
         return out
@@ -225,6 +237,47 @@ def main_reference(args):
 
 # ---- our arm -----------------------------------------------------------------------------------
 
+def per_layer_line(net, y_dev, cfg, device, stream, first_id, want_survivors, passes=3):
+    """The same workload with ONE launch per layer (SPDNN_RESIDENT=0): the formulation whose bytes
+    the roofline counts -- every layer reads and writes every live image's N activations in HBM.
+    Reported beside the headline so that the hand-written gather kernel can be read against the
+    measured copy bandwidth; it is not the path `value` times."""
+    from graphchallenge21_b200 import SpDNN
+    n, L = cfg["neurons"], cfg["layers"]
+    old = os.environ.get("SPDNN_RESIDENT")
+    os.environ["SPDNN_RESIDENT"] = "0"
+    try:
+        g = SpDNN(n, L, float(net.bias), device=device)
+    finally:
+        if old is None:
+            del os.environ["SPDNN_RESIDENT"]
+        else:
+            os.environ["SPDNN_RESIDENT"] = old
+    try:
+        for l in range(L):
+            g.set_layer_csc(l, *net.layer_csc(l))
+        g.set_stream(stream.cuda_stream)
+        ms, r = [], None
+        for i in range(passes + 1):                   # the first pass builds the launch graph and warms up
+            g.set_input_dense(y_dev, first_id)
+            r = g.infer()
+            if i:
+                ms.append(r.infer_ms)
+        assert r.survivors == want_survivors, (r.survivors, want_survivors)
+        peak, peak_kind = peaks()
+        loop_ms = sum(ms) / len(ms)
+        achieved = r.algorithmic_bytes / (loop_ms * 1e-3) / 1e9
+        return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "peak_kind": peak_kind + " copy bandwidth (MEASURED_PEAKS.json hbm_gbs)", "kernel": "layer_kernel",
+                "launches_per_pass": int(r.loop_launches), "layer_loop_ms": loop_ms, "us_per_layer": loop_ms * 1e3 / L,
+                "passes": passes, "traffic": None,
+                "note": "one launch per layer, activations in HBM between layers; layers after the first few work on the "
+                        "survivors only, whose two activation buffers (%.0f MB) can partly stay in the 126 MB L2"
+                        % (2.0 * r.survivors * n * 4 / 1e6)}
+    finally:
+        g.close()
+
+
 def main_ours(args):
     import torch
     import torch.distributed as dist
@@ -297,12 +350,13 @@ def main_ours(args):
         sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     infer_ms, prep_ms, algo_bytes, launches, loop_launches, group = [], [], 0.0, 0, 0, 0
+    t_host0 = time.perf_counter()
     ev0.record(stream)
     for _ in range(args.steps):
         step_resident()          # queued back to back on the stream; only the last pass is synchronised
     ev1.record(stream)
     barrier()
-    clocks = sampler.stop() if rank == 0 else None
+    sampler.window(t_host0, time.perf_counter())
     ms = ev0.elapsed_time(ev1)
     r = g.sync()                 # statistics of the last timed pass (every pass does the same work)
     infer_ms.append(r.infer_ms); prep_ms.append(r.prepare_ms)
@@ -315,14 +369,17 @@ def main_ours(args):
         step_e2e(kind)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
         e0.record(stream)
         for _ in range(args.steps):
             c_ = step_e2e(kind)
         e1.record(stream)
         barrier()
+        sampler.window(t0, time.perf_counter())
         return e0.elapsed_time(e1), c_
     ms_e2e_dense, _ = time_e2e("dense")
     ms_e2e, cats = time_e2e("coo")
+    clocks = sampler.stop() if rank == 0 else None
     e2e_prepare_ms = g.sync().prepare_ms          # H2D + layout conversion of the last end-to-end step
     d2h = int(len(cats) * 4 + (L + 1) * 16 + 4)
     all_cats = gather_categories(np.asarray(cats).copy())
@@ -374,6 +431,8 @@ def main_ours(args):
             # per launch, like `achieved`: the capture's per-layer figure times the layers of an average launch
             out["roofline"]["traffic"] = tr * L / max(loop_launches, 1)
     g.close()
+    if rank == 0 and world == 1 and not args.no_per_layer_line:
+        out["roofline_per_layer_kernel"] = per_layer_line(net, y_dev, cfg, local, stream, rank * B, survivors)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cb = run_cpu_reference(cfg, args.pattern, args.cpu_seconds)
         cb.pop("seconds", None)

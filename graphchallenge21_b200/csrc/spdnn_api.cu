@@ -118,6 +118,12 @@ struct spdnn {
     cudaGraphExec_t graph_exec[2] = {nullptr, nullptr};
     int graph_steps[2] = {0, 0}, graph_group[2] = {0, 0};
     bool graph_dirty = true;
+    bool lazy_expand = true;           // SPDNN_LAZY_EXPAND=0: the last launch of a pass writes all member rows itself
+    int expand_layer_of_plan = -1;     // set by enqueue_layers
+    int graph_expand_layer[2] = {-1, -1};   // per captured pass: the layer whose classes spdnn_get_activations must
+                                            // still expand to all member rows (-1: the tiles are complete)
+    bool final_needs_expand = false;   // ... pending for the pass that ran last
+    int final_expand_layer = -1;
     bool dense_direct = false;         // SPDNN_DENSE_DIRECT=1: let the first launch read a dense input in place where
                                        // it can (measured slower than the layout pass + per-layer kernel at N = 1024)
     const float **dense_cell = nullptr;     // device: address of the row-major input of the pass being set up
@@ -252,15 +258,15 @@ int blocks_per_sm(int k, bool uniform) {
     return uniform ? blocks_per_sm_t<0, true>() : blocks_per_sm_t<0, false>();
 }
 
-template <int TI, int IPT, int MODE, int KT, bool UNIFORM, bool STAGED>
+template <int TI, int IPT, int KT, bool UNIFORM, bool STAGED>
 int launch_resident_t(spdnn *c, const ResArgs &a, int grid, size_t smem) {
     static bool configured[64] = {};
     if (!configured[c->device & 63]) {
-        CK(cudaFuncSetAttribute(resident_kernel<TI, IPT, MODE, KT, UNIFORM, STAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        CK(cudaFuncSetAttribute(resident_kernel<TI, IPT, KT, UNIFORM, STAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 c->smem_optin - 1024));     // the kernel also has a little static shared memory
         configured[c->device & 63] = true;
     }
-    resident_kernel<TI, IPT, MODE, KT, UNIFORM, STAGED><<<grid, ResThreads<MODE>::value, smem, c->stream>>>(a);
+    resident_kernel<TI, IPT, KT, UNIFORM, STAGED><<<grid, SPDNN_GENERIC_THREADS, smem, c->stream>>>(a);
     CK(cudaGetLastError());
     return SPDNN_OK;
 }
@@ -289,15 +295,15 @@ template <int TI>
 int launch_generic(spdnn *c, const ResArgs &a, int grid, size_t smem, bool k32, bool uniform) {
     const bool staged = a.table_bytes > 0;
     if (k32) {
-        if (uniform) return staged ? launch_resident_t<TI, 4, kResGeneric, 32, true, true>(c, a, grid, smem)
-                                   : launch_resident_t<TI, 4, kResGeneric, 32, true, false>(c, a, grid, smem);
-        return staged ? launch_resident_t<TI, 4, kResGeneric, 32, false, true>(c, a, grid, smem)
-                      : launch_resident_t<TI, 4, kResGeneric, 32, false, false>(c, a, grid, smem);
+        if (uniform) return staged ? launch_resident_t<TI, 4, 32, true, true>(c, a, grid, smem)
+                                   : launch_resident_t<TI, 4, 32, true, false>(c, a, grid, smem);
+        return staged ? launch_resident_t<TI, 4, 32, false, true>(c, a, grid, smem)
+                      : launch_resident_t<TI, 4, 32, false, false>(c, a, grid, smem);
     }
-    if (uniform) return staged ? launch_resident_t<TI, 4, kResGeneric, 0, true, true>(c, a, grid, smem)
-                               : launch_resident_t<TI, 4, kResGeneric, 0, true, false>(c, a, grid, smem);
-    return staged ? launch_resident_t<TI, 4, kResGeneric, 0, false, true>(c, a, grid, smem)
-                  : launch_resident_t<TI, 4, kResGeneric, 0, false, false>(c, a, grid, smem);
+    if (uniform) return staged ? launch_resident_t<TI, 4, 0, true, true>(c, a, grid, smem)
+                               : launch_resident_t<TI, 4, 0, true, false>(c, a, grid, smem);
+    return staged ? launch_resident_t<TI, 4, 0, false, true>(c, a, grid, smem)
+                  : launch_resident_t<TI, 4, 0, false, false>(c, a, grid, smem);
 }
 
 int launch_resident(spdnn *c, int ti, int ipt, const ResArgs &a, int grid, size_t smem, int mode, bool k32, bool uniform) {
@@ -516,6 +522,12 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan) {
         const float *yin = c->y[step & 1];
         float *yout = c->y[(step & 1) ^ 1];
         const bool next_resident = c->reps_only && step + 1 < plan.size() && plan[step + 1].ti != 0;
+        // The last launch of a pass stores one row per class too when it is a resident chunk: the categories
+        // and survivor counts need no more, and spdnn_get_activations expands the classes when it is called.
+        const int last_layer = st.first + st.count - 1;
+        const bool lazy_last = c->lazy_expand && c->reps_only && step + 1 == plan.size() && st.ti != 0 && c->res[last_layer] &&
+                               c->res[last_layer]->mem_ptr != nullptr;
+        if (step + 1 == plan.size()) c->expand_layer_of_plan = lazy_last ? last_layer : -1;
         if (st.ti) {
             const DevRes &R0 = *c->res[l];
             ResArgs a;
@@ -529,7 +541,7 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan) {
             a.stream = st.stream; a.stream_stride = st.stride; a.tgroup_shift = st.gshift; a.tring = st.tring;
             a.wring = st.wring; a.rows_w = st.rows_w; a.bit_multi = st.max_classes > 64 ? 1 : 0;
             a.n = c->n; a.bias = c->bias; a.clip = c->clip;
-            a.reps_only = next_resident ? 1 : 0;
+            a.reps_only = (next_resident || lazy_last) ? 1 : 0;
             a.exact_ok = (l > 0 && c->clip <= 1024.0f && c->exact_shortcut) ? 1 : 0;
             const int grid = std::max(1, (c->tiles_cap * 32 + st.ti - 1) / st.ti);
             const bool alt2 = (R0.mode == kResAlt2);
@@ -612,6 +624,7 @@ int build_graph_kind(spdnn *c, int kind) {
     if (e != cudaSuccess) return fail(c, SPDNN_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
     c->graph_steps[kind] = c->nsteps;
     c->graph_group[kind] = c->last_group;
+    c->graph_expand_layer[kind] = c->expand_layer_of_plan;
     return SPDNN_OK;
 }
 
@@ -705,6 +718,7 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
         if (const char *e = getenv("SPDNN_PRINT_SCHEDULE")) c->print_schedule = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_EXACT_SHORTCUT")) c->exact_shortcut = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BIT_FORM")) c->bit_form = atoi(e) != 0;
+        if (const char *e = getenv("SPDNN_LAZY_EXPAND")) c->lazy_expand = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_DENSE_DIRECT")) c->dense_direct = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_TABLE_RING")) c->table_ring_max = atoi(e) >= 4 ? 4 : 2;
         if (const char *e = getenv("SPDNN_WORD_RING")) c->word_ring_max = std::max(2, std::min(33, atoi(e)));
@@ -935,6 +949,8 @@ int spdnn_infer_async(spdnn_t *c) {
         return fail(c, SPDNN_ERR_STATE, "the network changed after the input was set: set the input again");
     c->nsteps = c->graph_steps[c->input_kind];
     c->last_group = c->graph_group[c->input_kind];
+    c->final_expand_layer = c->graph_expand_layer[c->input_kind];
+    c->final_needs_expand = c->final_expand_layer >= 0;
     CK(cudaGraphLaunch(c->graph_exec[c->input_kind], c->stream));
     CK(cudaEventRecord(c->ev_inf1, c->stream));
     c->input_ready = false;
@@ -1036,7 +1052,17 @@ int spdnn_get_activations(spdnn_t *c, float *y, int64_t capacity_rows) {
     chunk_rows = std::min<size_t>(chunk_rows, (size_t)(live + 31) / 32 * 32);
     int rc = ensure_stage(c, chunk_rows * row_bytes);
     if (rc) return rc;
-    const float *fin = c->y[c->nsteps & 1];
+    float *fin = c->y[c->nsteps & 1];
+    if (c->final_needs_expand) {
+        // the last launch stored one row per class: copy it to the other members in every tile it wrote
+        const DevRes &R = *c->res[c->final_expand_layer];
+        const int tiles = (c->host_ctl[c->nsteps - 1].live + 31) / 32;
+        const long long warps = (long long)tiles * R.classes;
+        const int grid = (int)std::min<long long>((warps + 7) / 8, (long long)c->sm_count * 16);
+        expand_members_kernel<<<std::max(1, grid), 256, 0, c->stream>>>(fin, c->tile_stride, tiles, R.mem_ptr, R.mem, R.classes);
+        CK(cudaGetLastError());
+        c->final_needs_expand = false;
+    }
     // the kernel indexes images from 0; a chunk is selected by offsetting the output pointer
     // and launching only its tile rows
     for (size_t r0 = 0; r0 < (size_t)live; r0 += chunk_rows) {

@@ -382,6 +382,22 @@ static __global__ void tiles_to_dense_kernel(const float *__restrict__ y, long l
 }
 
 // After the last launch: the ids of the final order, if that launch changed the order.
+// After a pass whose last launch stored one row per class (its first member): copy that row to the
+// other member rows of every tile the launch wrote, so that the tiles hold all N activations.
+// One warp per (tile, class), lane = image; mem[] holds member column * 32.
+static __global__ void expand_members_kernel(float *__restrict__ y, long long tile_stride, int tiles, const int32_t *__restrict__ mem_ptr,
+                                             const int32_t *__restrict__ mem, int classes) {
+    const int lane = threadIdx.x & 31;
+    const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+    for (long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w < (long long)tiles * classes; w += warps) {
+        const int tile = (int)(w / classes), u = (int)(w - (long long)tile * classes);
+        float *t = y + (size_t)tile * tile_stride + lane;
+        const int mb = __ldg(mem_ptr + u), me = __ldg(mem_ptr + u + 1);
+        const float v = t[__ldg(mem + mb)];
+        for (int m = mb + 1; m < me; ++m) t[__ldg(mem + m)] = v;
+    }
+}
+
 static __global__ void finalize_ids_kernel(const LoopCtl *ctl, const int32_t *__restrict__ slot, int32_t *ids0, int32_t *ids1) {
     const LoopCtl c = *ctl;
     if (c.identity) return;

@@ -19,9 +19,10 @@
 // a gather is one 16-byte shared-memory load, two adds are one packed add.rn.f32x2 (sm_100
 // packed fp32).  Each element is added in ascending-input order, so results are bit-identical
 // to the per-layer kernel and to the CPU loop of src/utils/cpu_spmm.h:14-43.  Two table forms:
-//   GENERIC  K row numbers per class, gathered one by one;
+//   GENERIC  K row numbers per class, gathered one by one: resident_kernel, in this file;
 //   ALT2     the K terms alternate between two rows a,b,a,b,... (what a 16-wide butterfly block
-//            looks like in value ids): two loads, then K adds in that order.
+//            looks like in value ids): two loads, then K adds in that order: alt2_kernel
+//            (spdnn_alt2.cuh), which shares the helpers defined here.
 // The per-layer tables come into shared memory by bulk asynchronous copy (TMA, cp.async.bulk
 // completing on an mbarrier), the table of layer l+1 while layer l is computed.
 //
@@ -314,26 +315,19 @@ __device__ __forceinline__ bool load_dense_rows(const float *dense, int n, int j
 // Grid: one block per TI live images (launched for the worst case; surplus blocks only take
 // part in the last-block ticket).  Dynamic shared memory: two activation buffers of
 // buf_rows * TI * 4 bytes, then (STAGED) two table buffers of table_bytes each.
-// Threads per block: the GENERIC form is bound by shared-memory latency with one block per SM
-// (its buffers fill the shared memory), so it runs 16 warps; the light ALT2 form runs many
-// small blocks per SM.
+// Threads per block: the GENERIC form is bound by shared-memory latency with one or two blocks
+// per SM (its buffers fill the shared memory), so it runs 16 warps.
 #ifndef SPDNN_GENERIC_THREADS
 #define SPDNN_GENERIC_THREADS 512
 #endif
 #ifndef SPDNN_GENERIC_MIN_BLOCKS
 #define SPDNN_GENERIC_MIN_BLOCKS 2      // <= 64 registers: two blocks of 16 warps per SM where the shared memory allows
 #endif
-template <int MODE>
-struct ResThreads {
-    static constexpr int value = (MODE == kResAlt2) ? kThreads : SPDNN_GENERIC_THREADS;
-};
-// IPT = images per thread (4 or 8): with 8 a thread carries two float4 halves through every
-// step, which halves the per-layer bookkeeping (barrier, table wait, loop control, addresses)
-// per image; it is used for the light ALT2 form.
-template <int TI, int IPT, int MODE, int KT, bool UNIFORM, bool STAGED>
-__global__ void __launch_bounds__(ResThreads<MODE>::value, SPDNN_GENERIC_MIN_BLOCKS)
+// IPT = images per thread (4 here; the ALT2 kernel also runs 8).
+template <int TI, int IPT, int KT, bool UNIFORM, bool STAGED>
+__global__ void __launch_bounds__(SPDNN_GENERIC_THREADS, SPDNN_GENERIC_MIN_BLOCKS)
 resident_kernel(const ResArgs a) {
-    constexpr int NT = ResThreads<MODE>::value;
+    constexpr int NT = SPDNN_GENERIC_THREADS;
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ unsigned int s_alive[3];
     __shared__ int s_last, s_fail;
@@ -463,24 +457,13 @@ resident_kernel(const ResArgs a) {
             for (int u = grp; u < classes; u += CPI) {
                 float4 s[NQ];
                 int out_row;
-                if (MODE == kResAlt2) {
-                    const int4 e = STAGED ? reinterpret_cast<const int4 *>(T)[1 + u] : __ldg(reinterpret_cast<const int4 *>(T) + 1 + u);
+                const int kp = lk + 4;
+                const int32_t *rows = T + 4 + (size_t)u * kp;
 #pragma unroll
-                    for (int h = 0; h < NQ; ++h) {
-                        const float4 va = *reinterpret_cast<const float4 *>(in + e.x * RS + 16 * h);
-                        const float4 vb = *reinterpret_cast<const float4 *>(in + e.y * RS + 16 * h);
-                        s[h] = class_sum_alt2<KT>(va, vb, lk, lw, a.exact_ok != 0);
-                    }
-                    out_row = e.z;
-                } else {
-                    const int kp = lk + 4;
-                    const int32_t *rows = T + 4 + (size_t)u * kp;
-#pragma unroll
-                    for (int h = 0; h < NQ; ++h)
-                        s[h] = class_sum_generic<KT, UNIFORM, STAGED, RS>(rows, reinterpret_cast<const float *>(rows) + (size_t)classes * kp,
-                                                                          lk, lw, in + 16 * h);
-                    out_row = STAGED ? rows[lk] : __ldg(rows + lk);
-                }
+                for (int h = 0; h < NQ; ++h)
+                    s[h] = class_sum_generic<KT, UNIFORM, STAGED, RS>(rows, reinterpret_cast<const float *>(rows) + (size_t)classes * kp,
+                                                                      lk, lw, in + 16 * h);
+                out_row = STAGED ? rows[lk] : __ldg(rows + lk);
 #pragma unroll
                 for (int h = 0; h < NQ; ++h) {
                     float4 y;
@@ -500,7 +483,7 @@ resident_kernel(const ResArgs a) {
                     *reinterpret_cast<float4 *>(nxt + out_row * RS + sub * TB + 16 * h) = y;
                 }
             }
-            if (MODE == kResGeneric) {
+            {
                 // zero rows of the buffer just written (the next layer's padded entries point there)
                 const int ue = (classes + 1) & ~1;
                 for (int r = classes + grp; r < ue + 2; r += CPI)
