@@ -345,6 +345,9 @@ def main_ours(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.prepare()
+        # the timed loop is a few milliseconds of Python that enqueues work: let the polling thread
+        # preempt it (the default switch interval of the interpreter is 5 ms)
+        sys.setswitchinterval(1e-4)
     barrier()
     if rank == 0:
         sampler.start()

@@ -112,7 +112,9 @@ constexpr int kAlt2MaxTableRing = 4;
 // Grid: one block per TI live images (launched for the worst case; surplus blocks only take
 // part in the last-block ticket).  Dynamic shared memory: two activation buffers of
 // buf_rows * TI * 4 bytes, then (STAGED) tring buffers of (stream_stride << tgroup_shift) bytes for
-// groups of layer records, then wring buffers of rows_w words for the bit form.
+// groups of layer records.  The bit form keeps its ring of wring word buffers (rows_w words each) in
+// the activation buffer that is free at that moment: while a block is in the bit form it needs
+// neither float buffer (it converts `cur` on the way in and rebuilds `cur` on the way out).
 // IPT = images per thread (4 or 8): with 8 a thread carries two float4 halves through every step.
 template <int TI, int IPT, int KT, bool STAGED>
 __global__ void __launch_bounds__(kThreads, SPDNN_ALT2_MIN_BLOCKS) alt2_kernel(const ResArgs a) {
@@ -147,7 +149,7 @@ __global__ void __launch_bounds__(kThreads, SPDNN_ALT2_MIN_BLOCKS) alt2_kernel(c
         const int tring = STAGED ? a.tring : 0, tshift = tring == 4 ? 2 : 1;
         const int group_bytes = stride << gshift;
         const int ngroups = STAGED ? (a.nlayers + gmask) >> gshift : 0;
-        unsigned int *const wring0 = reinterpret_cast<unsigned int *>(tbl0 + (size_t)tring * group_bytes);
+        unsigned int *wring0 = nullptr;      // bit form: its word buffers, in the float buffer that is not `cur`
         const bool use_bits = a.bit_ok != 0;
         const int j0 = blockIdx.x * TI;
         int next_group = 0;          // thread 0: the next group of tables to request
@@ -158,9 +160,9 @@ __global__ void __launch_bounds__(kThreads, SPDNN_ALT2_MIN_BLOCKS) alt2_kernel(c
             const int lim = min((li >> gshift) + tring, ngroups);
             while (next_group < lim) {
                 const int l0 = next_group << gshift, cnt = min(1 << gshift, a.nlayers - l0);
-#ifdef SPDNN_ALT2_PROXY_FENCE
+                // orders the block's earlier reads of this buffer before the copy that overwrites it
+                // (measured: no cost at one copy per 32 layers)
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#endif
                 bulk_load_table(tbl0 + (size_t)(next_group & (tring - 1)) * group_bytes, a.stream + (size_t)l0 * stride,
                                 (unsigned int)(cnt * stride), &s_bar[next_group & (tring - 1)]);
                 ++next_group;
@@ -260,6 +262,7 @@ __global__ void __launch_bounds__(kThreads, SPDNN_ALT2_MIN_BLOCKS) alt2_kernel(c
         int ws = 0;                  // bit form: the word buffer that holds the current activations
         bool bitmode = false;
         if (start_in_bits) {
+            wring0 = reinterpret_cast<unsigned int *>(nxt);
             rows_to_bits(cur, wring0);
             __syncthreads();
             bitmode = true;
@@ -506,6 +509,7 @@ __global__ void __launch_bounds__(kThreads, SPDNN_ALT2_MIN_BLOCKS) alt2_kernel(c
             if (alive_prev == 0u) break;
             if (saturated && li < a.nlayers) {
                 // every output of the layer is 0 or clip: continue in the bit form
+                wring0 = reinterpret_cast<unsigned int *>(nxt);
                 rows_to_bits(cur, wring0);
                 ws = 0;
                 __syncthreads();

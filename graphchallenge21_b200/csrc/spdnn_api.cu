@@ -393,10 +393,10 @@ inline int resident_rows(const DevRes &R) { return ((std::max(R.v_in, R.classes)
 
 // Dynamic shared memory of a resident block.  GENERIC chunks: two activation buffers and two
 // staged tables.  ALT2 chunks: two activation buffers, `tring` groups of 1 << gshift layer records
-// of `stride` bytes, `wring` buffers of rows_w words for the bit form.
+// of `stride` bytes (the word buffers of the bit form live in the activation buffer that is free).
 inline size_t resident_smem_bytes(int ti, int rows, int table) { return 2 * (size_t)rows * ti * 4 + 2 * (size_t)table; }
-inline size_t alt2_smem_bytes(int ti, int rows, int stride, int gshift, int tring, int wring, int rows_w) {
-    return 2 * (size_t)rows * ti * 4 + (size_t)tring * ((size_t)stride << gshift) + (size_t)wring * rows_w * 4;
+inline size_t alt2_smem_bytes(int ti, int rows, int stride, int gshift, int tring) {
+    return 2 * (size_t)rows * ti * 4 + (size_t)tring * ((size_t)stride << gshift);
 }
 
 // Enqueues the whole network: chunks of layers through the resident kernel where a group of
@@ -476,20 +476,20 @@ std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
                     st.max_classes = maxc;
                     st.stride = alt2_stream_stride(maxc);
                     st.rows_w = std::max(rows, (maxc + 63) / 64 * 64);
-                    auto afits = [&](int gs, int tr, int wr) {
-                        return alt2_smem_bytes(ti, rows, st.stride, gs, tr, wr, st.rows_w) + 2048 <= (size_t)c->smem_optin;
+                    auto afits = [&](int gs, int tr) {
+                        return alt2_smem_bytes(ti, rows, st.stride, gs, tr) + 2048 <= (size_t)c->smem_optin;
                     };
-                    st.tring = 0; st.gshift = 0; st.wring = 2;
+                    st.tring = 0; st.gshift = 0;
+                    // word buffers of the bit form: as many as one activation buffer holds, 33 at most (under
+                    // two the chunk runs without the bit form)
+                    st.wring = (int)std::min<size_t>((size_t)c->word_ring_max, ((size_t)rows * ti * 4) / ((size_t)st.rows_w * 4));
                     // staging may take a quarter of the shared memory at most, so that the blocks per SM stay
                     // what the activations allow
                     if (c->stage_tables)
                         for (int gs = 5; gs >= 0 && !st.tring; --gs)
                             for (int tr = 4; tr >= 2 && !st.tring; tr /= 2)
-                                if ((1 << gs) <= c->table_group_max && ((1 << gs) < 2 * f || gs == 0) && tr <= c->table_ring_max && afits(gs, tr, 2) &&
+                                if ((1 << gs) <= c->table_group_max && ((1 << gs) < 2 * f || gs == 0) && tr <= c->table_ring_max && afits(gs, tr) &&
                                     (size_t)tr * ((size_t)st.stride << gs) <= (size_t)c->smem_optin / 4) { st.gshift = gs; st.tring = tr; }
-                    for (int wr = std::min(c->word_ring_max, (st.tring ? (1 << st.gshift) : 8) + 1); wr > 2; --wr)
-                        if (afits(st.gshift, st.tring, wr) && (size_t)wr * st.rows_w * 4 <= (size_t)c->smem_optin / 8) { st.wring = wr; break; }
-                    if (!afits(st.gshift, st.tring, st.wring)) ti = 0;      // not even the two word buffers fit
                 }
                 // A lone layer that reads all N rows of every image but computes few classes from
                 // them (the first layer of a network with repeated columns) gains nothing from
@@ -545,9 +545,9 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan) {
             a.exact_ok = (l > 0 && c->clip <= 1024.0f && c->exact_shortcut) ? 1 : 0;
             const int grid = std::max(1, (c->tiles_cap * 32 + st.ti - 1) / st.ti);
             const bool alt2 = (R0.mode == kResAlt2);
-            const size_t smem = alt2 ? alt2_smem_bytes(st.ti, st.rows, st.stride, st.gshift, st.tring, st.wring, st.rows_w)
+            const size_t smem = alt2 ? alt2_smem_bytes(st.ti, st.rows, st.stride, st.gshift, st.tring)
                                      : resident_smem_bytes(st.ti, st.rows, st.table);
-            a.bit_ok = (alt2 && c->bit_form && c->clip > 0.0f) ? 1 : 0;
+            a.bit_ok = (alt2 && c->bit_form && c->clip > 0.0f && st.wring >= 2) ? 1 : 0;
             int rc = launch_resident(c, st.ti, st.ipt, a, grid, smem, R0.mode, R0.k == 32, R0.uniform);
             if (rc) return rc;
             c->last_group = st.ti;
