@@ -7,10 +7,10 @@
 //
 // 1. Packed table stream.  The tables of a chunk are one contiguous array in global memory,
 //    `stride` bytes per layer: a 16-byte header {classes, K, bits of w, truth table}, then per pass
-//    of 64 classes 32 slots of 16 bytes; slot `lane` holds the entries of classes 64p + lane and
-//    64p + 32 + lane, 8 bytes each: {4 * row a | (4 * row b) << 16} twice, first in the plain row
-//    numbers (value ids) the bit form uses, then in the permuted rows of the float buffers.  The
-//    output row of class u is u (float buffers: resident_phys_row(u)) and is not stored.  One bulk asynchronous copy (TMA) brings a GROUP of up
+//    of 64 classes 32 slots of 8 bytes; slot `lane` holds the entries of classes 64p + lane and
+//    64p + 32 + lane, 4 bytes each: 4 * row a | (4 * row b) << 16 in plain row numbers (value ids;
+//    the float buffers keep row r at resident_phys_row(r)).  The output row of class u is u and is
+//    not stored.  One bulk asynchronous copy (TMA) brings a GROUP of up
 //    to 8 layers into shared memory, several groups ahead of the layer being computed.
 //
 // 2. Bit form of saturated activations.  Once every activation of a block's images is exactly 0
@@ -37,11 +37,11 @@
 namespace spdnn_impl {
 
 // Bytes per layer of a packed stream whose largest layer has max_classes classes.
-__host__ __device__ __forceinline__ int alt2_stream_stride(int max_classes) { return 16 + ((max_classes + 63) / 64) * 512; }
+__host__ __device__ __forceinline__ int alt2_stream_stride(int max_classes) { return 16 + ((max_classes + 63) / 64) * 256; }
 
 // Byte offset of class u's entry inside a layer's record.
 __host__ __device__ __forceinline__ int alt2_entry_offset(int u) {
-    return 16 + (u >> 6) * 512 + (u & 31) * 16 + ((u >> 5) & 1) * 8;
+    return 16 + (u >> 6) * 256 + (u & 31) * 8 + ((u >> 5) & 1) * 4;
 }
 
 // Builds the packed stream of a chunk from the per-layer blobs (ALT2: int32 t[U][4] = {row a,
@@ -63,16 +63,16 @@ static __global__ void alt2_pack_kernel(const ResLayer *layers, int stride, unsi
         }
         *reinterpret_cast<int4 *>(rec) = make_int4(classes, k, blob[2], (int)tt);
     }
-    const int slots = (stride - 16) / 8;
+    const int slots = (stride - 16) / 4;
     for (int u = threadIdx.x; u < slots; u += blockDim.x) {
-        uint2 e = make_uint2(0u, 0u);        // a class past the end reads row 0 twice; its output row is never read
+        unsigned int e = 0u;                 // a class past the end reads row 0 twice; its output row is never read
         if (u < classes) {
-            // the blob names rows of the float buffers, which are permuted (resident_phys_row, an involution)
+            // the blob names rows of the float buffers, which are permuted (resident_phys_row, an involution):
+            // the stream holds the plain row numbers (value ids)
             const int pa = blob[4 + 4 * u], pb = blob[4 + 4 * u + 1];
-            e.x = (unsigned int)(resident_phys_row(pa) * 4) | ((unsigned int)(resident_phys_row(pb) * 4) << 16);
-            e.y = (unsigned int)(pa * 4) | ((unsigned int)(pb * 4) << 16);
+            e = (unsigned int)(resident_phys_row(pa) * 4) | ((unsigned int)(resident_phys_row(pb) * 4) << 16);
         }
-        *reinterpret_cast<uint2 *>(rec + alt2_entry_offset(u)) = e;
+        *reinterpret_cast<unsigned int *>(rec + alt2_entry_offset(u)) = e;
     }
 }
 
@@ -116,9 +116,10 @@ constexpr int kAlt2MaxTableRing = 4;
 // the activation buffer that is free at that moment: while a block is in the bit form it needs
 // neither float buffer (it converts `cur` on the way in and rebuilds `cur` on the way out).
 // IPT = images per thread (4 or 8): with 8 a thread carries two float4 halves through every step.
-template <int TI, int IPT, int KT, bool STAGED>
-__global__ void __launch_bounds__(kThreads, SPDNN_ALT2_MIN_BLOCKS) alt2_kernel(const ResArgs a) {
-    constexpr int NT = kThreads;
+// NT = threads per block: 256, or 128 for chunks whose layers have at most 64 classes -- there one warp
+// does the bit form, and smaller blocks let twice as many of those warps share an SM.
+template <int TI, int IPT, int KT, bool STAGED, int NT>
+__global__ void __launch_bounds__(NT, (NT == 128 ? 2 : 1) * SPDNN_ALT2_MIN_BLOCKS) alt2_kernel(const ResArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ unsigned int s_alive[3];          // float form: images alive after layer li % 3
     __shared__ int s_ns[3];                      // float form: layer li % 3 produced an output that is neither 0 nor clip
@@ -322,16 +323,16 @@ __global__ void __launch_bounds__(kThreads, SPDNN_ALT2_MIN_BLOCKS) alt2_kernel(c
                             // A slot past the layer's classes reads row 0 twice and writes a row nobody reads;
                             // its bits can only add to `ns` (a needless return to the float form, never a
                             // wrong one) -- an image with all-zero rows gets 0 there like everywhere else.
-                            const uint4 *slot = reinterpret_cast<const uint4 *>(T + 16) + lane;
-                            uint4 e = STAGED ? *slot : __ldg(slot);
+                            const uint2 *slot = reinterpret_cast<const uint2 *>(T + 16) + lane;
+                            uint2 e = STAGED ? *slot : __ldg(slot);
                             for (int g = 0; g < cnt; ++g) {
-                                slot = reinterpret_cast<const uint4 *>(reinterpret_cast<const unsigned char *>(slot) + stride);
-                                uint4 en = e;
+                                slot = reinterpret_cast<const uint2 *>(reinterpret_cast<const unsigned char *>(slot) + stride);
+                                uint2 en = e;
                                 if (g + 1 < cnt) en = STAGED ? *slot : __ldg(slot);      // next layer's entries, early
                                 const unsigned int a1 = *reinterpret_cast<const unsigned int *>(wc + (e.x & 0xffffu));
                                 const unsigned int b1 = *reinterpret_cast<const unsigned int *>(wc + (e.x >> 16));
-                                const unsigned int a2 = *reinterpret_cast<const unsigned int *>(wc + (e.z & 0xffffu));
-                                const unsigned int b2 = *reinterpret_cast<const unsigned int *>(wc + (e.z >> 16));
+                                const unsigned int a2 = *reinterpret_cast<const unsigned int *>(wc + (e.y & 0xffffu));
+                                const unsigned int b2 = *reinterpret_cast<const unsigned int *>(wc + (e.y >> 16));
                                 unsigned char *wn = const_cast<unsigned char *>(wc) + wbytes;
                                 if (wn == wend) wn = wbase;
                                 o1 = select4(a1, b1, tm.hi) & keep;
@@ -354,12 +355,12 @@ __global__ void __launch_bounds__(kThreads, SPDNN_ALT2_MIN_BLOCKS) alt2_kernel(c
                                 if (wn == wend) wn = wbase;
                                 o1 = 0u; o2 = 0u;
                                 for (int p = warp; p < passes; p += NT / 32) {
-                                    const uint4 *slot = reinterpret_cast<const uint4 *>(Tg + 16 + p * 512) + lane;
-                                    const uint4 e = STAGED ? *slot : __ldg(slot);
+                                    const uint2 *slot = reinterpret_cast<const uint2 *>(Tg + 16 + p * 256) + lane;
+                                    const uint2 e = STAGED ? *slot : __ldg(slot);
                                     const unsigned int a1 = *reinterpret_cast<const unsigned int *>(wc + (e.x & 0xffffu));
                                     const unsigned int b1 = *reinterpret_cast<const unsigned int *>(wc + (e.x >> 16));
-                                    const unsigned int a2 = *reinterpret_cast<const unsigned int *>(wc + (e.z & 0xffffu));
-                                    const unsigned int b2 = *reinterpret_cast<const unsigned int *>(wc + (e.z >> 16));
+                                    const unsigned int a2 = *reinterpret_cast<const unsigned int *>(wc + (e.y & 0xffffu));
+                                    const unsigned int b2 = *reinterpret_cast<const unsigned int *>(wc + (e.y >> 16));
                                     const unsigned int x1 = select4(a1, b1, tm.hi) & keep, x2 = select4(a2, b2, tm.hi) & keep;
                                     ns |= (select4(a1, b1, tm.ns) | select4(a2, b2, tm.ns)) & keep;
                                     reinterpret_cast<unsigned int *>(wn)[p * 64 + lane] = x1;
@@ -461,9 +462,9 @@ __global__ void __launch_bounds__(kThreads, SPDNN_ALT2_MIN_BLOCKS) alt2_kernel(c
             bool ns = false;
             const unsigned char *in = cur + sub * TB;
             for (int u = grp; u < classes; u += CPI) {
-                const unsigned int *ep = reinterpret_cast<const unsigned int *>(T + alt2_entry_offset(u) + 4);
+                const unsigned int *ep = reinterpret_cast<const unsigned int *>(T + alt2_entry_offset(u));
                 const unsigned int e = STAGED ? *ep : __ldg(ep);
-                const int ao = (int)(e & 0xffffu) * TI, bo = (int)(e >> 16) * TI;      // 4 * row * TI = row * RS
+                const int ao = resident_phys_row((int)(e & 0xffffu) >> 2) * RS, bo = resident_phys_row((int)(e >> 18)) * RS;
                 unsigned char *out = nxt + resident_phys_row(u) * RS + sub * TB;
 #pragma unroll
                 for (int h = 0; h < NQ; ++h) {

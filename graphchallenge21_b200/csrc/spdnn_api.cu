@@ -118,6 +118,7 @@ struct spdnn {
     cudaGraphExec_t graph_exec[2] = {nullptr, nullptr};
     int graph_steps[2] = {0, 0}, graph_group[2] = {0, 0};
     bool graph_dirty = true;
+    bool alt2_small_blocks = true;     // SPDNN_ALT2_SMALL_BLOCKS=0: 256-thread blocks also for layers of <= 64 classes
     bool lazy_expand = true;           // SPDNN_LAZY_EXPAND=0: the last launch of a pass writes all member rows itself
     int expand_layer_of_plan = -1;     // set by enqueue_layers
     int graph_expand_layer[2] = {-1, -1};   // per captured pass: the layer whose classes spdnn_get_activations must
@@ -271,24 +272,24 @@ int launch_resident_t(spdnn *c, const ResArgs &a, int grid, size_t smem) {
     return SPDNN_OK;
 }
 
-template <int TI, int IPT, int KT, bool STAGED>
+template <int TI, int IPT, int KT, bool STAGED, int NT>
 int launch_alt2_t(spdnn *c, const ResArgs &a, int grid, size_t smem) {
     static bool configured[64] = {};
     if (!configured[c->device & 63]) {
-        CK(cudaFuncSetAttribute(alt2_kernel<TI, IPT, KT, STAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, c->smem_optin - 1024));
+        CK(cudaFuncSetAttribute(alt2_kernel<TI, IPT, KT, STAGED, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, c->smem_optin - 1024));
         configured[c->device & 63] = true;
     }
-    alt2_kernel<TI, IPT, KT, STAGED><<<grid, kThreads, smem, c->stream>>>(a);
+    alt2_kernel<TI, IPT, KT, STAGED, NT><<<grid, NT, smem, c->stream>>>(a);
     CK(cudaGetLastError());
     return SPDNN_OK;
 }
 
 // ALT2 form (always a uniform weight): group sizes 32/16 with 8 images per thread, 16/8/4 with 4.
-template <int TI, int IPT>
+template <int TI, int IPT, int NT>
 int launch_alt2(spdnn *c, const ResArgs &a, int grid, size_t smem, bool k32) {
     const bool staged = a.tring > 0;
-    if (k32) return staged ? launch_alt2_t<TI, IPT, 32, true>(c, a, grid, smem) : launch_alt2_t<TI, IPT, 32, false>(c, a, grid, smem);
-    return staged ? launch_alt2_t<TI, IPT, 0, true>(c, a, grid, smem) : launch_alt2_t<TI, IPT, 0, false>(c, a, grid, smem);
+    if (k32) return staged ? launch_alt2_t<TI, IPT, 32, true, NT>(c, a, grid, smem) : launch_alt2_t<TI, IPT, 32, false, NT>(c, a, grid, smem);
+    return staged ? launch_alt2_t<TI, IPT, 0, true, NT>(c, a, grid, smem) : launch_alt2_t<TI, IPT, 0, false, NT>(c, a, grid, smem);
 }
 
 template <int TI>
@@ -308,11 +309,13 @@ int launch_generic(spdnn *c, const ResArgs &a, int grid, size_t smem, bool k32, 
 
 int launch_resident(spdnn *c, int ti, int ipt, const ResArgs &a, int grid, size_t smem, int mode, bool k32, bool uniform) {
     if (mode == kResAlt2) {
-        if (ipt == 8) return ti == 32 ? launch_alt2<32, 8>(c, a, grid, smem, k32) : launch_alt2<16, 8>(c, a, grid, smem, k32);
+        // layers of at most 64 classes: blocks of 128 threads (one warp does the bit form; twice the blocks per SM)
+        if (ipt == 8 && ti == 32 && !a.bit_multi && c->alt2_small_blocks) return launch_alt2<32, 8, 128>(c, a, grid, smem, k32);
+        if (ipt == 8) return ti == 32 ? launch_alt2<32, 8, kThreads>(c, a, grid, smem, k32) : launch_alt2<16, 8, kThreads>(c, a, grid, smem, k32);
         switch (ti) {
-            case 16: return launch_alt2<16, 4>(c, a, grid, smem, k32);
-            case 8: return launch_alt2<8, 4>(c, a, grid, smem, k32);
-            default: return launch_alt2<4, 4>(c, a, grid, smem, k32);
+            case 16: return launch_alt2<16, 4, kThreads>(c, a, grid, smem, k32);
+            case 8: return launch_alt2<8, 4, kThreads>(c, a, grid, smem, k32);
+            default: return launch_alt2<4, 4, kThreads>(c, a, grid, smem, k32);
         }
     }
     switch (ti) {
@@ -719,6 +722,7 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
         if (const char *e = getenv("SPDNN_EXACT_SHORTCUT")) c->exact_shortcut = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BIT_FORM")) c->bit_form = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_LAZY_EXPAND")) c->lazy_expand = atoi(e) != 0;
+        if (const char *e = getenv("SPDNN_ALT2_SMALL_BLOCKS")) c->alt2_small_blocks = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_DENSE_DIRECT")) c->dense_direct = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_TABLE_RING")) c->table_ring_max = atoi(e) >= 4 ? 4 : 2;
         if (const char *e = getenv("SPDNN_WORD_RING")) c->word_ring_max = std::max(2, std::min(33, atoi(e)));
