@@ -126,6 +126,7 @@ __global__ void __launch_bounds__(NT, (NT == 128 ? 2 : 1) * SPDNN_ALT2_MIN_BLOCK
     __shared__ unsigned int s_grp[2][2];         // bit form, many warps: {unsaturated, last layer's outputs} of a group
     __shared__ int s_x[4];                       // state handed from the bit form to the block
     __shared__ int s_last, s_fail;
+    __shared__ int s_next_group;                 // the next group of tables to request (used by one thread at a time)
     __shared__ __align__(8) unsigned long long s_bar[kAlt2MaxTableRing];
     constexpr int NQ = IPT / 4;                  // float4 halves per thread
     constexpr int LPC = TI / IPT;                // threads per class
@@ -153,12 +154,13 @@ __global__ void __launch_bounds__(NT, (NT == 128 ? 2 : 1) * SPDNN_ALT2_MIN_BLOCK
         unsigned int *wring0 = nullptr;      // bit form: its word buffers, in the float buffer that is not `cur`
         const bool use_bits = a.bit_ok != 0;
         const int j0 = blockIdx.x * TI;
-        int next_group = 0;          // thread 0: the next group of tables to request
-        // Thread 0 requests the groups in order.  At the top of layer li every thread has left layer
+        // One thread requests the groups in order (thread 0 in the float form, the leader of the working
+        // warp in the bit form; barriers separate the two).  At the top of layer li every thread has left layer
         // li - 1, so the buffers of all groups before li's are free: groups up to (li's group) + tring - 1
         // may be on their way.
         auto issue_groups = [&](int li) {
             const int lim = min((li >> gshift) + tring, ngroups);
+            int next_group = s_next_group;
             while (next_group < lim) {
                 const int l0 = next_group << gshift, cnt = min(1 << gshift, a.nlayers - l0);
                 // orders the block's earlier reads of this buffer before the copy that overwrites it
@@ -168,6 +170,7 @@ __global__ void __launch_bounds__(NT, (NT == 128 ? 2 : 1) * SPDNN_ALT2_MIN_BLOCK
                                 (unsigned int)(cnt * stride), &s_bar[next_group & (tring - 1)]);
                 ++next_group;
             }
+            s_next_group = next_group;
         };
         auto wait_table = [&](int l) -> bool {        // bounded
             const int g = l >> gshift;
@@ -178,6 +181,7 @@ __global__ void __launch_bounds__(NT, (NT == 128 ? 2 : 1) * SPDNN_ALT2_MIN_BLOCK
                           : a.stream + (size_t)l * stride;
         };
         if (tid == 0) {
+            s_next_group = 0;
             s_alive[0] = 0u;
             s_ns[0] = 0;
             s_grp[0][0] = s_grp[0][1] = s_grp[1][0] = s_grp[1][1] = 0u;
@@ -260,6 +264,10 @@ __global__ void __launch_bounds__(NT, (NT == 128 ? 2 : 1) * SPDNN_ALT2_MIN_BLOCK
         int last_classes = 0;
         const bool force_dead = a.bias > 0.0f;
         const bool multi = a.bit_multi != 0;     // layers of more than one pass of 64 classes: all warps work in the bit form
+        // Otherwise ONE warp of the block does the bit form.  Warp w of every block sits on the same scheduler
+        // of an SM, so blocks that are likely to share an SM (numbers a multiple of the SM count apart) use
+        // different warps; a wrong guess only costs speed.
+        const int work_warp = (int)((blockIdx.x / (unsigned int)max(a.sm_count, 1)) % (NT / 32));
         int ws = 0;                  // bit form: the word buffer that holds the current activations
         bool bitmode = false;
         if (start_in_bits) {
@@ -273,7 +281,8 @@ __global__ void __launch_bounds__(NT, (NT == 128 ? 2 : 1) * SPDNN_ALT2_MIN_BLOCK
                 // ---- bit form.  Worker warps (warp 0 alone when a layer is one pass of 64 classes, else
                 //      all warps) apply groups of layers until the chunk ends, every image is dead, or a
                 //      layer yields an output that is neither 0 nor clip (redone in the float form).
-                if (multi || tid < 32) {
+                if (multi || warp == work_warp) {
+                    const bool leader = multi ? tid == 0 : lane == 0;
                     unsigned int alive = alive_prev;
                     int done_classes = last_classes;
                     int careful = 0;             // layers still to be applied one at a time
@@ -283,7 +292,7 @@ __global__ void __launch_bounds__(NT, (NT == 128 ? 2 : 1) * SPDNN_ALT2_MIN_BLOCK
                     TruthMasks tm = truth_masks(0u);
                     while (li < a.nlayers) {
                         if (STAGED && (li >> gshift) != waited_group) {
-                            if (tid == 0) issue_groups(li);
+                            if (leader) issue_groups(li);
                             const bool arrived = wait_table(li);
                             // one verdict for all workers, so that they leave the loop together
                             if (!(multi ? __syncthreads_and(arrived ? 1 : 0) != 0 : __all_sync(0xffffffffu, arrived))) {
@@ -338,8 +347,8 @@ __global__ void __launch_bounds__(NT, (NT == 128 ? 2 : 1) * SPDNN_ALT2_MIN_BLOCK
                                 o1 = select4(a1, b1, tm.hi) & keep;
                                 o2 = select4(a2, b2, tm.hi) & keep;
                                 ns |= (select4(a1, b1, tm.ns) | select4(a2, b2, tm.ns)) & keep;
-                                reinterpret_cast<unsigned int *>(wn)[lane] = o1;
-                                reinterpret_cast<unsigned int *>(wn)[lane + 32] = o2;
+                                reinterpret_cast<unsigned int *>(wn)[lane] = o1;         // rows_w >= 32
+                                if (lane + 32 < a.rows_w) reinterpret_cast<unsigned int *>(wn)[lane + 32] = o2;
                                 wc = wn;
                                 e = en;
                                 __syncwarp();
@@ -363,8 +372,8 @@ __global__ void __launch_bounds__(NT, (NT == 128 ? 2 : 1) * SPDNN_ALT2_MIN_BLOCK
                                     const unsigned int b2 = *reinterpret_cast<const unsigned int *>(wc + (e.y >> 16));
                                     const unsigned int x1 = select4(a1, b1, tm.hi) & keep, x2 = select4(a2, b2, tm.hi) & keep;
                                     ns |= (select4(a1, b1, tm.ns) | select4(a2, b2, tm.ns)) & keep;
-                                    reinterpret_cast<unsigned int *>(wn)[p * 64 + lane] = x1;
-                                    reinterpret_cast<unsigned int *>(wn)[p * 64 + 32 + lane] = x2;
+                                    if (p * 64 + lane < a.rows_w) reinterpret_cast<unsigned int *>(wn)[p * 64 + lane] = x1;
+                                    if (p * 64 + 32 + lane < a.rows_w) reinterpret_cast<unsigned int *>(wn)[p * 64 + 32 + lane] = x2;
                                     o1 |= p * 64 + lane < classes ? x1 : 0u;         // a slot past the classes does not count
                                     o2 |= p * 64 + 32 + lane < classes ? x2 : 0u;
                                 }
@@ -400,7 +409,7 @@ __global__ void __launch_bounds__(NT, (NT == 128 ? 2 : 1) * SPDNN_ALT2_MIN_BLOCK
                             careful = cnt;               // repeat the group from its first buffer, layer by layer
                             continue;
                         }
-                        if (now != alive && tid == 0) atomicAdd(a.died_at + li, __popc(alive & ~now));     // cnt == 1
+                        if (now != alive && leader) atomicAdd(a.died_at + li, __popc(alive & ~now));     // cnt == 1
                         alive = now;
                         ws = s;
                         li += cnt;
@@ -408,7 +417,7 @@ __global__ void __launch_bounds__(NT, (NT == 128 ? 2 : 1) * SPDNN_ALT2_MIN_BLOCK
                         if (careful > 0) --careful;
                         if (alive == 0u) break;
                     }
-                    if (tid == 0) {
+                    if (leader) {
                         s_x[0] = li; s_x[1] = (int)alive; s_x[2] = done_classes; s_x[3] = ws;
                         s_alive[li % 3] = 0u;        // the float form may take over at layer li
                         s_ns[li % 3] = 0;
@@ -521,7 +530,7 @@ __global__ void __launch_bounds__(NT, (NT == 128 ? 2 : 1) * SPDNN_ALT2_MIN_BLOCK
             // tables may still be on their way: wait for them (bounded) so that the block does not
             // exit, and its shared memory get reused, under a copy in flight
             if (tid == 0)
-                for (int g = min(li, a.nlayers - 1) >> gshift; g < next_group; ++g)
+                for (int g = min(li, a.nlayers - 1) >> gshift; g < s_next_group; ++g)
                     if (!mbar_wait(&s_bar[g & (tring - 1)], (unsigned int)((g >> tshift) & 1))) atomicExch(a.status, 4);
             __syncthreads();
         }

@@ -403,7 +403,7 @@ inline size_t alt2_smem_bytes(int ti, int rows, int stride, int gshift, int trin
 }
 
 // Enqueues the whole network: chunks of layers through the resident kernel where a group of
-// images fits in shared memory (chunk lengths chunk_first, x2, ... up to chunk_max: short while
+// images fits in shared memory (chunk lengths chunk_first, x chunk_growth, ... up to chunk_max: short while
 // images still die, long once the survivors are stable), one launch per layer otherwise.
 struct Step {
     int first = 0, count = 1;      // layers [first, first + count)
@@ -478,7 +478,7 @@ std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
                     // it starts from -- whatever of that fits
                     st.max_classes = maxc;
                     st.stride = alt2_stream_stride(maxc);
-                    st.rows_w = std::max(rows, (maxc + 63) / 64 * 64);
+                    st.rows_w = std::max(rows, 32);
                     auto afits = [&](int gs, int tr) {
                         return alt2_smem_bytes(ti, rows, st.stride, gs, tr) + 2048 <= (size_t)c->smem_optin;
                     };
@@ -512,7 +512,7 @@ std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
 }
 
 // Enqueues the whole network: chunks of layers through the resident kernel where a group of
-// images fits in shared memory (chunk lengths chunk_first, x2, ... up to chunk_max: short while
+// images fits in shared memory (chunk lengths chunk_first, x chunk_growth, ... up to chunk_max: short while
 // images still die, long once the survivors are stable), one launch per layer otherwise.  A
 // launch that is followed by a resident chunk writes only the one row per class that chunk
 // will read.
@@ -541,6 +541,7 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan) {
             a.layers = c->res_table + l; a.died_at = c->died_at + l; a.nlayers = st.count;
             a.buf_rows = st.rows; a.table_bytes = st.table;
             a.dense_in = st.dense ? c->dense_cell : nullptr;
+            a.sm_count = c->sm_count;
             a.stream = st.stream; a.stream_stride = st.stride; a.tgroup_shift = st.gshift; a.tring = st.tring;
             a.wring = st.wring; a.rows_w = st.rows_w; a.bit_multi = st.max_classes > 64 ? 1 : 0;
             a.n = c->n; a.bias = c->bias; a.clip = c->clip;

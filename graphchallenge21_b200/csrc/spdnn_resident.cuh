@@ -84,13 +84,14 @@ struct ResArgs {
     int tgroup_shift;         // staged: one bulk copy brings 1 << tgroup_shift layers of the stream
     int tring;                // staged: buffers of one such group (2 or 4); 0 = read the stream from global memory
     int wring;                // bit form: buffers of one word per row (>= 2)
-    int rows_w;               // bit form: words per buffer (>= buf_rows, covers all 64-class passes)
+    int rows_w;               // bit form: words per buffer (>= buf_rows and >= 32; a row past it belongs to no class)
     int bit_ok;               // bit form allowed (clip > 0, not switched off)
     int bit_multi;            // bit form: some layer of the chunk has more than 64 classes
     // First launch of a pass that reads the caller's row-major input (batch x n floats) in place: the cell
     // that holds its address (init_loop_kernel), else nullptr (the input is in yin, in tiles).  Loading the
     // block's rows into shared memory does the change of layout that dense_to_tiles_kernel would do.
     const float *const *dense_in;
+    int sm_count;             // SMs of the device (alt2_kernel spreads the working warps of its blocks by it)
 };
 
 __host__ __device__ __forceinline__ int resident_phys_row(int r) {
