@@ -9,7 +9,7 @@
 //    `stride` bytes per layer: a 16-byte header {classes, K, bits of w, truth table}, then per pass
 //    of 64 classes 32 slots of 8 bytes; slot `lane` holds the entries of classes 64p + lane and
 //    64p + 32 + lane, 4 bytes each: 4 * row a | (4 * row b) << 16 in plain row numbers (value ids;
-//    the float buffers keep row r at resident_phys_row(r)).  The output row of class u is u and is
+//    the float buffers keep row r at alt2_row_pos(r)).  The output row of class u is u and is
 //    not stored.  One bulk asynchronous copy (TMA) brings a GROUP of up
 //    to 8 layers into shared memory, several groups ahead of the layer being computed.
 //
@@ -103,6 +103,12 @@ __device__ __forceinline__ unsigned int select4(unsigned int wa, unsigned int wb
     const unsigned int t1 = (wa & m[3]) | (~wa & m[2]);
     return (wb & t1) | (~wb & t0);
 }
+
+// Where the float buffers keep row r.  With fewer than 32 images a row is shorter than the 128 bytes
+// the banks span, and rows are permuted (resident_phys_row) so that classes whose rows share one
+// parity do not pile onto the same banks; a row of 32 images covers all banks and stays where it is.
+template <int TI>
+__device__ __forceinline__ int alt2_row_pos(int r) { return TI == 32 ? r : resident_phys_row(r); }
 
 #ifndef SPDNN_ALT2_MIN_BLOCKS
 #define SPDNN_ALT2_MIN_BLOCKS 4      // blocks per SM asked of the compiler: <= 64 registers, no spills
@@ -213,12 +219,12 @@ __global__ void __launch_bounds__(NT, (NT == 128 ? 2 : 1) * SPDNN_ALT2_MIN_BLOCK
             if (my_valid != kFull) contiguous = false;
             const ResLayer L0 = a.layers[0];
             const bool fast_dense = dense && !L0.rep && L0.v_in == a.n && (a.n & 3) == 0 && (reinterpret_cast<size_t>(dense) & 15) == 0;
-            if (fast_dense) load_ns |= load_dense_rows<TI, NT, true>(dense, a.n, j0, live_in, L0.v_in, cur, a.clip);
+            if (fast_dense) load_ns |= load_dense_rows<TI, NT, true, TI != 32>(dense, a.n, j0, live_in, L0.v_in, cur, a.clip);
             for (int v = grp; v < L0.v_in && !fast_dense; v += CPI) {
                 // element of row r: r * 32 floats into a tile's column, r floats into a row-major image
                 size_t e = L0.rep ? (size_t)__ldg(L0.rep + v) : (size_t)v * 32;
                 if (dense) e >>= 5;
-                unsigned char *dst = cur + resident_phys_row(v) * RS + sub * TB;
+                unsigned char *dst = cur + alt2_row_pos<TI>(v) * RS + sub * TB;
 #pragma unroll
                 for (int h = 0; h < NQ; ++h) {
                     float4 x;
@@ -256,7 +262,7 @@ __global__ void __launch_bounds__(NT, (NT == 128 ? 2 : 1) * SPDNN_ALT2_MIN_BLOCK
                 m <<= sub * IPT;
 #pragma unroll
                 for (int s = 1; s < LPC; s <<= 1) m |= __shfl_xor_sync(0xffffffffu, m, s);
-                if (sub == 0 && r < a.buf_rows) w[resident_phys_row(r)] = m;       // words are kept by plain row number
+                if (sub == 0 && r < a.buf_rows) w[alt2_row_pos<TI>(r)] = m;       // words are kept by plain row number
             }
         };
         // ---- the layers of this chunk
@@ -431,7 +437,7 @@ __global__ void __launch_bounds__(NT, (NT == 128 ? 2 : 1) * SPDNN_ALT2_MIN_BLOCK
                 // back to floats: the rows the next float layer (or the expansion below) reads
                 const unsigned int *wcur = wring0 + (size_t)ws * a.rows_w;
                 for (int r = grp; r < a.buf_rows; r += CPI) {
-                    const unsigned int wv = wcur[resident_phys_row(r)] >> (sub * IPT);
+                    const unsigned int wv = wcur[alt2_row_pos<TI>(r)] >> (sub * IPT);
 #pragma unroll
                     for (int h = 0; h < NQ; ++h) {
                         const unsigned int q = wv >> (4 * h);
@@ -473,8 +479,8 @@ __global__ void __launch_bounds__(NT, (NT == 128 ? 2 : 1) * SPDNN_ALT2_MIN_BLOCK
             for (int u = grp; u < classes; u += CPI) {
                 const unsigned int *ep = reinterpret_cast<const unsigned int *>(T + alt2_entry_offset(u));
                 const unsigned int e = STAGED ? *ep : __ldg(ep);
-                const int ao = resident_phys_row((int)(e & 0xffffu) >> 2) * RS, bo = resident_phys_row((int)(e >> 18)) * RS;
-                unsigned char *out = nxt + resident_phys_row(u) * RS + sub * TB;
+                const int ao = alt2_row_pos<TI>((int)(e & 0xffffu) >> 2) * RS, bo = alt2_row_pos<TI>((int)(e >> 18)) * RS;
+                unsigned char *out = nxt + alt2_row_pos<TI>(u) * RS + sub * TB;
 #pragma unroll
                 for (int h = 0; h < NQ; ++h) {
                     const float4 va = *reinterpret_cast<const float4 *>(in + ao + 16 * h);
@@ -541,7 +547,7 @@ __global__ void __launch_bounds__(NT, (NT == 128 ? 2 : 1) * SPDNN_ALT2_MIN_BLOCK
             const int tile = j0 >> 5, lane0 = j0 & 31;
             float *out = a.yout + (size_t)tile * a.tile_stride + lane0 + sub * IPT;
             for (int u = grp; u < last_classes; u += CPI) {
-                const unsigned char *src = cur + resident_phys_row(u) * RS + sub * TB;
+                const unsigned char *src = cur + alt2_row_pos<TI>(u) * RS + sub * TB;
 #pragma unroll
                 for (int h = 0; h < NQ; ++h) {
                     const float4 y = *reinterpret_cast<const float4 *>(src + 16 * h);

@@ -272,7 +272,7 @@ __device__ __forceinline__ float finish_output(float sum, float bias, float clip
 // thread in flight before its stores; the scattered 4-byte stores are the change of layout.
 // Requires n % 4 == 0 and a 16-byte aligned base.  Returns (WANT_NS) whether any loaded value is
 // neither 0 nor clip.
-template <int TI, int NT, bool WANT_NS>
+template <int TI, int NT, bool WANT_NS, bool PERMUTE>
 __device__ __forceinline__ bool load_dense_rows(const float *dense, int n, int j0, int live_in, int rows, unsigned char *cur,
                                                 float clip) {
     constexpr int RS = TI * 4;
@@ -298,7 +298,7 @@ __device__ __forceinline__ bool load_dense_rows(const float *dense, int n, int j
             if (r < rows) {
                 // resident_phys_row flips the low bit of a row by the parity of the bits above it; r is a
                 // multiple of 4, so rows r, r+1 share the parity of r >> 1 and rows r+2, r+3 have the other one
-                const int par = __popc((unsigned int)(r >> 1)) & 1;
+                const int par = PERMUTE ? (__popc((unsigned int)(r >> 1)) & 1) : 0;
                 unsigned char *dst = cur + r * RS + i * 4;
                 *reinterpret_cast<float *>(dst + (0 ^ par) * RS) = x[u].x;
                 *reinterpret_cast<float *>(dst + (1 ^ par) * RS) = x[u].y;
@@ -380,7 +380,7 @@ resident_kernel(const ResArgs a) {
             if (my_valid != kFull) contiguous = false;
             const ResLayer L0 = a.layers[0];
             const bool fast_dense = dense && !L0.rep && L0.v_in == a.n && (a.n & 3) == 0 && (reinterpret_cast<size_t>(dense) & 15) == 0;
-            if (fast_dense) load_dense_rows<TI, NT, false>(dense, a.n, j0, live_in, L0.v_in, cur, a.clip);
+            if (fast_dense) load_dense_rows<TI, NT, false, true>(dense, a.n, j0, live_in, L0.v_in, cur, a.clip);
             for (int v = grp; v < L0.v_in && !fast_dense; v += CPI) {
                 // element of row r: r * 32 floats into a tile's column, r floats into a row-major image
                 size_t e = L0.rep ? (size_t)__ldg(L0.rep + v) : (size_t)v * 32;
