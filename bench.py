@@ -52,6 +52,7 @@ def parse():
     p.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                    help="weak: every GPU runs --batch images; strong: --batch images are split over the GPUs")
     p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--no-two-contexts", action="store_true", help="skip the end-to-end loop that alternates two contexts")
     p.add_argument("--no-per-layer-line", action="store_true",
                    help="skip the extra line that times the per-layer kernel alone (SPDNN_RESIDENT=0) against the HBM roofline")
     p.add_argument("--cpu-seconds", type=float, default=12.0, help="target CPU time of the cpu_baseline sample")
@@ -382,14 +383,54 @@ def main_ours(args):
         return e0.elapsed_time(e1), c_
     ms_e2e_dense, _ = time_e2e("dense")
     ms_e2e, cats = time_e2e("coo")
+
+    # -- the same end-to-end step with TWO contexts taking turns (each with its own stream and buffers, the
+    #    weights held twice): the host->device copy of step k+1's input runs while step k's pass computes
+    def time_e2e_two_contexts():
+        g2 = SpDNN(n, L, float(net.bias), device=local)
+        try:
+            for l in range(L):
+                g2.set_layer_csc(l, *net.layer_csc(l))
+            stream2 = torch.cuda.Stream()
+            g2.set_stream(stream2.cuda_stream)
+            ctx = [g, g2]
+
+            def enqueue(c):
+                c.set_input_coo(coo_img.numpy(), coo_neu.numpy(), None, B, rank * B, index_base=0)
+                c.infer_async()
+
+            for c in ctx:                      # graph build and warm-up of both
+                enqueue(c)
+                c.categories()
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0 = time.perf_counter()
+            e0.record(stream)
+            enqueue(ctx[0])
+            c_ = None
+            for k in range(args.steps):
+                if k + 1 < args.steps:
+                    enqueue(ctx[(k + 1) % 2])
+                c_ = ctx[k % 2].categories()   # D2H of step k's result (waits for step k only)
+            stream.wait_stream(stream2)
+            e1.record(stream)
+            barrier()
+            sampler.window(t0, time.perf_counter())
+            return e0.elapsed_time(e1), np.asarray(c_).copy()
+        finally:
+            g2.close()
+    ms_e2e_two, cats_two = (None, None) if args.no_two_contexts else time_e2e_two_contexts()
+    if cats_two is not None:
+        assert np.array_equal(cats_two, np.asarray(cats)), "the two-context loop returned other categories"
     clocks = sampler.stop() if rank == 0 else None
     e2e_prepare_ms = g.sync().prepare_ms          # H2D + layout conversion of the last end-to-end step
     d2h = int(len(cats) * 4 + (L + 1) * 16 + 4)
     all_cats = gather_categories(np.asarray(cats).copy())
-    t = torch.tensor([ms, ms_e2e, ms_e2e_dense], dtype=torch.float64, device="cuda")
+    t = torch.tensor([ms, ms_e2e, ms_e2e_dense, ms_e2e_two or 0.0], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, ms_e2e, ms_e2e_dense = float(t[0]), float(t[1]), float(t[2])
+    ms_e2e_two = float(t[3]) if ms_e2e_two is not None else None
     edges_step = float(world) * B * n * 32.0 * L
     out = None
     if rank == 0:
@@ -414,6 +455,10 @@ def main_ours(args):
                     "ms_per_step": ms_e2e / args.steps, "input_ms": e2e_prepare_ms,
                     "call": "spdnn_set_input_coo (the input file's img/neuron triplets, pinned host memory) + spdnn_infer "
                             "+ spdnn_get_categories",
+                    "two_contexts": None if ms_e2e_two is None else {
+                        "value": edges_step * args.steps / (ms_e2e_two * 1e-3), "ms_per_step": ms_e2e_two / args.steps,
+                        "call": "the same three calls on two contexts in turn (own stream and buffers each): the copy of "
+                                "step k+1's input overlaps step k's pass; every step's H2D and D2H are inside the region"},
                     "dense_input": {"value": edges_step * args.steps / (ms_e2e_dense * 1e-3), "h2d_bytes_per_step": B * n * 4,
                                     "ms_per_step": ms_e2e_dense / args.steps,
                                     "call": "spdnn_set_input_dense (batch x N fp32, pinned host memory)"}},
