@@ -284,7 +284,7 @@ __global__ void __launch_bounds__(NT, (NT == 128 ? 2 : 1) * SPDNN_ALT2_MIN_BLOCK
         }
         while (li < a.nlayers) {
             if (bitmode) {
-                // ---- bit form.  Worker warps (warp 0 alone when a layer is one pass of 64 classes, else
+                // ---- bit form.  Worker warps (one warp when a layer is one pass of 64 classes, else
                 //      all warps) apply groups of layers until the chunk ends, every image is dead, or a
                 //      layer yields an output that is neither 0 nor clip (redone in the float form).
                 if (multi || warp == work_warp) {
