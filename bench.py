@@ -104,7 +104,7 @@ class ClockSampler:
                 self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
                 self.stamps.append(time.perf_counter())
                 self.bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))
-                if len(self.samples) % 8 == 1:
+                if len(self.samples) % 32 == 16:      # the power query can take milliseconds: rarely, and not first
                     self.power.append(nv.nvmlDeviceGetPowerUsage(h) / 1000.0)
             except Exception:
                 pass
@@ -124,7 +124,8 @@ class ClockSampler:
                     pass
             h = nv.nvmlDeviceGetHandleByIndex(idx)
             self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
-            nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)          # first call pays for lazy set-up inside NVML
+            nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)          # first calls pay for lazy set-up inside NVML
+            nv.nvmlDeviceGetCurrentClocksEventReasons(h)
             self.nv, self.handle = nv, h
         except Exception:
             self.nv = self.handle = None

@@ -866,7 +866,7 @@ int spdnn_set_input_dense_device(spdnn_t *c, const float *y0_dev, int batch, int
     DeviceGuard guard(c->device);
     int rc = begin_input(c, batch, first_global_id);
     if (rc) return rc;
-    if (batch > 0 && graphs_ready(c) && c->graph_exec[1]) {
+    if (batch > 0 && c->dense_direct && graphs_ready(c) && c->graph_exec[1]) {
         c->dense_src = y0_dev;       // read in place by the first launch of the pass
         c->input_kind = 1;
         return end_input(c);
@@ -883,7 +883,7 @@ int spdnn_set_input_dense(spdnn_t *c, const float *y0, int batch, int first_glob
     int rc = begin_input(c, batch, first_global_id);
     if (rc) return rc;
     const size_t row_bytes = sizeof(float) * (size_t)c->n;
-    if (batch > 0 && (size_t)batch * row_bytes <= ((size_t)1 << 30) && graphs_ready(c) && c->graph_exec[1]) {
+    if (batch > 0 && c->dense_direct && (size_t)batch * row_bytes <= ((size_t)1 << 30) && graphs_ready(c) && c->graph_exec[1]) {
         // one copy into the staging buffer, which the first launch of the pass reads in place
         rc = ensure_stage(c, (size_t)batch * row_bytes);
         if (rc) return rc;
