@@ -26,6 +26,7 @@ class Stats(C.Structure):
 SYMBOLS = {
     "spdnn_create": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, C.c_float, C.c_float]),
     "spdnn_set_layer_csc": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "spdnn_set_layer_same_as": (C.c_int, [C.c_void_p, C.c_int, C.c_int]),
     "spdnn_set_layer_coo": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]),
     "spdnn_set_input_dense": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "spdnn_set_input_dense_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int]),

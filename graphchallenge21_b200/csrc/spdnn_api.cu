@@ -261,12 +261,10 @@ int blocks_per_sm(int k, bool uniform) {
 
 template <int TI, int IPT, int KT, bool UNIFORM, bool STAGED>
 int launch_resident_t(spdnn *c, const ResArgs &a, int grid, size_t smem) {
-    static bool configured[64] = {};
-    if (!configured[c->device & 63]) {
-        CK(cudaFuncSetAttribute(resident_kernel<TI, IPT, KT, UNIFORM, STAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                c->smem_optin - 1024));     // the kernel also has a little static shared memory
-        configured[c->device & 63] = true;
-    }
+    // set at every launch that is captured (a handful per graph build): the attribute is per device, and a flag
+    // shared between contexts would be a data race between host threads
+    CK(cudaFuncSetAttribute(resident_kernel<TI, IPT, KT, UNIFORM, STAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                            c->smem_optin - 1024));         // the kernel also has a little static shared memory
     resident_kernel<TI, IPT, KT, UNIFORM, STAGED><<<grid, SPDNN_GENERIC_THREADS, smem, c->stream>>>(a);
     CK(cudaGetLastError());
     return SPDNN_OK;
@@ -274,11 +272,7 @@ int launch_resident_t(spdnn *c, const ResArgs &a, int grid, size_t smem) {
 
 template <int TI, int IPT, int KT, bool STAGED, int NT>
 int launch_alt2_t(spdnn *c, const ResArgs &a, int grid, size_t smem) {
-    static bool configured[64] = {};
-    if (!configured[c->device & 63]) {
-        CK(cudaFuncSetAttribute(alt2_kernel<TI, IPT, KT, STAGED, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, c->smem_optin - 1024));
-        configured[c->device & 63] = true;
-    }
+    CK(cudaFuncSetAttribute(alt2_kernel<TI, IPT, KT, STAGED, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, c->smem_optin - 1024));
     alt2_kernel<TI, IPT, KT, STAGED, NT><<<grid, NT, smem, c->stream>>>(a);
     CK(cudaGetLastError());
     return SPDNN_OK;
@@ -584,7 +578,12 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan) {
             a.slot = c->slot; a.mask = c->mask; a.ids0 = c->ids[0]; a.ids1 = c->ids[1];
             a.counter = c->counter; a.work = c->counter + 1; a.status = c->status;
             a.died_at = c->died_at + l;
-            a.first_member_only = (next_resident && !L.identity_members) ? 1 : 0;
+            // one row per class suffices only when the chunk that follows reads through the representatives of
+            // this layer's classes; a layer whose canonical form was not kept on the host (budget) has no
+            // resident tables, the next layer then reads all N rows
+            const bool next_reads_reps = next_resident && c->res[l] && l + 1 < c->layers && c->res[l + 1] &&
+                                         c->res[l + 1]->rep != nullptr;
+            a.first_member_only = (next_reads_reps && !L.identity_members) ? 1 : 0;
             a.bias = c->bias; a.clip = c->clip;
             const long long ncb = (L.classes + d.classes_per_item - 1) / d.classes_per_item;
             if ((long long)c->tiles_cap * ncb >= 0xffffffffLL) return fail(c, SPDNN_ERR_LIMIT, "batch too large for one launch");
@@ -827,6 +826,21 @@ int spdnn_set_layer_csc(spdnn_t *c, int layer, const int32_t *col_ptr, const int
     }
     c->layer[layer] = L;
     c->shared[host->hash1] = L;
+    return SPDNN_OK;
+}
+
+int spdnn_set_layer_same_as(spdnn_t *c, int layer, int other_layer) {
+    if (!c) return SPDNN_ERR_ARG;
+    if (layer < 0 || layer >= c->layers || other_layer < 0 || other_layer >= c->layers)
+        return fail(c, SPDNN_ERR_ARG, "layer %d or %d out of range [0, %d)", layer, other_layer, c->layers);
+    if (!c->layer[other_layer]) return fail(c, SPDNN_ERR_STATE, "layer %d was never set", other_layer);
+    DeviceGuard guard(c->device);
+    if (c->in_flight) {
+        int rc = spdnn_sync(c, nullptr);
+        if (rc) return rc;
+    }
+    c->layer[layer] = c->layer[other_layer];
+    c->graph_dirty = true;
     return SPDNN_OK;
 }
 

@@ -167,7 +167,8 @@ extern "C" int spdnn_layer_static(const float *yin, float *yout, int neurons, in
                                   int32_t *survivors, int32_t *survivor_count, void *cuda_stream, char *err,
                                   int err_len) {
     if (!yin || !yout || !off || !survivors || !survivor_count) return say(err, err_len, SPDNN_ERR_ARG, "null device pointer");
-    if (neurons <= 0 || neurons > (1 << 26)) return say(err, err_len, SPDNN_ERR_ARG, "neurons must be in [1, 2^26]");
+    // the padding entry of `off` is neurons * 32 and must fit in int32
+    if (neurons <= 0 || neurons >= (1 << 26)) return say(err, err_len, SPDNN_ERR_ARG, "neurons must be in [1, 2^26)");
     if (k <= 0 || (k & 3)) return say(err, err_len, SPDNN_ERR_ARG, "k must be a positive multiple of 4");
     if (live_in < 0) return say(err, err_len, SPDNN_ERR_ARG, "live_in must be >= 0");
     if (live_in > SPDNN_STATIC_MAX_IMAGES) {

@@ -108,6 +108,22 @@ class SpDNN:
                 raise SpDNNError(-1, "val size must equal row_idx size")
         self._check(self._lib.spdnn_set_layer_csc(self._ctx, layer, _ptr(col_ptr), _ptr(row_idx), _ptr(val)))
 
+    def set_layer_same_as(self, layer: int, other_layer: int):
+        """Layer ``layer`` is the matrix of ``other_layer`` (set before): no data is passed again."""
+        self._check(self._lib.spdnn_set_layer_same_as(self._ctx, layer, other_layer))
+
+    def set_network(self, net):
+        """All layers of a generated network (``layer_csc(l)``, ``pattern_id(l)``): layers with equal
+        pattern ids are declared once and aliased afterwards."""
+        first = {}
+        for l in range(self.layers):
+            pid = net.pattern_id(l) if hasattr(net, "pattern_id") else l
+            if pid in first:
+                self.set_layer_same_as(l, first[pid])
+            else:
+                self.set_layer_csc(l, *net.layer_csc(l))
+                first[pid] = l
+
     def set_layer_rows(self, layer: int, rows, vals=None):
         """``rows`` int [N, K]: the K input neurons of every output neuron (entries < 0 are skipped)."""
         rows = np.asarray(rows)

@@ -19,10 +19,14 @@
  *
  * Conventions: every function returns SPDNN_OK (0) or a negative status and never exits
  * the process (the reference's Safe_Call does); spdnn_last_error() gives the message.
- * Host buffers are borrowed for the duration of the call.  All device memory belongs to
+ * Host buffers that describe LAYERS are borrowed for the duration of the call.  Host buffers that hold
+ * INPUT images are copied with cudaMemcpyAsync on the context's stream: from pageable memory the
+ * copy has read the buffer when the call returns, from page-locked (pinned) memory it may still be
+ * reading it, so keep a pinned input buffer unchanged until the next call that waits for the stream
+ * (spdnn_infer, spdnn_sync, spdnn_get_*) has returned.  All device memory belongs to
  * the context and is released by spdnn_destroy().  One context drives one GPU; different
- * contexts may be used from different host threads concurrently, one context must not be
- * used by two threads at once.
+ * contexts may be used from different host threads concurrently (no mutable state is shared
+ * between contexts), one context must not be used by two threads at once.
  */
 #ifndef SPDNN_B200_H
 #define SPDNN_B200_H
@@ -78,6 +82,13 @@ int spdnn_set_layer_csc(spdnn_t *ctx, int layer, const int32_t *col_ptr, const i
  * (src/utils/matrix.h:255-282 with T == false). */
 int spdnn_set_layer_coo(spdnn_t *ctx, int layer, int64_t nnz, const int32_t *in_neuron, const int32_t *out_neuron,
                         const float *val, int index_base);
+
+/* Layer `layer` is the same matrix as `other_layer`, which was set before: both share one device
+ * copy and the host-side preparation is not repeated.  (spdnn_set_layer_csc finds equal layers by
+ * content as well, but only after canonicalising the new one.)  The reference uploads every layer
+ * separately (all_network.cu:296-303); networks whose layers repeat with a short period -- its
+ * stride table all_network.cu:316-327 cycles -- make this the cheap way to declare 1920 of them. */
+int spdnn_set_layer_same_as(spdnn_t *ctx, int layer, int other_layer);
 
 /* Input images, dense batch x N row-major fp32 in HOST memory (the reference's `input`
  * vectors flattened, all_network.cu:240-248, 283-284).  Image i gets the global number
@@ -168,7 +179,12 @@ int spdnn_inspect_network_csc(int neurons, int layers, const int32_t *const *col
  *   cuda_stream    cudaStream_t as void* (NULL = default stream); the call only enqueues
  *   err, err_len   optional host buffer that receives the message of a failure
  *
- * Limits: at most SPDNN_STATIC_MAX_IMAGES images per call (SPDNN_ERR_LIMIT beyond that: split
+ * What a caller that chains calls must know: positions live_in .. 32 * ceil(live_in / 32) - 1 of yout (the
+ * unused lanes of the last tile) are overwritten with a copy of that tile's first image; row `neurons`
+ * of yout is never written, so a buffer that is fed back as yin must have that row zeroed once by its
+ * owner; live_in == 0 is valid (survivor_count becomes 0, nothing else is written).
+ *
+ * Limits: neurons < 2^26; at most SPDNN_STATIC_MAX_IMAGES images per call (SPDNN_ERR_LIMIT beyond that: split
  * the batch).  The scratch array (about 264 KB) is held by every GPU that loads the library
  * until the process exits and is shared by all calls on that GPU: calls that overlap on the
  * device race, so keep them on one stream or order them with events.  The first call on a

@@ -15,7 +15,9 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("SPDNN_REFERENCE", "/root/reference")
+# the reference's source tree: the directory named by SPDNN_REFERENCE, else a `reference` folder beside
+# this repository (where the build container keeps it); absent on the GPU box, which uses the built binary
+REF = os.environ.get("SPDNN_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def _compilers(names):

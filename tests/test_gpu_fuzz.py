@@ -16,16 +16,17 @@ pytestmark = pytest.mark.gpu
 
 SWITCHES = [{}, {"SPDNN_RESIDENT_TI": "16"}, {"SPDNN_RESIDENT_TI": "8"}, {"SPDNN_TABLE_GROUP": "4"}, {"SPDNN_WORD_RING": "3"},
             {"SPDNN_CHUNK_FIRST": "3", "SPDNN_CHUNK_GROWTH": "2"}, {"SPDNN_STAGE_TABLES": "0"}, {"SPDNN_RESIDENT_IPT": "4"},
-            {"SPDNN_ALT2_SMALL_BLOCKS": "0"}, {"SPDNN_CHUNK_MAX": "5"}, {"SPDNN_LAZY_EXPAND": "0"}, {"SPDNN_DENSE_DIRECT": "1"}]
+            {"SPDNN_ALT2_SMALL_BLOCKS": "0"}, {"SPDNN_CHUNK_MAX": "5"}, {"SPDNN_LAZY_EXPAND": "0"}, {"SPDNN_DENSE_DIRECT": "1"},
+            {"SPDNN_RESIDENT_TI": "4"}, {"SPDNN_WORD_RING": "2"}, {"SPDNN_BITS_KERNEL": "0"}]
 
 
 @pytest.mark.parametrize("seed", [11, 12, 13])
 def test_random_configurations_match_the_oracle(seed, monkeypatch, oracle):
     rng = random.Random(seed)
     for it in range(14):
-        n = rng.choice([1024, 1024, 1024, 4096])
-        L = rng.randint(5, 200 if n == 1024 else 50)
-        b = rng.choice([1, 31, 32, 33, 100, 257, 640, 1500, 3000])
+        n = rng.choice([1024, 1024, 1024, 4096, 4096, 16384, 65536])
+        L = rng.randint(5, {1024: 200, 4096: 50, 16384: 40, 65536: 24}[n])
+        b = rng.choice([1, 31, 32, 33, 100, 257, 640, 1500, 3000] if n <= 4096 else [1, 31, 33, 64, 100])
         bias = rng.choice([-0.3, -0.3, -0.35, 0.0, -1.0, -32.0, 0.01, -0.0625, -16.0])
         clip = rng.choice([32.0, 32.0, 32.0, 8.0, 2.5, 1.0, 100.0])
         for k in [k for k in os.environ if k.startswith("SPDNN_") and k not in ("SPDNN_B200_LIB", "SPDNN_DATA_DIR")]:
@@ -45,8 +46,11 @@ def test_random_configurations_match_the_oracle(seed, monkeypatch, oracle):
                 y0[1::3] *= np.float32(0.37 * clip)
         want_c, want_a, want_l = oracle.infer(y0, [(net.layer_rows(l), None) for l in range(L)], bias, clip=clip, first_image=7)
         with SpDNN(n, L, bias, clip=clip) as g:
-            for l in range(L):
-                g.set_layer_csc(l, *net.layer_csc(l))
+            if rng.random() < 0.5:
+                g.set_network(net)
+            else:
+                for l in range(L):
+                    g.set_layer_csc(l, *net.layer_csc(l))
             if rng.random() < 0.5:
                 g.set_input_dense(y0, 7)
             else:

@@ -16,10 +16,12 @@ GOLDEN = sorted(glob.glob(os.path.join(ROOT, "tests", "golden", "*.npz")))
 REL_TOL = 1e-5        # stated tolerance for activations; the tests below get 0 (bit-exact)
 
 
-def run_gpu(net, y0, first=0, how="dense", layers=None, vals=None, clip=32.0):
+def run_gpu(net, y0, first=0, how="dense", layers=None, vals=None, clip=32.0, alias=False, order=None):
     n, L = net.neurons, (net.layers if layers is None else layers)
     with SpDNN(n, L, float(net.bias), clip=clip) as g:
-        for l in range(L):
+        if alias:
+            g.set_network(net)           # equal layers declared once, then spdnn_set_layer_same_as
+        for l in ([] if alias else (order or range(L))):
             if vals is None:
                 g.set_layer_csc(l, *net.layer_csc(l))
             else:
@@ -148,6 +150,76 @@ def test_bit_form_of_saturated_activations(bias, clip, n, L, env, monkeypatch, o
     if key not in _BIT_FORM_WANT:
         _BIT_FORM_WANT[key] = oracle.infer(y0, [(r, None) for r in rows_of(net)], bias, clip=clip)
     check(run_gpu(net, y0, clip=clip), _BIT_FORM_WANT[key])
+
+
+_LARGE_WANT = {}
+
+
+def _large_case(oracle, bias, clip, n, L, b):
+    """Batch with every kind of image the bit form distinguishes: ordinary blobs, runs that are
+    saturated from the start (whole 32-image blocks begin a chunk as words), values off the
+    1/16 grid and all-clip images."""
+    net = SyntheticNetwork(n, L, "radix16", bias=bias)
+    y0 = synthetic_images(n, b)
+    y0[32:64] *= np.float32(clip)
+    y0[64:80:3] *= np.float32(0.37 * clip)
+    y0[80:88] = np.float32(clip)
+    key = (bias, clip, n, L, b)
+    if key not in _LARGE_WANT:
+        _LARGE_WANT[key] = oracle.infer(y0, [(r, None) for r in rows_of(net)], bias, clip=clip, first_image=11)
+    return net, y0, _LARGE_WANT[key]
+
+
+@pytest.mark.parametrize("env", [{}, {"SPDNN_BIT_FORM": "0"}, {"SPDNN_STAGE_TABLES": "0"}, {"SPDNN_RESIDENT_TI": "8"},
+                                 {"SPDNN_RESIDENT_TI": "4"}, {"SPDNN_WORD_RING": "2"}, {"SPDNN_CHUNK_FIRST": "3", "SPDNN_CHUNK_GROWTH": "2"},
+                                 {"SPDNN_BITS_KERNEL": "0"}],
+                         ids=lambda e: ",".join(f"{k[6:]}={v}" for k, v in e.items()) or "default")
+@pytest.mark.parametrize("bias,clip,n,L,b", [(-0.4, 32.0, 16384, 80, 96), (-0.45, 32.0, 65536, 48, 96)])
+def test_bit_form_at_the_large_network_sizes(bias, clip, n, L, b, env, monkeypatch, oracle):
+    """N = 16384 (1024 classes per layer) and N = 65536 (4096 classes): every warp of a block works
+    on a layer of the bit form, the tables are staged in small groups or read from global memory,
+    and the float form runs 16, 8 or 4 images per block.  These are the launch shapes of the two
+    largest challenge networks (the reference needed its 64-bit build for them,
+    src/microbenchmark/out_memory.cu:24,35,58)."""
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    net, y0, want = _large_case(oracle, bias, clip, n, L, b)
+    check(run_gpu(net, y0, first=11, clip=clip, alias=True), want)
+    assert 0 < len(want[0]) < b
+
+
+@pytest.mark.parametrize("n,L,b", [(4096, 240, 200), (16384, 130, 96)])
+def test_long_networks_enter_and_leave_the_bit_form_in_mid_chunk(n, L, b, oracle):
+    """Long enough for the chunks to grow to hundreds of layers with >= 256 classes per layer:
+    blocks enter the bit form in the middle of a chunk, images die inside it."""
+    net, y0, want = _large_case(oracle, float(SyntheticNetwork(n, 1).bias), 32.0, n, L, b)
+    check(run_gpu(net, y0, first=11, alias=True), want)
+
+
+@pytest.mark.parametrize("n,b", [(16384, 64), (65536, 32)])
+def test_full_depth_of_the_largest_networks(n, b, oracle):
+    """All 1920 layers of the two largest challenge networks on a small batch, against the oracle."""
+    L = 1920
+    net = SyntheticNetwork(n, L, "radix16")
+    y0 = synthetic_images(n, b, first_image=77)
+    want = oracle.infer(y0, [(r, None) for r in rows_of(net)], float(net.bias), first_image=77)
+    check(run_gpu(net, y0, first=77, alias=True), want)
+    assert 0 < len(want[0]) < b
+
+
+def test_layers_without_a_host_copy_mix_with_resident_chunks(oracle, monkeypatch):
+    """The canonical form of a layer is kept on the host only within a budget; a layer without it runs in
+    the per-layer kernel and must then write ALL rows, because the resident chunk behind it has no class
+    representatives to read through.  Layers are declared back to front so that layer 0 is the one that
+    does not fit the budget."""
+    monkeypatch.setenv("SPDNN_HOST_BUDGET_MB", "3")          # six of the eight distinct 512 KB layers
+    n, L, b = 4096, 20, 300
+    net = SyntheticNetwork(n, L, "radix16")
+    y0 = synthetic_images(n, b)
+    want = oracle.infer(y0, [(r, None) for r in rows_of(net)], float(net.bias))
+    check(run_gpu(net, y0, order=list(range(L - 1, -1, -1))), want)
+    monkeypatch.setenv("SPDNN_HOST_BUDGET_MB", "0")          # nothing kept: every layer in the per-layer kernel
+    check(run_gpu(net, y0), want)
 
 
 def test_positive_bias_all_zero_inputs_stay_alive(oracle):
