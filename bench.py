@@ -256,8 +256,7 @@ def per_layer_line(net, y_dev, cfg, device, stream, first_id, want_survivors, pa
         else:
             os.environ["SPDNN_RESIDENT"] = old
     try:
-        for l in range(L):
-            g.set_layer_csc(l, *net.layer_csc(l))
+        g.set_network(net)
         g.set_stream(stream.cuda_stream)
         ms, r = [], None
         for i in range(passes + 1):                   # the first pass builds the launch graph and warms up
@@ -300,8 +299,7 @@ def main_ours(args):
         B = (B + world - 1) // world              # contiguous slices of one batch, as src/multi_gpu.cpp:146-151
     net = SyntheticNetwork(n, L, args.pattern)
     g = SpDNN(n, L, float(net.bias), device=local)
-    for l in range(L):
-        g.set_layer_csc(l, *net.layer_csc(l))
+    g.set_network(net)
     info = g.layer_info(min(1, L - 1))
     if args.inputs == "mixed":
         from graphchallenge21_b200.generator import mixed_density_images
@@ -392,8 +390,7 @@ def main_ours(args):
     def time_e2e_two_contexts():
         g2 = SpDNN(n, L, float(net.bias), device=local)
         try:
-            for l in range(L):
-                g2.set_layer_csc(l, *net.layer_csc(l))
+            g2.set_network(net)
             stream2 = torch.cuda.Stream()
             g2.set_stream(stream2.cuda_stream)
             ctx = [g, g2]

@@ -148,7 +148,9 @@ __global__ void __launch_bounds__(NT, (NT == 128 ? 2 : 1) * SPDNN_ALT2_MIN_BLOCK
     const int buf_bytes = a.buf_rows * RS;
     const int stride = a.stream_stride;
 
-    if ((int)blockIdx.x < nblk) {
+    // a tile that the bits_kernel pre-pass finished is skipped (TI divides 32: a block lies inside one tile)
+    const bool tile_finished = a.tile_done != nullptr && (int)blockIdx.x < nblk && a.tile_done[(blockIdx.x * TI) >> 5] != 0;
+    if ((int)blockIdx.x < nblk && !tile_finished) {
         unsigned char *cur = smem, *nxt = smem + buf_bytes;
         unsigned char *const tbl0 = smem + 2 * buf_bytes;
         // Staged tables: group g = layers [g << gshift, (g + 1) << gshift) lives in buffer g & (tring - 1)

@@ -21,6 +21,7 @@
 #include "layer_inspect.h"
 #include "spdnn_kernels.cuh"
 #include "spdnn_alt2.cuh"
+#include "spdnn_bits.cuh"
 #include "spdnn_resident.cuh"
 
 using namespace spdnn_impl;
@@ -104,6 +105,12 @@ struct spdnn {
     std::vector<int32_t> host_died, host_live;
     int32_t *slot = nullptr;
     uint32_t *mask = nullptr;
+    unsigned char *tile_done = nullptr;   // [tiles] verdict of the bits_kernel pre-pass of an ALT2 chunk
+    bool bits_prepass = true;          // SPDNN_BITS_KERNEL=0: ALT2 chunks of wide layers run without the pre-pass
+    bool bits_first_chunk = false;     // SPDNN_BITS_FIRST=1: also before the first resident chunk of a pass
+    int bits_threads = 0;              // SPDNN_BITS_THREADS: threads per block of the pre-pass (0: by the classes)
+    int extra_launches = 0;            // pre-pass launches of the captured schedule
+    int graph_extra[2] = {0, 0};
     int32_t *ids[2] = {nullptr, nullptr};
     unsigned int *counter = nullptr;   // [0] blocks finished, [1] next work item
     int32_t *status = nullptr;
@@ -159,9 +166,10 @@ int fail(spdnn *c, int code, const char *fmt, ...) {
     } while (0)
 
 int free_buffers(spdnn *c) {
-    cudaFree(c->y[0]); cudaFree(c->y[1]); cudaFree(c->slot); cudaFree(c->mask);
+    cudaFree(c->y[0]); cudaFree(c->y[1]); cudaFree(c->slot); cudaFree(c->mask); cudaFree(c->tile_done);
     cudaFree(c->ids[0]); cudaFree(c->ids[1]);
     c->y[0] = c->y[1] = nullptr; c->slot = nullptr; c->mask = nullptr; c->ids[0] = c->ids[1] = nullptr;
+    c->tile_done = nullptr;
     c->tiles_cap = 0;
     return SPDNN_OK;
 }
@@ -180,6 +188,8 @@ int ensure_capacity(spdnn *c, int batch) {
     CK(cudaMalloc(&c->slot, sizeof(int32_t) * (size_t)tiles * 32));
     CK(cudaMalloc(&c->mask, sizeof(uint32_t) * (size_t)tiles));
     CK(cudaMemsetAsync(c->mask, 0, sizeof(uint32_t) * (size_t)tiles, c->stream));
+    CK(cudaMalloc(&c->tile_done, (size_t)tiles));
+    CK(cudaMemsetAsync(c->tile_done, 0, (size_t)tiles, c->stream));
     c->tiles_cap = tiles;
     return SPDNN_OK;
 }
@@ -407,6 +417,8 @@ struct Step {
     int stride = 0, gshift = 0, tring = 0, wring = 2, rows_w = 0, max_classes = 0;
     unsigned char *stream = nullptr;
     bool dense = false;            // resident chunk that reads the caller's row-major input in place
+    // bits_kernel pre-pass of an ALT2 chunk (0 threads: none): its own staging of the packed stream
+    int bits_threads = 0, bits_gshift = 0, bits_tring = 0, wwords = 0;
 };
 
 // The launches of one pass, front to back.
@@ -416,6 +428,7 @@ struct Step {
 std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
     std::vector<Step> plan;
     int l = 0, chunk = c->chunk_first;
+    int alt2_chunks = 0;           // ALT2 chunks planned so far
     while (l < c->layers) {
         Step st;
         st.first = l;
@@ -487,6 +500,27 @@ std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
                             for (int tr = 4; tr >= 2 && !st.tring; tr /= 2)
                                 if ((1 << gs) <= c->table_group_max && ((1 << gs) < 2 * f || gs == 0) && tr <= c->table_ring_max && afits(gs, tr) &&
                                     (size_t)tr * ((size_t)st.stride << gs) <= (size_t)c->smem_optin / 4) { st.gshift = gs; st.tring = tr; }
+                    // Pre-pass for tiles that are saturated already (bits_kernel): layers of more than one pass of 64
+                    // classes, where the float buffers leave this kernel's own bit form few images per block.  Not
+                    // before the first chunk of a pass, whose input is not saturated unless the images are.
+                    const int rows_max = std::max(rows, maxc);
+                    if (c->bits_prepass && c->bit_form && c->clip > 0.0f && maxc > 64 && rows_max <= 16383 &&
+                        (alt2_chunks > 0 || c->bits_first_chunk)) {
+                        st.wwords = (rows_max + 63) / 64 * 64;
+                        const int passes = (maxc + 63) / 64;
+                        int nt = c->bits_threads > 0 ? c->bits_threads : 32 * ((passes + 1) / 2);
+                        st.bits_threads = std::max(128, std::min(kBitsMaxThreads, (nt + 31) / 32 * 32));
+                        // table staging: groups of about 16 KB, four in flight when a group is one layer
+                        st.bits_gshift = 0; st.bits_tring = 0;
+                        if (c->stage_tables) {
+                            while (st.bits_gshift < 5 && ((size_t)st.stride << (st.bits_gshift + 1)) <= (size_t)20 << 10 &&
+                                   (1 << (st.bits_gshift + 1)) <= c->table_group_max) ++st.bits_gshift;
+                            st.bits_tring = st.bits_gshift == 0 ? 4 : 2;
+                            if (c->table_ring_max < st.bits_tring) st.bits_tring = 2;
+                            if ((size_t)st.wwords * 8 + (size_t)st.bits_tring * ((size_t)st.stride << st.bits_gshift) + 2048 > (size_t)c->smem_optin)
+                                st.bits_tring = 0;
+                        }
+                    }
                 }
                 // A lone layer that reads all N rows of every image but computes few classes from
                 // them (the first layer of a network with repeated columns) gains nothing from
@@ -499,6 +533,8 @@ std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
             }
         }
         if (st.ti) chunk = std::min(chunk * c->chunk_growth, c->chunk_max);
+        if (st.ti && st.max_classes > 0) ++alt2_chunks;
+        if (!(st.ti && st.max_classes > 0)) st.bits_threads = 0;
         plan.push_back(st);
         l += st.count;
     }
@@ -512,6 +548,7 @@ std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
 // will read.
 int enqueue_layers(spdnn *c, const std::vector<Step> &plan) {
     c->last_group = 0;
+    c->extra_launches = 0;
     for (size_t step = 0; step < plan.size(); ++step) {
         const Step &st = plan[step];
         const int l = st.first;
@@ -546,6 +583,27 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan) {
             const size_t smem = alt2 ? alt2_smem_bytes(st.ti, st.rows, st.stride, st.gshift, st.tring)
                                      : resident_smem_bytes(st.ti, st.rows, st.table);
             a.bit_ok = (alt2 && c->bit_form && c->clip > 0.0f && st.wring >= 2) ? 1 : 0;
+            a.tile_done = nullptr; a.wwords = 0;
+            if (alt2 && st.bits_threads > 0) {
+                // pre-pass: tiles of 32 images that are saturated already run the whole chunk as words
+                ResArgs b = a;
+                b.tile_done = c->tile_done; b.wwords = st.wwords;
+                b.tgroup_shift = st.bits_gshift; b.tring = st.bits_tring;
+                const size_t bsmem = (size_t)st.wwords * 8 + (size_t)st.bits_tring * ((size_t)st.stride << st.bits_gshift);
+                if (st.bits_tring > 0) {
+                    CK(cudaFuncSetAttribute(bits_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, c->smem_optin - 2048));
+                    bits_kernel<true><<<c->tiles_cap, st.bits_threads, bsmem, c->stream>>>(b);
+                } else {
+                    CK(cudaFuncSetAttribute(bits_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, c->smem_optin - 2048));
+                    bits_kernel<false><<<c->tiles_cap, st.bits_threads, bsmem, c->stream>>>(b);
+                }
+                CK(cudaGetLastError());
+                c->extra_launches += 1;
+                a.tile_done = c->tile_done;
+                if (c->print_schedule)
+                    fprintf(stderr, "[spdnn] step %zu: pre-pass for saturated tiles, layers %d..%d  %d threads per 32 images  %d words  smem %zu B  tables %s (%d layers per copy, %d in flight)\n",
+                            step, l, l + st.count - 1, st.bits_threads, st.wwords, bsmem, st.bits_tring ? "staged" : "global", 1 << st.bits_gshift, st.bits_tring);
+            }
             int rc = launch_resident(c, st.ti, st.ipt, a, grid, smem, R0.mode, R0.k == 32, R0.uniform);
             if (rc) return rc;
             c->last_group = st.ti;
@@ -626,6 +684,7 @@ int build_graph_kind(spdnn *c, int kind) {
     cudaGraphDestroy(g);
     if (e != cudaSuccess) return fail(c, SPDNN_ERR_CUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
     c->graph_steps[kind] = c->nsteps;
+    c->graph_extra[kind] = c->extra_launches;
     c->graph_group[kind] = c->last_group;
     c->graph_expand_layer[kind] = c->expand_layer_of_plan;
     return SPDNN_OK;
@@ -721,6 +780,9 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
         if (const char *e = getenv("SPDNN_PRINT_SCHEDULE")) c->print_schedule = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_EXACT_SHORTCUT")) c->exact_shortcut = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BIT_FORM")) c->bit_form = atoi(e) != 0;
+        if (const char *e = getenv("SPDNN_BITS_KERNEL")) c->bits_prepass = atoi(e) != 0;
+        if (const char *e = getenv("SPDNN_BITS_FIRST")) c->bits_first_chunk = atoi(e) != 0;
+        if (const char *e = getenv("SPDNN_BITS_THREADS")) c->bits_threads = std::max(0, std::min(kBitsMaxThreads, atoi(e)));
         if (const char *e = getenv("SPDNN_LAZY_EXPAND")) c->lazy_expand = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_ALT2_SMALL_BLOCKS")) c->alt2_small_blocks = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_DENSE_DIRECT")) c->dense_direct = atoi(e) != 0;
@@ -968,6 +1030,7 @@ int spdnn_infer_async(spdnn_t *c) {
     if (c->input_kind == 1 && !c->graph_exec[1])
         return fail(c, SPDNN_ERR_STATE, "the network changed after the input was set: set the input again");
     c->nsteps = c->graph_steps[c->input_kind];
+    c->extra_launches = c->graph_extra[c->input_kind];
     c->last_group = c->graph_group[c->input_kind];
     c->final_expand_layer = c->graph_expand_layer[c->input_kind];
     c->final_needs_expand = c->final_expand_layer >= 0;
@@ -1020,7 +1083,7 @@ int spdnn_sync(spdnn_t *c, spdnn_stats_t *stats) {
             bytes += 4.0 * (c->n + 1) + 8.0 * (double)c->layer[l]->nnz;
         }
         s.algorithmic_bytes = bytes;
-        s.kernel_launches = c->nsteps + 1 + c->prep_launches;      // + finalize_ids_kernel
+        s.kernel_launches = c->nsteps + c->extra_launches + 1 + c->prep_launches;      // + finalize_ids_kernel
         s.loop_launches = c->nsteps;
         s.resident_group = c->last_group;
         c->stats = s;

@@ -92,6 +92,10 @@ struct ResArgs {
     // block's rows into shared memory does the change of layout that dense_to_tiles_kernel would do.
     const float *const *dense_in;
     int sm_count;             // SMs of the device (alt2_kernel spreads the working warps of its blocks by it)
+    // ALT2 chunks with a bits_kernel pre-pass (spdnn_bits.cuh): one byte per tile of 32 images of the work list,
+    // 1 = the pre-pass finished the tile and alt2_kernel's blocks of that tile skip their work; nullptr = no pre-pass
+    unsigned char *tile_done;
+    int wwords;               // bits_kernel: words per word buffer (a multiple of 64)
 };
 
 __host__ __device__ __forceinline__ int resident_phys_row(int r) {

@@ -17,7 +17,8 @@ pytestmark = pytest.mark.gpu
 SWITCHES = [{}, {"SPDNN_RESIDENT_TI": "16"}, {"SPDNN_RESIDENT_TI": "8"}, {"SPDNN_TABLE_GROUP": "4"}, {"SPDNN_WORD_RING": "3"},
             {"SPDNN_CHUNK_FIRST": "3", "SPDNN_CHUNK_GROWTH": "2"}, {"SPDNN_STAGE_TABLES": "0"}, {"SPDNN_RESIDENT_IPT": "4"},
             {"SPDNN_ALT2_SMALL_BLOCKS": "0"}, {"SPDNN_CHUNK_MAX": "5"}, {"SPDNN_LAZY_EXPAND": "0"}, {"SPDNN_DENSE_DIRECT": "1"},
-            {"SPDNN_RESIDENT_TI": "4"}, {"SPDNN_WORD_RING": "2"}, {"SPDNN_BITS_KERNEL": "0"}]
+            {"SPDNN_RESIDENT_TI": "4"}, {"SPDNN_WORD_RING": "2"}, {"SPDNN_BITS_KERNEL": "0"},
+            {"SPDNN_BITS_FIRST": "1"}, {"SPDNN_BITS_FIRST": "1", "SPDNN_CHUNK_FIRST": "2"}, {"SPDNN_BITS_FIRST": "1", "SPDNN_BITS_THREADS": "256"}]
 
 
 @pytest.mark.parametrize("seed", [11, 12, 13])

@@ -128,7 +128,8 @@ _BIT_FORM_WANT = {}
 @pytest.mark.parametrize("env", [{}, {"SPDNN_BIT_FORM": "0"}, {"SPDNN_CHUNK_FIRST": "1", "SPDNN_CHUNK_MAX": "3"},
                                  {"SPDNN_RESIDENT_TI": "8"}, {"SPDNN_STAGE_TABLES": "0"}, {"SPDNN_RESIDENT_IPT": "4"},
                                  {"SPDNN_TABLE_GROUP": "1"}, {"SPDNN_TABLE_GROUP": "2", "SPDNN_TABLE_RING": "2"},
-                                 {"SPDNN_ALT2_SMALL_BLOCKS": "0"}, {"SPDNN_WORD_RING": "2"}])
+                                 {"SPDNN_ALT2_SMALL_BLOCKS": "0"}, {"SPDNN_WORD_RING": "2"}, {"SPDNN_BITS_FIRST": "1"},
+                                 {"SPDNN_BITS_FIRST": "1", "SPDNN_BITS_THREADS": "1024", "SPDNN_CHUNK_FIRST": "40"}])
 @pytest.mark.parametrize("bias,clip,n,L", [(-0.3, 32.0, 1024, 70), (0.0, 32.0, 1024, 70), (-32.0, 32.0, 1024, 70), (0.01, 32.0, 1024, 70),
                                            (-0.3, 8.0, 1024, 70), (-1.0, 2.5, 1024, 70), (-0.35, 32.0, 4096, 50), (0.0, 16.0, 4096, 50)])
 def test_bit_form_of_saturated_activations(bias, clip, n, L, env, monkeypatch, oracle):
@@ -172,7 +173,9 @@ def _large_case(oracle, bias, clip, n, L, b):
 
 @pytest.mark.parametrize("env", [{}, {"SPDNN_BIT_FORM": "0"}, {"SPDNN_STAGE_TABLES": "0"}, {"SPDNN_RESIDENT_TI": "8"},
                                  {"SPDNN_RESIDENT_TI": "4"}, {"SPDNN_WORD_RING": "2"}, {"SPDNN_CHUNK_FIRST": "3", "SPDNN_CHUNK_GROWTH": "2"},
-                                 {"SPDNN_BITS_KERNEL": "0"}],
+                                 {"SPDNN_BITS_KERNEL": "0"}, {"SPDNN_BITS_FIRST": "1"}, {"SPDNN_BITS_FIRST": "1", "SPDNN_BITS_THREADS": "128"},
+                                 {"SPDNN_BITS_FIRST": "1", "SPDNN_STAGE_TABLES": "0"}, {"SPDNN_BITS_FIRST": "1", "SPDNN_TABLE_GROUP": "1", "SPDNN_TABLE_RING": "2"},
+                                 {"SPDNN_BITS_FIRST": "1", "SPDNN_CHUNK_FIRST": "1", "SPDNN_CHUNK_MAX": "3"}],
                          ids=lambda e: ",".join(f"{k[6:]}={v}" for k, v in e.items()) or "default")
 @pytest.mark.parametrize("bias,clip,n,L,b", [(-0.4, 32.0, 16384, 80, 96), (-0.45, 32.0, 65536, 48, 96)])
 def test_bit_form_at_the_large_network_sizes(bias, clip, n, L, b, env, monkeypatch, oracle):
