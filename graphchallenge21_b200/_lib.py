@@ -31,6 +31,8 @@ SYMBOLS = {
     "spdnn_set_input_dense": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "spdnn_set_input_dense_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
     "spdnn_set_input_coo": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]),
+    "spdnn_set_input_bits": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int]),
+    "spdnn_set_input_bits_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int]),
     "spdnn_infer": (C.c_int, [C.c_void_p, C.POINTER(Stats)]),
     "spdnn_infer_async": (C.c_int, [C.c_void_p]),
     "spdnn_sync": (C.c_int, [C.c_void_p, C.POINTER(Stats)]),

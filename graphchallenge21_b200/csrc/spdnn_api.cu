@@ -22,6 +22,7 @@
 #include "spdnn_kernels.cuh"
 #include "spdnn_alt2.cuh"
 #include "spdnn_bits.cuh"
+#include "spdnn_front.cuh"
 #include "spdnn_resident.cuh"
 
 using namespace spdnn_impl;
@@ -106,6 +107,16 @@ struct spdnn {
     int32_t *slot = nullptr;
     uint32_t *mask = nullptr;
     unsigned char *tile_done = nullptr;   // [tiles] verdict of the bits_kernel pre-pass of an ALT2 chunk
+    // Binary inputs (spdnn_front.cuh): the input as one word per (tile, neuron); in_flag is raised on the device
+    // while an input is converted when it holds a value other than 0 and 1, and picks the variant of the first
+    // layer's launches; has_floats marks the tiles whose float form was written.
+    uint32_t *xw = nullptr;
+    int nw = 0;
+    int32_t *in_flag = nullptr;
+    unsigned char *has_floats = nullptr;
+    bool binary_front = true;          // SPDNN_BINARY_FRONT=0: inputs are always converted to float tiles
+    bool fused_front = true;           // SPDNN_FUSED_FRONT=0: layer 0 of a binary input runs in the per-layer kernel
+                                       // even where the first ALT2 chunk could compute it while loading
     bool bits_prepass = true;          // SPDNN_BITS_KERNEL=0: ALT2 chunks of wide layers run without the pre-pass
     bool bits_first_chunk = false;     // SPDNN_BITS_FIRST=1: also before the first resident chunk of a pass
     int bits_threads = 0;              // SPDNN_BITS_THREADS: threads per block of the pre-pass (0: by the classes)
@@ -117,6 +128,7 @@ struct spdnn {
 
     void *stage = nullptr;             // device staging for host inputs / outputs
     size_t stage_bytes = 0;
+    size_t stage_chunk = (size_t)512 << 20;   // SPDNN_STAGE_KB: most bytes of a host input staged per copy
 
     int batch = 0, first_id = 0;
     bool input_ready = false, result_ready = false, in_flight = false, prep_timed = false;
@@ -167,9 +179,9 @@ int fail(spdnn *c, int code, const char *fmt, ...) {
 
 int free_buffers(spdnn *c) {
     cudaFree(c->y[0]); cudaFree(c->y[1]); cudaFree(c->slot); cudaFree(c->mask); cudaFree(c->tile_done);
-    cudaFree(c->ids[0]); cudaFree(c->ids[1]);
+    cudaFree(c->ids[0]); cudaFree(c->ids[1]); cudaFree(c->xw); cudaFree(c->has_floats);
     c->y[0] = c->y[1] = nullptr; c->slot = nullptr; c->mask = nullptr; c->ids[0] = c->ids[1] = nullptr;
-    c->tile_done = nullptr;
+    c->tile_done = nullptr; c->xw = nullptr; c->has_floats = nullptr;
     c->tiles_cap = 0;
     return SPDNN_OK;
 }
@@ -190,6 +202,10 @@ int ensure_capacity(spdnn *c, int batch) {
     CK(cudaMemsetAsync(c->mask, 0, sizeof(uint32_t) * (size_t)tiles, c->stream));
     CK(cudaMalloc(&c->tile_done, (size_t)tiles));
     CK(cudaMemsetAsync(c->tile_done, 0, (size_t)tiles, c->stream));
+    CK(cudaMalloc(&c->xw, sizeof(uint32_t) * (size_t)tiles * c->nw));
+    CK(cudaMemsetAsync(c->xw, 0, sizeof(uint32_t) * (size_t)tiles * c->nw, c->stream));     // incl. the zero words behind the neurons
+    CK(cudaMalloc(&c->has_floats, (size_t)tiles));
+    CK(cudaMemsetAsync(c->has_floats, 0, (size_t)tiles, c->stream));
     c->tiles_cap = tiles;
     return SPDNN_OK;
 }
@@ -221,6 +237,24 @@ int begin_input(spdnn *c, int batch, int first_global_id) {
     c->dense_src = nullptr;
     c->input_kind = 0;
     CK(cudaEventRecord(c->ev_prep0, c->stream));
+    // the input counts as binary until a conversion kernel sees another value; with the binary front
+    // switched off every input takes the float path
+    CK(cudaMemsetAsync(c->in_flag, c->binary_front ? 0 : 1, 1, c->stream));
+    CK(cudaMemsetAsync(c->has_floats, 0, (size_t)((batch + 31) / 32 > 0 ? (batch + 31) / 32 : 1), c->stream));
+    return SPDNN_OK;
+}
+
+// An input that turned out not to be binary after some of its tiles were converted as words only: their
+// float form is rebuilt from the words (those tiles held zeros and ones).
+int repair_float_tiles(spdnn *c) {
+    const int tiles = (c->batch + 31) / 32;
+    if (!c->binary_front || tiles == 0) return SPDNN_OK;
+    const long long warps = (long long)tiles * c->n;
+    const int grid = (int)std::min<long long>((warps + 7) / 8, (long long)c->sm_count * 32);
+    words_to_tiles_kernel<<<std::max(1, grid), 256, 0, c->stream>>>(c->xw, c->nw, c->n, tiles, c->y[0], c->tile_stride, c->has_floats,
+                                                                     c->in_flag, 1);
+    CK(cudaGetLastError());
+    c->prep_launches += 1;
     return SPDNN_OK;
 }
 
@@ -239,7 +273,15 @@ int convert_dense_device(spdnn *c, const float *dev_rows, int rows, int first_ti
     // rows is a multiple of 32 except for the last chunk
     const dim3 block(32, 8), grid((rows + 31) / 32, (c->n + kLayoutCols - 1) / kLayoutCols);
     if (rows <= 0) return SPDNN_OK;
-    dense_to_tiles_kernel<<<grid, block, 0, c->stream>>>(dev_rows, c->y[0], c->n, rows, c->tile_stride, first_tile);
+    if (c->binary_front) {
+        // words first (this raises the flag when a value is neither 0 nor 1); the float tiles only once the flag is up
+        const dim3 wgrid((rows + 31) / 32, (c->n + 1023) / 1024);
+        dense_to_words_kernel<<<wgrid, block, 0, c->stream>>>(dev_rows, c->n, rows, c->xw, c->nw, first_tile, c->in_flag);
+        CK(cudaGetLastError());
+        c->prep_launches += 1;
+    }
+    dense_to_tiles_kernel<<<grid, block, 0, c->stream>>>(dev_rows, c->y[0], c->n, rows, c->tile_stride, first_tile,
+                                                         c->binary_front ? c->in_flag : nullptr, c->has_floats);
     CK(cudaGetLastError());
     c->prep_launches += 1;
     return SPDNN_OK;
@@ -247,7 +289,8 @@ int convert_dense_device(spdnn *c, const float *dev_rows, int rows, int first_ti
 
 template <int KT, bool UNIFORM>
 int launch_layer_t(spdnn *c, const LayerDesc &d, const LayerArgs &a, int grid) {
-    layer_kernel<KT, UNIFORM><<<grid, kThreads, 0, c->stream>>>(d, a);
+    if (a.xw != nullptr) layer_kernel<KT, UNIFORM, true><<<grid, kThreads, 0, c->stream>>>(d, a);      // input as words
+    else layer_kernel<KT, UNIFORM, false><<<grid, kThreads, 0, c->stream>>>(d, a);
     CK(cudaGetLastError());
     return SPDNN_OK;
 }
@@ -546,9 +589,38 @@ std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
 // images still die, long once the survivors are stable), one launch per layer otherwise.  A
 // launch that is followed by a resident chunk writes only the one row per class that chunk
 // will read.
-int enqueue_layers(spdnn *c, const std::vector<Step> &plan) {
+//
+// gated: the pass may start from a binary input kept as words (spdnn_front.cuh).  The launches of the first
+// layer then exist twice, one variant per value of the flag that the input conversion leaves on the device
+// (0: binary, read the words; 1: read the float tiles), and each checks the flag at entry:
+//   kFrontWords   layer 0 runs in the per-layer kernel, whose BITS variant gathers from the words;
+//   kFrontFused   layer 0 is followed by an ALT2 chunk, which computes it from the words while loading
+//                 (the per-layer launch of layer 0 is then the float variant only);
+//   kFrontExpand  the pass starts with a resident chunk: the words are expanded to float tiles first.
+enum { kFrontNone = 0, kFrontWords = 1, kFrontFused = 2, kFrontExpand = 3 };
+
+int enqueue_layers(spdnn *c, const std::vector<Step> &plan, bool gated) {
     c->last_group = 0;
     c->extra_launches = 0;
+    int front = kFrontNone;
+    if (gated) {
+        if (plan[0].ti == 0) {
+            front = kFrontWords;
+            if (c->fused_front && plan.size() > 1 && plan[1].ti != 0 && plan[1].first == 1 && c->res[0] && c->res[1] &&
+                c->res[1]->mode == kResAlt2 && c->res[0]->mode == kResGeneric && c->res[0]->uniform && c->res[0]->k <= 252 &&
+                c->res[0]->v_in == c->n && c->res[0]->rep == nullptr && c->res[1]->v_in == c->res[0]->classes)
+                front = kFrontFused;
+        } else {
+            front = kFrontExpand;
+            const long long warps = (long long)c->tiles_cap * c->n;
+            const int grid = (int)std::min<long long>((warps + 7) / 8, (long long)c->sm_count * 32);
+            words_to_tiles_kernel<<<std::max(1, grid), 256, 0, c->stream>>>(c->xw, c->nw, c->n, c->tiles_cap, c->y[0], c->tile_stride,
+                                                                             nullptr, c->in_flag, 0);
+            CK(cudaGetLastError());
+            c->extra_launches += 1;
+            if (c->print_schedule) fprintf(stderr, "[spdnn] binary inputs: words expanded to float tiles before step 0\n");
+        }
+    }
     for (size_t step = 0; step < plan.size(); ++step) {
         const Step &st = plan[step];
         const int l = st.first;
@@ -584,9 +656,24 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan) {
                                      : resident_smem_bytes(st.ti, st.rows, st.table);
             a.bit_ok = (alt2 && c->bit_form && c->clip > 0.0f && st.wring >= 2) ? 1 : 0;
             a.tile_done = nullptr; a.wwords = 0;
+            a.front_words = nullptr; a.front_nw = 0; a.front_layer = nullptr; a.front_died_at = nullptr; a.front_ctl_copy = nullptr;
+            a.gate = nullptr; a.gate_want = 0;
+            if (front == kFrontFused && step == 1) {
+                // binary inputs: this chunk computes layer 0 from the words while it loads; it starts from the
+                // state before layer 0 and stands for steps 0 and 1
+                ResArgs f = a;
+                f.ctl_in = c->ctl; f.front_ctl_copy = c->ctl + 1;
+                f.front_words = c->xw; f.front_nw = c->nw; f.front_layer = c->res_table; f.front_died_at = c->died_at;
+                f.gate = c->in_flag; f.gate_want = 0;
+                int rc = launch_resident(c, st.ti, st.ipt, f, grid, smem, R0.mode, R0.k == 32, R0.uniform);
+                if (rc) return rc;
+                c->extra_launches += 1;
+                if (c->print_schedule) fprintf(stderr, "[spdnn] step 1, binary inputs: the chunk computes layer 0 from the input words\n");
+                a.gate = c->in_flag; a.gate_want = 1;
+            }
             if (alt2 && st.bits_threads > 0) {
                 // pre-pass: tiles of 32 images that are saturated already run the whole chunk as words
-                ResArgs b = a;
+                ResArgs b = a;                 // (gated like the launch it prepares)
                 b.tile_done = c->tile_done; b.wwords = st.wwords;
                 b.tgroup_shift = st.bits_gshift; b.tring = st.bits_tring;
                 const size_t bsmem = (size_t)st.wwords * 8 + (size_t)st.bits_tring * ((size_t)st.stride << st.bits_gshift);
@@ -643,9 +730,21 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan) {
                                          c->res[l + 1]->rep != nullptr;
             a.first_member_only = (next_reads_reps && !L.identity_members) ? 1 : 0;
             a.bias = c->bias; a.clip = c->clip;
+            a.xw = nullptr; a.nw = 0; a.gate = nullptr; a.gate_want = 0;
             const long long ncb = (L.classes + d.classes_per_item - 1) / d.classes_per_item;
             if ((long long)c->tiles_cap * ncb >= 0xffffffffLL) return fail(c, SPDNN_ERR_LIMIT, "batch too large for one launch");
             int grid = c->grid_override > 0 ? c->grid_override : c->sm_count * blocks_per_sm(L.k, L.uniform);
+            if (step == 0 && (front == kFrontWords || front == kFrontFused)) {
+                if (front == kFrontWords) {
+                    LayerArgs w = a;           // binary inputs: gather from the words
+                    w.xw = c->xw; w.nw = c->nw; w.gate = c->in_flag; w.gate_want = 0;
+                    int rc = launch_layer(c, d, w, grid, L.uniform);
+                    if (rc) return rc;
+                    c->extra_launches += 1;
+                    if (c->print_schedule) fprintf(stderr, "[spdnn] step 0, binary inputs: per-layer kernel on the input words\n");
+                }
+                a.gate = c->in_flag; a.gate_want = 1;
+            }
             int rc = launch_layer(c, d, a, grid, L.uniform);
             if (rc) return rc;
             if (c->print_schedule)
@@ -676,7 +775,7 @@ int build_graph_kind(spdnn *c, int kind) {
     CK(cudaStreamSynchronize(c->stream));
     cudaGraph_t g = nullptr;
     CK(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
-    int rc = enqueue_layers(c, plan);
+    int rc = enqueue_layers(c, plan, kind == 0 && c->binary_front);
     cudaError_t e = cudaStreamEndCapture(c->stream, &g);
     if (rc) { if (g) cudaGraphDestroy(g); return rc; }
     if (e != cudaSuccess) return fail(c, SPDNN_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
@@ -743,6 +842,7 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
     if (device < 0 || device >= count) return fail(c, SPDNN_ERR_ARG, "device %d not present (%d devices)", device, count);
     c->device = device; c->n = neurons; c->layers = layers; c->bias = bias; c->clip = clip;
     c->tile_stride = ((long long)neurons + 1) * 32;
+    c->nw = front_words_per_tile(neurons);
     DeviceGuard guard(device);
     cudaDeviceProp prop;
     CK(cudaGetDeviceProperties(&prop, device));
@@ -760,6 +860,8 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
     CK(cudaMalloc(&c->dense_cell, sizeof(const float *)));
     CK(cudaMemset(c->dense_cell, 0, sizeof(const float *)));
     CK(cudaMemset(c->status, 0, sizeof(int32_t)));
+    CK(cudaMalloc(&c->in_flag, sizeof(int32_t)));
+    CK(cudaMemset(c->in_flag, 0, sizeof(int32_t)));
     CK(cudaMalloc(&c->died_at, sizeof(int32_t) * (size_t)layers));
     CK(cudaMemset(c->died_at, 0, sizeof(int32_t) * (size_t)layers));
     CK(cudaMalloc(&c->res_table, sizeof(ResLayer) * (size_t)layers));
@@ -780,6 +882,9 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
         if (const char *e = getenv("SPDNN_PRINT_SCHEDULE")) c->print_schedule = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_EXACT_SHORTCUT")) c->exact_shortcut = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BIT_FORM")) c->bit_form = atoi(e) != 0;
+        if (const char *e = getenv("SPDNN_STAGE_KB")) c->stage_chunk = (size_t)std::max(1, atoi(e)) << 10;
+        if (const char *e = getenv("SPDNN_BINARY_FRONT")) c->binary_front = atoi(e) != 0;
+        if (const char *e = getenv("SPDNN_FUSED_FRONT")) c->fused_front = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BITS_KERNEL")) c->bits_prepass = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BITS_FIRST")) c->bits_first_chunk = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BITS_THREADS")) c->bits_threads = std::max(0, std::min(kBitsMaxThreads, atoi(e)));
@@ -807,7 +912,7 @@ void spdnn_destroy(spdnn_t *c) {
         if (c->graph_exec[kind]) cudaGraphExecDestroy(c->graph_exec[kind]);
     cudaFree(c->dense_cell);
     free_buffers(c);
-    cudaFree(c->ctl); cudaFree(c->counter); cudaFree(c->status); cudaFree(c->stage);
+    cudaFree(c->ctl); cudaFree(c->counter); cudaFree(c->status); cudaFree(c->stage); cudaFree(c->in_flag);
     cudaFree(c->died_at); cudaFree(c->res_table);
     for (unsigned char *p : c->streams) cudaFree(p);
     c->layer.clear();
@@ -949,6 +1054,8 @@ int spdnn_set_input_dense_device(spdnn_t *c, const float *y0_dev, int batch, int
     }
     rc = convert_dense_device(c, y0_dev, batch, 0);
     if (rc) return rc;
+    rc = repair_float_tiles(c);
+    if (rc) return rc;
     return end_input(c);
 }
 
@@ -969,7 +1076,7 @@ int spdnn_set_input_dense(spdnn_t *c, const float *y0, int batch, int first_glob
         return end_input(c);
     }
     // staged through a device buffer in chunks of whole tiles
-    size_t chunk_rows = std::max<size_t>(32, ((size_t)512 << 20) / row_bytes / 32 * 32);
+    size_t chunk_rows = std::max<size_t>(32, c->stage_chunk / row_bytes / 32 * 32);
     chunk_rows = std::min<size_t>(chunk_rows, (size_t)(batch + 31) / 32 * 32);
     if (batch > 0) {
         rc = ensure_stage(c, chunk_rows * row_bytes);
@@ -981,6 +1088,8 @@ int spdnn_set_input_dense(spdnn_t *c, const float *y0, int batch, int first_glob
         rc = convert_dense_device(c, (const float *)c->stage, (int)rows, (int)(r0 / 32));
         if (rc) return rc;
     }
+    rc = repair_float_tiles(c);
+    if (rc) return rc;
     return end_input(c);
 }
 
@@ -993,7 +1102,14 @@ int spdnn_set_input_coo(spdnn_t *c, int64_t nnz, const int32_t *img, const int32
     int rc = begin_input(c, batch, first_global_id);
     if (rc) return rc;
     const int tiles = (batch + 31) / 32;
-    if (tiles) CK(cudaMemsetAsync(c->y[0], 0, sizeof(float) * (size_t)tiles * c->tile_stride, c->stream));
+    // Triplets without values are ones: a binary input, kept as words only.  With values both forms are built
+    // (the words' flag tells the pass which one to read).
+    const bool words = c->binary_front, floats = !c->binary_front || val != nullptr;
+    if (tiles && floats) {
+        CK(cudaMemsetAsync(c->y[0], 0, sizeof(float) * (size_t)tiles * c->tile_stride, c->stream));
+        CK(cudaMemsetAsync(c->has_floats, 1, (size_t)tiles, c->stream));
+    }
+    if (tiles && words) CK(cudaMemsetAsync(c->xw, 0, sizeof(uint32_t) * (size_t)tiles * c->nw, c->stream));
     const int64_t chunk = std::min<int64_t>(std::max<int64_t>(nnz, 1), (int64_t)32 << 20);
     const size_t per = val ? 12 : 8;
     if (nnz) {
@@ -1008,12 +1124,82 @@ int spdnn_set_input_coo(spdnn_t *c, int64_t nnz, const int32_t *img, const int32
         CK(cudaMemcpyAsync(d_neu, neuron + s, sizeof(int32_t) * (size_t)m, cudaMemcpyHostToDevice, c->stream));
         if (val) CK(cudaMemcpyAsync(d_val, val + s, sizeof(float) * (size_t)m, cudaMemcpyHostToDevice, c->stream));
         const int grid = (int)std::min<int64_t>((m + 255) / 256, (int64_t)c->sm_count * 16);
-        coo_to_tiles_kernel<<<grid, 256, 0, c->stream>>>(d_img, d_neu, d_val, m, index_base, c->n, batch, c->y[0],
-                                                         c->tile_stride, c->status);
+        if (words) {
+            coo_to_words_kernel<<<grid, 256, 0, c->stream>>>(d_img, d_neu, d_val, m, index_base, c->n, batch, c->xw, c->nw,
+                                                             c->in_flag, c->status);
+            CK(cudaGetLastError());
+            c->prep_launches += 1;
+        }
+        if (floats) {
+            coo_to_tiles_kernel<<<grid, 256, 0, c->stream>>>(d_img, d_neu, d_val, m, index_base, c->n, batch, c->y[0],
+                                                             c->tile_stride, c->status);
+            CK(cudaGetLastError());
+            c->prep_launches += 1;
+        }
+    }
+    return end_input(c);
+}
+
+// Packed rows on the device -> words; with the binary front switched off, on to float tiles.
+static int convert_bits_device(spdnn *c, const uint32_t *dev_rows, long long row_words, int rows, int first_tile) {
+    if (rows <= 0) return SPDNN_OK;
+    const long long warps = (long long)((rows + 31) / 32) * ((c->n + 31) / 32);
+    const int grid = (int)std::min<long long>((warps + 7) / 8, (long long)c->sm_count * 32);
+    rows_to_words_kernel<<<std::max(1, grid), 256, 0, c->stream>>>(dev_rows, row_words, c->n, rows, c->xw, c->nw, first_tile);
+    CK(cudaGetLastError());
+    c->prep_launches += 1;
+    return SPDNN_OK;
+}
+
+static int finish_bits_input(spdnn *c) {
+    if (!c->binary_front && c->batch > 0) {
+        // every pass reads float tiles: expand the words (the flag is 1 for the whole life of such a context)
+        const int tiles = (c->batch + 31) / 32;
+        const long long warps = (long long)tiles * c->n;
+        const int grid = (int)std::min<long long>((warps + 7) / 8, (long long)c->sm_count * 32);
+        words_to_tiles_kernel<<<std::max(1, grid), 256, 0, c->stream>>>(c->xw, c->nw, c->n, tiles, c->y[0], c->tile_stride, nullptr,
+                                                                         c->in_flag, 1);
         CK(cudaGetLastError());
         c->prep_launches += 1;
     }
     return end_input(c);
+}
+
+int spdnn_set_input_bits_device(spdnn_t *c, const uint8_t *bits_dev, int64_t row_bytes, int batch, int first_global_id) {
+    if (!c) return SPDNN_ERR_ARG;
+    if (!bits_dev && batch > 0) return fail(c, SPDNN_ERR_ARG, "input pointer is null");
+    if (row_bytes < (c->n + 7) / 8 || (row_bytes & 3) || (reinterpret_cast<size_t>(bits_dev) & 3))
+        return fail(c, SPDNN_ERR_ARG, "row_bytes must be a multiple of 4 and at least ceil(neurons / 8); the buffer 4-byte aligned");
+    DeviceGuard guard(c->device);
+    int rc = begin_input(c, batch, first_global_id);
+    if (rc) return rc;
+    rc = convert_bits_device(c, reinterpret_cast<const uint32_t *>(bits_dev), row_bytes / 4, batch, 0);
+    if (rc) return rc;
+    return finish_bits_input(c);
+}
+
+int spdnn_set_input_bits(spdnn_t *c, const uint8_t *bits, int64_t row_bytes, int batch, int first_global_id) {
+    if (!c) return SPDNN_ERR_ARG;
+    if (!bits && batch > 0) return fail(c, SPDNN_ERR_ARG, "input pointer is null");
+    if (row_bytes < (c->n + 7) / 8 || (row_bytes & 3))
+        return fail(c, SPDNN_ERR_ARG, "row_bytes must be a multiple of 4 and at least ceil(neurons / 8)");
+    DeviceGuard guard(c->device);
+    int rc = begin_input(c, batch, first_global_id);
+    if (rc) return rc;
+    // staged through a device buffer in chunks of whole tiles
+    size_t chunk_rows = std::max<size_t>(32, c->stage_chunk / 2 / (size_t)row_bytes / 32 * 32);
+    chunk_rows = std::min<size_t>(chunk_rows, (size_t)(batch + 31) / 32 * 32);
+    if (batch > 0) {
+        rc = ensure_stage(c, chunk_rows * (size_t)row_bytes);
+        if (rc) return rc;
+    }
+    for (size_t r0 = 0; r0 < (size_t)batch; r0 += chunk_rows) {
+        const size_t rows = std::min(chunk_rows, (size_t)batch - r0);
+        CK(cudaMemcpyAsync(c->stage, bits + r0 * (size_t)row_bytes, rows * (size_t)row_bytes, cudaMemcpyHostToDevice, c->stream));
+        rc = convert_bits_device(c, (const uint32_t *)c->stage, row_bytes / 4, (int)rows, (int)(r0 / 32));
+        if (rc) return rc;
+    }
+    return finish_bits_input(c);
 }
 
 int spdnn_infer_async(spdnn_t *c) {
@@ -1131,7 +1317,7 @@ int spdnn_get_activations(spdnn_t *c, float *y, int64_t capacity_rows) {
     if (!y || capacity_rows < live) return fail(c, SPDNN_ERR_ARG, "capacity %lld < survivors %d", (long long)capacity_rows, live);
     DeviceGuard guard(c->device);
     const size_t row_bytes = sizeof(float) * (size_t)c->n;
-    size_t chunk_rows = std::max<size_t>(32, ((size_t)512 << 20) / row_bytes / 32 * 32);
+    size_t chunk_rows = std::max<size_t>(32, c->stage_chunk / row_bytes / 32 * 32);
     chunk_rows = std::min<size_t>(chunk_rows, (size_t)(live + 31) / 32 * 32);
     int rc = ensure_stage(c, chunk_rows * row_bytes);
     if (rc) return rc;

@@ -38,6 +38,7 @@ __global__ void __launch_bounds__(kBitsMaxThreads, 1) bits_kernel(const ResArgs 
     __shared__ int s_next_group;
     __shared__ int s_nev, s_ev_layer[32], s_ev_cnt[32];      // deaths seen so far (at most one per image)
     __shared__ __align__(8) unsigned long long s_bar[kAlt2MaxTableRing];
+    if (a.gate != nullptr && *a.gate != a.gate_want) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const LoopCtl ctl = *a.ctl_in;
     const int live_in = ctl.live;

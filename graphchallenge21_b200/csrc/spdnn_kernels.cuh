@@ -64,6 +64,14 @@ struct LayerArgs {
     int32_t *died_at;          // where the per-layer kernel records how many images died in its layer (or nullptr)
     int first_member_only;     // 1: the next launch reads one row per class (its first member): store only that row
     float bias, clip;
+    // BITS variant (first layer of a pass on a binary input): the input is one word per (tile, neuron),
+    // nw words per tile, bit i = image i of the tile is 1.0 (spdnn_front.cuh)
+    const uint32_t *xw;
+    int nw;
+    // the launch runs only when *gate == gate_want (nullptr: always): the first layer exists in a variant
+    // for binary inputs and one for any input, and the flag raised while the input was converted picks one
+    const int32_t *gate;
+    int gate_want;
 };
 
 // L2 residency hints of the per-layer kernel (SPDNN_L2_HINT: 0 none, 1 input rows are read
@@ -110,8 +118,16 @@ __device__ __forceinline__ float relu_clip(float x, float clip) {
 
 // Sum of one class for this lane's image: the K inputs in ascending input order, one fp32
 // add after the other, starting from 0 -- the order of src/utils/cpu_spmm.h:14-43.
-template <int KT, bool UNIFORM>
-__device__ __forceinline__ float class_sum(const LayerDesc &d, int u, const float *__restrict__ yin, unsigned long long pol = 0) {
+// One gathered input of this lane's image: element `o` (row * 32) of the tile at yin -- or, BITS, bit
+// `lane` of word `o >> 5` of the tile's words (yin then points at those words).
+template <bool BITS>
+__device__ __forceinline__ float in_value(const float *__restrict__ yin, int o, unsigned long long pol, int lane) {
+    if (BITS) return ((__ldg(reinterpret_cast<const uint32_t *>(yin) + (o >> 5)) >> lane) & 1u) ? 1.0f : 0.0f;
+    return load_row(yin + o, pol);
+}
+
+template <int KT, bool UNIFORM, bool BITS = false>
+__device__ __forceinline__ float class_sum(const LayerDesc &d, int u, const float *__restrict__ yin, unsigned long long pol = 0, int lane = 0) {
     float acc = 0.0f;
     if (KT > 0) {
         constexpr int KA = KT > 0 ? KT : 4;      // array extent (the branch is dead for KT == 0)
@@ -124,7 +140,7 @@ __device__ __forceinline__ float class_sum(const LayerDesc &d, int u, const floa
         }
         float v[KA];
 #pragma unroll
-        for (int i = 0; i < KT; ++i) v[i] = load_row(yin + o[i], pol);
+        for (int i = 0; i < KT; ++i) v[i] = in_value<BITS>(yin, o[i], pol, lane);
         if (UNIFORM) {
 #pragma unroll
             for (int i = 0; i < KT; ++i) acc = __fadd_rn(acc, v[i]);
@@ -145,7 +161,8 @@ __device__ __forceinline__ float class_sum(const LayerDesc &d, int u, const floa
         const float4 *w4 = UNIFORM ? nullptr : reinterpret_cast<const float4 *>(d.vals + (size_t)u * k);
         for (int i = 0; i < k / 4; ++i) {
             const int4 t = __ldg(o4 + i);
-            const float a = load_row(yin + t.x, pol), b = load_row(yin + t.y, pol), c = load_row(yin + t.z, pol), e = load_row(yin + t.w, pol);
+            const float a = in_value<BITS>(yin, t.x, pol, lane), b = in_value<BITS>(yin, t.y, pol, lane), c = in_value<BITS>(yin, t.z, pol, lane),
+                        e = in_value<BITS>(yin, t.w, pol, lane);
             if (UNIFORM) {
                 acc = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(acc, a), b), c), e);
             } else {
@@ -236,11 +253,12 @@ __device__ __forceinline__ void move_id(const LoopCtl &ctl, int32_t *ids0, int32
 // tiles and an uneven last wave costs one item, not one block's whole share.  Inside an item
 // every warp takes a contiguous run of classes: the host orders classes so that neighbours
 // share input rows, and the second read of a row then hits in L1.
-template <int KT, bool UNIFORM>
+template <int KT, bool UNIFORM, bool BITS = false>
 __global__ void __launch_bounds__(kThreads, SPDNN_MIN_BLOCKS) layer_kernel(const LayerDesc d, const LayerArgs a) {
     __shared__ unsigned int s_mask;
     __shared__ unsigned int s_item;
     __shared__ int s_last;
+    if (a.gate != nullptr && *a.gate != a.gate_want) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const LoopCtl ctl = *a.ctl_in;
     const int live_in = ctl.live;
@@ -267,7 +285,8 @@ __global__ void __launch_bounds__(kThreads, SPDNN_MIN_BLOCKS) layer_kernel(const
         const int jj = valid ? j : tile * 32;               // padding lanes shadow lane 0 and are masked out
         const int src = ctl.identity ? jj : __ldg(a.slot + jj);
         if (!ctl.identity && cb == 0 && warp == 0 && valid) move_id(ctl, a.ids0, a.ids1, j, src);
-        const float *__restrict__ yin = a.yin + (size_t)(src >> 5) * a.tile_stride + (src & 31);
+        const float *__restrict__ yin = BITS ? reinterpret_cast<const float *>(a.xw + (size_t)(src >> 5) * a.nw)
+                                             : a.yin + (size_t)(src >> 5) * a.tile_stride + (src & 31);
         float *__restrict__ yout = a.yout + (size_t)tile * a.tile_stride + lane;
         bool any = false;
         const int u_end = min(d.classes, (cb + 1) * cpi);
@@ -282,7 +301,7 @@ __global__ void __launch_bounds__(kThreads, SPDNN_MIN_BLOCKS) layer_kernel(const
                 me = __ldg(d.mem_ptr + u + 1);
                 mreg = (mb + lane < me) ? __ldg(d.mem + mb + lane) : 0;
             }
-            const float s = class_sum<KT, UNIFORM>(d, u, yin, pol_in);
+            const float s = class_sum<KT, UNIFORM, BITS>(d, u, yin, pol_in, src & 31);
             const float y = relu_clip(__fadd_rn(s, a.bias), a.clip);
             any |= (y != 0.0f);
             const int cnt = a.first_member_only ? 1 : me - mb;
@@ -316,10 +335,14 @@ __global__ void __launch_bounds__(kThreads, SPDNN_MIN_BLOCKS) layer_kernel(const
 // moves 32 images x kLayoutCols neurons, 512 contiguous bytes of every image's row, so that the reads
 // stay within few DRAM pages; all of a thread's 16 loads are in flight before the first store.
 constexpr int kLayoutCols = 128;
+// With a gate the kernel runs only once *gate is non-zero (the input is known not to be binary, see
+// spdnn_front.cuh) and marks the tiles it wrote in has_floats.
 static __global__ void dense_to_tiles_kernel(const float *__restrict__ in, float *__restrict__ out, int n, int batch,
-                                      long long tile_stride, int first_tile) {
+                                      long long tile_stride, int first_tile, const int32_t *gate, unsigned char *has_floats) {
     __shared__ float t[32][kLayoutCols + 1];
+    if (gate != nullptr && *gate == 0) return;
     const int c0 = blockIdx.y * kLayoutCols, tile = blockIdx.x;
+    if (gate != nullptr && blockIdx.y == 0 && threadIdx.x == 0 && threadIdx.y == 0) has_floats[first_tile + tile] = 1;
     const int img0 = tile * 32;
     float v[4][kLayoutCols / 32];
 #pragma unroll

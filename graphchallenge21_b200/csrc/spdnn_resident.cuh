@@ -96,6 +96,17 @@ struct ResArgs {
     // 1 = the pre-pass finished the tile and alt2_kernel's blocks of that tile skip their work; nullptr = no pre-pass
     unsigned char *tile_done;
     int wwords;               // bits_kernel: words per word buffer (a multiple of 64)
+    // First chunk of a pass on a binary input (spdnn_front.cuh): alt2_kernel computes the layer BEFORE the chunk
+    // (front_layer: GENERIC tables over the neurons, uniform weight, K <= 252) from the input's bit matrix while it
+    // loads, instead of reading that layer's output from yin.  nullptr = the chunk's input is in yin.
+    const uint32_t *front_words;
+    int front_nw;             // words per tile of the bit matrix
+    const ResLayer *front_layer;
+    int32_t *front_died_at;   // where the images that die in the front layer are counted
+    LoopCtl *front_ctl_copy;  // the record between the front layer and the chunk, which no launch writes in this variant
+    // the launch runs only when *gate == gate_want (nullptr: always), see LayerArgs
+    const int32_t *gate;
+    int gate_want;
 };
 
 __host__ __device__ __forceinline__ int resident_phys_row(int r) {
@@ -337,6 +348,7 @@ resident_kernel(const ResArgs a) {
     __shared__ unsigned int s_alive[3];
     __shared__ int s_last, s_fail;
     __shared__ __align__(8) unsigned long long s_bar[2];
+    if (a.gate != nullptr && *a.gate != a.gate_want) return;
     constexpr int NQ = IPT / 4;                  // float4 halves per thread
     constexpr int LPC = TI / IPT;                // threads per class
     constexpr int CPI = NT / LPC;                // classes per pass of the block
@@ -558,6 +570,7 @@ resident_kernel(const ResArgs a) {
     la.died_at = nullptr;
     la.first_member_only = 0;
     la.bias = a.bias; la.clip = a.clip;
+    la.xw = nullptr; la.nw = 0; la.gate = nullptr; la.gate_want = 0;
     rebuild_worklist(la, live_in, ctl.ids_buf);
 }
 

@@ -184,6 +184,23 @@ class SpDNN:
         self._check(self._lib.spdnn_set_input_coo(self._ctx, i.size, _ptr(i), _ptr(n), _ptr(v), batch, first_global_id,
                                                   index_base))
 
+    def set_input_bits(self, bits, first_global_id: int = 0):
+        """``bits``: uint8 [batch, row_bytes] bit matrix, bit (n & 7) of byte n >> 3 of row i = neuron n of image
+        i is 1.0 (``pack_bits`` makes it); a numpy array / CPU torch tensor (host path) or a CUDA torch tensor."""
+        if hasattr(bits, "is_cuda"):
+            import torch
+            if bits.dim() != 2 or bits.dtype != torch.uint8 or not bits.is_contiguous():
+                raise SpDNNError(-1, "bit matrix must be contiguous uint8 [batch, row_bytes]")
+            self.batch = int(bits.shape[0])
+            fn = self._lib.spdnn_set_input_bits_device if bits.is_cuda else self._lib.spdnn_set_input_bits
+            self._check(fn(self._ctx, C.c_void_p(bits.data_ptr()), int(bits.shape[1]), self.batch, first_global_id))
+            return
+        bits = np.ascontiguousarray(bits, dtype=np.uint8)
+        if bits.ndim != 2:
+            raise SpDNNError(-1, "bit matrix must be [batch, row_bytes]")
+        self.batch = int(bits.shape[0])
+        self._check(self._lib.spdnn_set_input_bits(self._ctx, _ptr(bits), int(bits.shape[1]), self.batch, first_global_id))
+
     # -- the loop --------------------------------------------------------------
     @staticmethod
     def _result(s: _lib.Stats) -> InferResult:
@@ -222,6 +239,15 @@ class SpDNN:
         y = np.empty((count, self.neurons), dtype=np.float32)
         self._check(self._lib.spdnn_get_activations(self._ctx, _ptr(y) if count else None, count))
         return y
+
+
+def pack_bits(y0: np.ndarray) -> np.ndarray:
+    """[batch, N] array -> the bit matrix ``set_input_bits`` takes (non-zero = 1), rows padded to whole 32-bit words."""
+    y0 = np.asarray(y0)
+    b, n = y0.shape
+    out = np.zeros((b, (n + 31) // 32 * 4), dtype=np.uint8)
+    out[:, : (n + 7) // 8] = np.packbits(y0 != 0, axis=1, bitorder="little")
+    return out
 
 
 def inspect_network(neurons: int, layer_csc) -> dict:

@@ -108,6 +108,16 @@ int spdnn_set_input_dense_device(spdnn_t *ctx, const float *y0_dev, int batch, i
 int spdnn_set_input_coo(spdnn_t *ctx, int64_t nnz, const int32_t *img, const int32_t *neuron, const float *val,
                         int batch, int first_global_id, int index_base);
 
+/* Input images as a bit matrix in HOST memory: image i is row i of `row_bytes` bytes, bit (n & 7) of byte
+ * n >> 3 set = neuron n of the image is 1.0, clear = 0.0 (numpy: packbits(y0 != 0, axis=1, bitorder="little")).
+ * row_bytes is a multiple of 4 and at least ceil(neurons / 8).  The challenge's inputs are binary -- every
+ * entry of the reference's input file carries the value 1 (src/network.cpp:49-51 logs anything else) -- so this
+ * is the same information as spdnn_set_input_coo's triplets or spdnn_set_input_dense's matrix in 1/32 of the
+ * dense bytes; it replaces the same H2D upload of A_d (all_network.cu:283-284).  The _device form takes the
+ * matrix from a 4-byte aligned buffer on the context's GPU. */
+int spdnn_set_input_bits(spdnn_t *ctx, const uint8_t *bits, int64_t row_bytes, int batch, int first_global_id);
+int spdnn_set_input_bits_device(spdnn_t *ctx, const uint8_t *bits_dev, int64_t row_bytes, int batch, int first_global_id);
+
 /* The layer loop of all_network.cu:333-519: all layers on the images of the last
  * set_input, with dead images removed on the device after every layer.  Blocks until the
  * result is on the device and fills *stats (may be NULL).  Consumes the input. */

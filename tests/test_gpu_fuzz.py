@@ -18,7 +18,8 @@ SWITCHES = [{}, {"SPDNN_RESIDENT_TI": "16"}, {"SPDNN_RESIDENT_TI": "8"}, {"SPDNN
             {"SPDNN_CHUNK_FIRST": "3", "SPDNN_CHUNK_GROWTH": "2"}, {"SPDNN_STAGE_TABLES": "0"}, {"SPDNN_RESIDENT_IPT": "4"},
             {"SPDNN_ALT2_SMALL_BLOCKS": "0"}, {"SPDNN_CHUNK_MAX": "5"}, {"SPDNN_LAZY_EXPAND": "0"}, {"SPDNN_DENSE_DIRECT": "1"},
             {"SPDNN_RESIDENT_TI": "4"}, {"SPDNN_WORD_RING": "2"}, {"SPDNN_BITS_KERNEL": "0"},
-            {"SPDNN_BITS_FIRST": "1"}, {"SPDNN_BITS_FIRST": "1", "SPDNN_CHUNK_FIRST": "2"}, {"SPDNN_BITS_FIRST": "1", "SPDNN_BITS_THREADS": "256"}]
+            {"SPDNN_BITS_FIRST": "1"}, {"SPDNN_BITS_FIRST": "1", "SPDNN_CHUNK_FIRST": "2"}, {"SPDNN_BITS_FIRST": "1", "SPDNN_BITS_THREADS": "256"},
+            {"SPDNN_BINARY_FRONT": "0"}, {"SPDNN_FUSED_FRONT": "0"}, {"SPDNN_RESIDENT": "0"}]
 
 
 @pytest.mark.parametrize("seed", [11, 12, 13])
@@ -52,7 +53,11 @@ def test_random_configurations_match_the_oracle(seed, monkeypatch, oracle):
             else:
                 for l in range(L):
                     g.set_layer_csc(l, *net.layer_csc(l))
-            if rng.random() < 0.5:
+            fmt = rng.random()
+            if fmt < 0.25 and kind in ("blobs", "mixed"):
+                from graphchallenge21_b200.network import pack_bits
+                g.set_input_bits(pack_bits(y0), 7)
+            elif fmt < 0.6:
                 g.set_input_dense(y0, 7)
             else:
                 img, neu, val = generator.dense_to_coo_1based(y0)

@@ -7,13 +7,14 @@ import numpy as np
 import pytest
 
 from conftest import ROOT, mixed_density_images, rows_of
-from graphchallenge21_b200 import SpDNN, SpDNNError, _lib, generator
+from graphchallenge21_b200 import SpDNN, SpDNNError, _lib, generator, network
 from graphchallenge21_b200.generator import SyntheticNetwork, synthetic_images
 
 pytestmark = pytest.mark.gpu
 
 GOLDEN = sorted(glob.glob(os.path.join(ROOT, "tests", "golden", "*.npz")))
 REL_TOL = 1e-5        # stated tolerance for activations; the tests below get 0 (bit-exact)
+_LARGE_WANT = {}      # oracle results shared by the parametrised cases of one input
 
 
 def run_gpu(net, y0, first=0, how="dense", layers=None, vals=None, clip=32.0, alias=False, order=None):
@@ -34,6 +35,11 @@ def run_gpu(net, y0, first=0, how="dense", layers=None, vals=None, clip=32.0, al
         elif how == "device":
             import torch
             g.set_input_dense(torch.from_numpy(y0).cuda(), first)
+        elif how == "bits":
+            g.set_input_bits(network.pack_bits(y0), first)
+        elif how == "bits_device":
+            import torch
+            g.set_input_bits(torch.from_numpy(network.pack_bits(y0)).cuda(), first)
         res = g.infer()
         return g.categories().copy(), g.activations(), g.layer_live().copy(), res
 
@@ -52,7 +58,7 @@ def check(got, want):
 
 
 @pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p) for p in GOLDEN])
-@pytest.mark.parametrize("how", ["dense", "coo", "device"])
+@pytest.mark.parametrize("how", ["dense", "coo", "device", "bits", "bits_device"])
 def test_golden_vectors(path, how):
     g = np.load(path)
     n, L = int(g["neurons"]), int(g["layers"])
@@ -78,7 +84,8 @@ def test_against_oracle(pattern, n, L, b, oracle):
                                  {"SPDNN_CHUNK_FIRST": "1", "SPDNN_CHUNK_MAX": "3"}, {"SPDNN_CHUNK_FIRST": "64"},
                                  {"SPDNN_STAGE_TABLES": "0"}, {"SPDNN_EXACT_SHORTCUT": "0"}, {"SPDNN_RESIDENT_IPT": "4"},
                                  {"SPDNN_BIT_FORM": "0"}, {"SPDNN_DENSE_DIRECT": "1"}, {"SPDNN_LAZY_EXPAND": "0"},
-                                 {"SPDNN_RESIDENT_TI": "16"}, {"SPDNN_REPS_ONLY": "0"}])
+                                 {"SPDNN_RESIDENT_TI": "16"}, {"SPDNN_REPS_ONLY": "0"}, {"SPDNN_BINARY_FRONT": "0"},
+                                 {"SPDNN_FUSED_FRONT": "0"}, {"SPDNN_RESIDENT": "2"}])
 def test_kernel_paths_agree(env, monkeypatch, oracle):
     """The per-layer kernel, and the shared-memory-resident kernel at every group size and chunk
     schedule, give the same bits as the oracle."""
@@ -89,6 +96,36 @@ def test_kernel_paths_agree(env, monkeypatch, oracle):
         y0 = synthetic_images(n, b) if pattern == "radix16" else mixed_density_images(n, b)
         want = oracle.infer(y0, [(r, None) for r in rows_of(net)], float(net.bias), first_image=7)
         check(run_gpu(net, y0, first=7), want)
+        check(run_gpu(net, y0, first=7, how="bits"), want)
+        check(run_gpu(net, y0, first=7, how="coo"), want)
+
+
+@pytest.mark.parametrize("n,L,b", [(1024, 30, 777), (4096, 20, 300), (16384, 12, 100), (65536, 10, 40)])
+@pytest.mark.parametrize("how", ["dense", "device", "coo", "bits", "bits_device"])
+def test_binary_inputs_in_every_format(n, L, b, how, oracle):
+    """A binary input is kept as one bit per activation whatever format it arrives in, and layer 0 is computed
+    from the bits (by the first chunk while it loads, or by the per-layer kernel); same bits as the oracle."""
+    net = SyntheticNetwork(n, L, "radix16")
+    y0 = synthetic_images(n, b, first_image=31)
+    key = ("binary", n, L, b)
+    if key not in _LARGE_WANT:
+        _LARGE_WANT[key] = oracle.infer(y0, [(r, None) for r in rows_of(net)], float(net.bias), first_image=9)
+    check(run_gpu(net, y0, first=9, how=how, alias=True), _LARGE_WANT[key])
+
+
+@pytest.mark.parametrize("odd_image", [0, 40, 299])
+@pytest.mark.parametrize("how", ["dense", "device", "coo"])
+def test_one_value_that_is_not_binary_switches_the_pass_to_floats(odd_image, how, oracle, monkeypatch):
+    """The input is staged in pieces of 32 images; the one value that is neither 0 nor 1 sits in the first, a
+    middle or the last piece, so pieces converted before it exist as bits only and are rebuilt as floats."""
+    monkeypatch.setenv("SPDNN_STAGE_KB", "128")          # 32 images of 1024 floats per copy
+    n, L, b = 1024, 12, 300
+    net = SyntheticNetwork(n, L, "radix16")
+    y0 = synthetic_images(n, b)
+    on = np.nonzero(y0[odd_image])[0]
+    y0[odd_image, on[: len(on) // 2]] = np.float32(1.75)
+    want = oracle.infer(y0, [(r, None) for r in rows_of(net)], float(net.bias))
+    check(run_gpu(net, y0, how=how), want)
 
 
 def test_dense_input_read_in_place(oracle, monkeypatch):
@@ -132,7 +169,7 @@ _BIT_FORM_WANT = {}
                                  {"SPDNN_BITS_FIRST": "1", "SPDNN_BITS_THREADS": "1024", "SPDNN_CHUNK_FIRST": "40"}])
 @pytest.mark.parametrize("bias,clip,n,L", [(-0.3, 32.0, 1024, 70), (0.0, 32.0, 1024, 70), (-32.0, 32.0, 1024, 70), (0.01, 32.0, 1024, 70),
                                            (-0.3, 8.0, 1024, 70), (-1.0, 2.5, 1024, 70), (-0.35, 32.0, 4096, 50), (0.0, 16.0, 4096, 50)])
-def test_bit_form_of_saturated_activations(bias, clip, n, L, env, monkeypatch, oracle):
+def test_bit_form_of_saturated_activations(bias, clip, n, L, env, monkeypatch, oracle):  # noqa: E302
     """Blocks whose activations are all exactly 0 or clip continue as one word per row and come
     back to floats in the layer where an output is not saturated; the bits are those of the
     float form for every bias and clip.  The batch holds runs of images that are saturated from
@@ -151,9 +188,6 @@ def test_bit_form_of_saturated_activations(bias, clip, n, L, env, monkeypatch, o
     if key not in _BIT_FORM_WANT:
         _BIT_FORM_WANT[key] = oracle.infer(y0, [(r, None) for r in rows_of(net)], bias, clip=clip)
     check(run_gpu(net, y0, clip=clip), _BIT_FORM_WANT[key])
-
-
-_LARGE_WANT = {}
 
 
 def _large_case(oracle, bias, clip, n, L, b):
