@@ -189,11 +189,12 @@ class SyntheticNetwork:
 
 
 def synthetic_images(neurons: int, batch: int, seed: int = 0x1A6E5, first_image: int = 0,
-                     density: float = 0.15, discs: int = 3) -> np.ndarray:
+                     density: float = 0.15, discs: int = 3, threads: int = 1) -> np.ndarray:
     """Binary float32 [batch, N] inputs: per image ``discs`` filled discs of
     random centre and radius on the sqrt(N) x sqrt(N) grid (stroke-like blobs),
     scaled so that about ``density`` of the pixels are 1.0.  Image ``i`` of the
-    result is global image ``first_image + i`` and depends on nothing else."""
+    result is global image ``first_image + i`` and depends on nothing else
+    (``threads`` only spreads the work over host threads)."""
     g = int(round(np.sqrt(neurons)))
     if g * g != neurons:
         raise ValueError("neurons must be a perfect square")
@@ -202,8 +203,9 @@ def synthetic_images(neurons: int, batch: int, seed: int = 0x1A6E5, first_image:
     # typical overlap and border clipping (calibrated factor 1.17)
     r_mean = g * np.sqrt(density * 1.17 / (np.pi * discs))
     yy, xx = np.meshgrid(np.arange(g, dtype=np.float32), np.arange(g, dtype=np.float32), indexing="ij")
-    chunk = max(1, min(batch, (1 << 24) // max(neurons, 1)))
-    for s in range(0, batch, chunk):
+    chunk = max(1, min(batch, (1 << 22) // max(neurons, 1)))
+
+    def fill(s):
         e = min(batch, s + chunk)
         ids = np.arange(first_image + s, first_image + e, dtype=np.uint64)
         on = np.zeros((e - s, g, g), dtype=bool)
@@ -215,6 +217,15 @@ def synthetic_images(neurons: int, batch: int, seed: int = 0x1A6E5, first_image:
             d2 = (xx[None] - cx[:, None, None]) ** 2 + (yy[None] - cy[:, None, None]) ** 2
             on |= d2 <= (rr * rr)[:, None, None]
         out[s:e] = on.reshape(e - s, neurons)
+
+    starts = range(0, batch, chunk)
+    if threads > 1 and len(starts) > 1:
+        from concurrent.futures import ThreadPoolExecutor
+        with ThreadPoolExecutor(threads) as pool:
+            list(pool.map(fill, starts))
+    else:
+        for s in starts:
+            fill(s)
     return out
 
 
