@@ -1,11 +1,12 @@
 """Builds the test oracle.  Nothing built here is part of the shipped library.
 
     python oracle/build.py          # liboracle.so (C restatement) and, when the reference
-                                    # tree is present, _ref/ref_harness
+                                    # tree is present, _ref/ref_harness and _ref/ref_snig
 
 ``_ref/ref_harness`` is the reference's own CPU checkers (src/utils/cpu_spmm.h,
-src/utils/cpu_spmm_fuse.h) compiled from the reference's sources where they lie; only the
-binary lands in ``oracle/_ref/`` (git-ignored).  No reference source is copied.
+src/utils/cpu_spmm_fuse.h), ``_ref/ref_snig`` its structure-agnostic GPU inference loop
+(src/microbenchmark/snig.cu), both compiled from the reference's sources where they lie; only
+the binaries land in ``oracle/_ref/`` (git-ignored).  No reference source is copied.
 """
 from __future__ import annotations
 
@@ -70,7 +71,30 @@ def build_ref(force: bool = False) -> str | None:
     raise RuntimeError("could not build the reference harness:\n" + "\n".join(errors))
 
 
+def build_ref_snig(force: bool = False) -> str | None:
+    """Compile the harness around the reference's structure-agnostic GPU loop (src/microbenchmark/snig.cu) with
+    nvcc, for sm_100a; None when neither the reference nor an earlier build is there."""
+    src = os.path.join(HERE, "ref_snig_harness.cu")
+    out = os.path.join(HERE, "_ref", "ref_snig")
+    if not os.path.isfile(os.path.join(REF, "src", "microbenchmark", "snig.cu")):
+        return out if os.path.exists(out) else None
+    if not force and _newer(out, src):
+        return out
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        return out if os.path.exists(out) else None
+    os.makedirs(os.path.dirname(out), exist_ok=True)
+    ccbin = ["-ccbin", "/usr/bin/g++"] if os.path.exists("/usr/bin/g++") else []
+    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", *ccbin, "-std=c++14", "-O2", "-w", "-I" + os.path.join(REF, "src"),
+           "-o", out, src]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("could not build the SNIG harness:\n" + " ".join(cmd) + "\n" + r.stderr[-800:])
+    return out
+
+
 if __name__ == "__main__":
     force = "--force" in sys.argv
     print(build_oracle(force))
     print(build_ref(force))
+    print(build_ref_snig(force))
