@@ -12,6 +12,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <memory>
 #include <new>
 #include <string>
@@ -43,9 +44,15 @@ struct DevLayer {
     uint64_t h1 = 0, h2 = 0;
     int device = 0;
     std::shared_ptr<HostLayer> host;      // null when the host copy was not kept (resident kernel unavailable)
+    // Streamed layer (the device budget for weights was used up when it was set): the four tables live in ONE
+    // block of page-locked host memory, [off][vals][mem_ptr][mem], and are copied into one of two device slots
+    // while the layer before runs; off/vals/mem_ptr/mem above stay null.
+    unsigned char *pinned = nullptr;
+    size_t pinned_bytes = 0, o_vals = 0, o_mem_ptr = 0, o_mem = 0;
     ~DevLayer() {
         cudaSetDevice(device);
         cudaFree(off); cudaFree(vals); cudaFree(mem_ptr); cudaFree(mem);
+        if (pinned) cudaFreeHost(pinned);
     }
 };
 
@@ -79,6 +86,15 @@ struct spdnn {
     std::vector<std::shared_ptr<DevRes>> res;                        // per layer, built when the graph is
     std::unordered_map<uint64_t, std::weak_ptr<DevRes>> res_shared;  // (layer, input partition) -> tables
     size_t host_bytes = 0, host_budget = (size_t)16 << 30;           // canonical layers kept on the host
+    // Out-of-core weights: per-layer tables beyond weight_budget bytes of device memory stay in page-locked host
+    // memory and are streamed through two device slots by a copy stream, double-buffered against the layer loop
+    // (what the reference's out_memory.cu:315-329, 368-388 does with its second stream).
+    size_t weight_bytes = 0, weight_budget = ~(size_t)0;             // SPDNN_WEIGHT_BUDGET_MB
+    unsigned char *wslot[2] = {nullptr, nullptr};
+    size_t wslot_bytes = 0;
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_ready[2] = {nullptr, nullptr}, ev_free[2] = {nullptr, nullptr};
+    int streamed_launches = 0;         // of the captured schedule
 
     long long tile_stride = 0;
     int tiles_cap = 0;
@@ -602,6 +618,7 @@ enum { kFrontNone = 0, kFrontWords = 1, kFrontFused = 2, kFrontExpand = 3 };
 int enqueue_layers(spdnn *c, const std::vector<Step> &plan, bool gated) {
     c->last_group = 0;
     c->extra_launches = 0;
+    c->streamed_launches = 0;
     int front = kFrontNone;
     if (gated) {
         if (plan[0].ti == 0) {
@@ -708,6 +725,27 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan, bool gated) {
             d.off = L.off; d.vals = L.vals;
             d.mem_ptr = L.identity_members ? nullptr : L.mem_ptr;
             d.mem = L.mem;
+            int wslot = -1;
+            if (L.pinned) {
+                // Streamed layer: its tables travel on the copy stream into the slot that the streamed launch before
+                // the last one has left, while the launches in between run (in the captured graph: the copy depends
+                // on that launch and on the copy before it, this launch on the copy).
+                wslot = c->streamed_launches & 1;
+                if (c->streamed_launches == 0) {
+                    CK(cudaEventRecord(c->ev_fork, c->stream));
+                    CK(cudaStreamWaitEvent(c->copy_stream, c->ev_fork, 0));
+                }
+                if (c->streamed_launches >= 2) CK(cudaStreamWaitEvent(c->copy_stream, c->ev_free[wslot], 0));
+                CK(cudaMemcpyAsync(c->wslot[wslot], L.pinned, L.pinned_bytes, cudaMemcpyHostToDevice, c->copy_stream));
+                CK(cudaEventRecord(c->ev_ready[wslot], c->copy_stream));
+                CK(cudaStreamWaitEvent(c->stream, c->ev_ready[wslot], 0));
+                unsigned char *base = c->wslot[wslot];
+                d.off = reinterpret_cast<const int32_t *>(base);
+                d.vals = L.uniform ? nullptr : reinterpret_cast<const float *>(base + L.o_vals);
+                d.mem_ptr = L.identity_members ? nullptr : reinterpret_cast<const int32_t *>(base + L.o_mem_ptr);
+                d.mem = reinterpret_cast<const int32_t *>(base + L.o_mem);
+                c->streamed_launches += 1;
+            }
             d.classes = L.classes; d.k = L.k; d.w = L.w;
             // Work item = (tile, block of classes).  Without duplicate columns every input row is
             // used by ~K classes: keep a whole tile in one block when it fits the L1 so those
@@ -747,9 +785,11 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan, bool gated) {
             }
             int rc = launch_layer(c, d, a, grid, L.uniform);
             if (rc) return rc;
+            if (wslot >= 0) CK(cudaEventRecord(c->ev_free[wslot], c->stream));
             if (c->print_schedule)
-                fprintf(stderr, "[spdnn] step %zu: per-layer kernel, layer %d  classes %d  k %d  grid %d%s\n", step, l, L.classes, L.k,
-                        grid, a.first_member_only ? "  writes representatives only" : "");
+                fprintf(stderr, "[spdnn] step %zu: per-layer kernel, layer %d  classes %d  k %d  grid %d%s%s\n", step, l, L.classes, L.k,
+                        grid, a.first_member_only ? "  writes representatives only" : "",
+                        wslot >= 0 ? "  tables streamed from host memory" : "");
         }
     }
     c->nsteps = (int)plan.size();
@@ -796,6 +836,20 @@ int build_graph(spdnn *c) {
     c->streams.clear();
     int rc = prepare_resident(c);
     if (rc) return rc;
+    {
+        // device slots of the streamed layers: two, each as large as the largest of them
+        size_t need = 0;
+        for (auto &L : c->layer) need = std::max(need, L->pinned_bytes);
+        if (need > c->wslot_bytes) {
+            CK(cudaStreamSynchronize(c->stream));
+            for (int i = 0; i < 2; ++i) {
+                cudaFree(c->wslot[i]);
+                c->wslot[i] = nullptr;
+                CK(cudaMalloc(&c->wslot[i], need));
+            }
+            c->wslot_bytes = need;
+        }
+    }
     rc = build_graph_kind(c, 0);
     if (rc) return rc;
     if (c->dense_direct && c->resident) {
@@ -851,6 +905,12 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
     c->stream = c->own_stream;
     CK(cudaEventCreate(&c->ev_prep0)); CK(cudaEventCreate(&c->ev_prep1));
     CK(cudaEventCreate(&c->ev_inf0)); CK(cudaEventCreate(&c->ev_inf1));
+    CK(cudaStreamCreateWithFlags(&c->copy_stream, cudaStreamNonBlocking));
+    CK(cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming));
+    for (int i = 0; i < 2; ++i) {
+        CK(cudaEventCreateWithFlags(&c->ev_ready[i], cudaEventDisableTiming));
+        CK(cudaEventCreateWithFlags(&c->ev_free[i], cudaEventDisableTiming));
+    }
     c->layer.resize(layers);
     CK(cudaMalloc(&c->ctl, sizeof(LoopCtl) * (size_t)(layers + 1)));
     CK(cudaMemset(c->ctl, 0, sizeof(LoopCtl) * (size_t)(layers + 1)));
@@ -899,6 +959,7 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
         if (const char *e = getenv("SPDNN_CHUNK_MAX")) c->chunk_max = std::max(1, atoi(e));
         if (const char *e = getenv("SPDNN_CHUNK_GROWTH")) c->chunk_growth = std::max(1, std::min(64, atoi(e)));
         if (const char *e = getenv("SPDNN_HOST_BUDGET_MB")) c->host_budget = (size_t)atoll(e) << 20;
+        if (const char *e = getenv("SPDNN_WEIGHT_BUDGET_MB")) c->weight_budget = (size_t)atoll(e) << 20;
     }
     c->res.resize(layers);
     return SPDNN_OK;
@@ -921,6 +982,13 @@ void spdnn_destroy(spdnn_t *c) {
     if (c->ev_inf0) cudaEventDestroy(c->ev_inf0);
     if (c->ev_inf1) cudaEventDestroy(c->ev_inf1);
     if (c->own_stream) cudaStreamDestroy(c->own_stream);
+    if (c->copy_stream) cudaStreamDestroy(c->copy_stream);
+    if (c->ev_fork) cudaEventDestroy(c->ev_fork);
+    for (int i = 0; i < 2; ++i) {
+        if (c->ev_ready[i]) cudaEventDestroy(c->ev_ready[i]);
+        if (c->ev_free[i]) cudaEventDestroy(c->ev_free[i]);
+        cudaFree(c->wslot[i]);
+    }
     delete c;
 }
 
@@ -971,6 +1039,29 @@ int spdnn_set_layer_csc(spdnn_t *c, int layer, const int32_t *col_ptr, const int
     L->device = c->device;
     L->classes = p.classes; L->k = host->k; L->uniform = host->uniform; L->identity_members = p.identity_members;
     L->w = host->w; L->nnz = host->nnz; L->h1 = host->hash1; L->h2 = host->hash2;
+    const size_t table_bytes = 4 * (std::max<size_t>(p.off.size(), 4) + (host->uniform ? 0 : std::max<size_t>(p.vals.size(), 4)) +
+                                    p.mem_ptr.size() + std::max<size_t>(p.mem.size(), 1));
+    if (c->weight_bytes + table_bytes > c->weight_budget) {
+        // over the device budget: keep the tables in page-locked host memory, streamed in by the layer loop
+        const size_t off_b = (4 * std::max<size_t>(p.off.size(), 4) + 15) / 16 * 16;
+        const size_t val_b = host->uniform ? 0 : (4 * std::max<size_t>(p.vals.size(), 4) + 15) / 16 * 16;
+        const size_t mp_b = (4 * p.mem_ptr.size() + 15) / 16 * 16, mem_b = (4 * std::max<size_t>(p.mem.size(), 1) + 15) / 16 * 16;
+        L->o_vals = off_b; L->o_mem_ptr = off_b + val_b; L->o_mem = L->o_mem_ptr + mp_b;
+        L->pinned_bytes = L->o_mem + mem_b;
+        if (cudaMallocHost(&L->pinned, L->pinned_bytes) != cudaSuccess) {
+            cudaGetLastError();
+            return fail(c, SPDNN_ERR_MEMORY, "out of page-locked host memory for streamed layer %d", layer);
+        }
+        memset(L->pinned, 0, L->pinned_bytes);
+        memcpy(L->pinned, p.off.data(), 4 * p.off.size());
+        if (!host->uniform) memcpy(L->pinned + L->o_vals, p.vals.data(), 4 * p.vals.size());
+        memcpy(L->pinned + L->o_mem_ptr, p.mem_ptr.data(), 4 * p.mem_ptr.size());
+        memcpy(L->pinned + L->o_mem, p.mem.data(), 4 * p.mem.size());
+        c->layer[layer] = L;               // no canonical host copy: a streamed layer runs in the per-layer kernel
+        c->shared[host->hash1] = L;
+        return SPDNN_OK;
+    }
+    c->weight_bytes += table_bytes;
     CK(cudaMalloc(&L->off, sizeof(int32_t) * std::max<size_t>(p.off.size(), 4)));
     CK(cudaMemcpyAsync(L->off, p.off.data(), sizeof(int32_t) * p.off.size(), cudaMemcpyHostToDevice, c->stream));
     if (!host->uniform) {

@@ -259,6 +259,22 @@ def test_layers_without_a_host_copy_mix_with_resident_chunks(oracle, monkeypatch
     check(run_gpu(net, y0), want)
 
 
+@pytest.mark.parametrize("pattern,n,L,b,budget_mb", [("random", 4096, 10, 300, 1), ("random", 1024, 12, 500, 1),
+                                                     ("radix16", 4096, 30, 300, 0), ("radix16", 1024, 40, 700, 0)])
+def test_weights_streamed_from_host_memory(pattern, n, L, b, budget_mb, oracle, monkeypatch):
+    """Layers beyond the device budget for weights keep their tables in page-locked host memory and are
+    copied into two device slots by a second stream while the layer before runs (the reference's
+    out-of-core variant, src/microbenchmark/out_memory.cu:315-329, 368-388).  Budget 1 MB: the first
+    layer(s) stay on the device (and may run in resident chunks), the rest are streamed; budget 0: all are."""
+    monkeypatch.setenv("SPDNN_WEIGHT_BUDGET_MB", str(budget_mb))
+    net = SyntheticNetwork(n, L, pattern)
+    y0 = synthetic_images(n, b) if pattern == "radix16" else mixed_density_images(n, b)
+    want = oracle.infer(y0, [(r, None) for r in rows_of(net)], float(net.bias), first_image=5)
+    check(run_gpu(net, y0, first=5), want)
+    check(run_gpu(net, y0, first=5, how="bits"), want)
+    assert 0 < len(want[0]) < b
+
+
 def test_positive_bias_all_zero_inputs_stay_alive(oracle):
     """With a positive bias even an all-zero input has non-zero activations after layer 0, so
     nothing is ever dropped (every image is in the work list until a layer zeroes it,
@@ -294,7 +310,10 @@ def test_alternating_pairs_with_k16(oracle):
     assert 0 < len(want[0]) < b
 
 
-def test_general_weights_and_ragged_columns(oracle):
+@pytest.mark.parametrize("budget_mb", [None, 0])
+def test_general_weights_and_ragged_columns(oracle, budget_mb, monkeypatch):
+    if budget_mb is not None:
+        monkeypatch.setenv("SPDNN_WEIGHT_BUDGET_MB", str(budget_mb))       # every layer streamed from host memory
     n, b, L = 512, 200, 6
     rng = np.random.default_rng(11)
     y0 = mixed_density_images(n, b)
