@@ -60,6 +60,8 @@ def parse():
     p.add_argument("--no-per-layer-line", action="store_true",
                    help="skip the extra line that times the per-layer kernel alone (SPDNN_RESIDENT=0) against the HBM roofline")
     p.add_argument("--cpu-seconds", type=float, default=10.0, help="target CPU time of each cpu_baseline sample")
+    p.add_argument("--only-value", action="store_true",
+                   help="time the HBM-resident passes only (no end-to-end loops, no extra lines): the short run a profiler capture wraps")
     return p.parse_args()
 
 
@@ -467,6 +469,11 @@ def run_workload(args, cfg, world, rank, local, stream, sampler, headline):
     rb = g.sync()
     res["prep_ms_bits"] = rb.prepare_ms
     assert np.array_equal(np.asarray(g.categories()), cats_dense), "bit-matrix input gave other categories"
+    if args.only_value:
+        res.update({"ms_e2e": res["ms_bits"], "gather_ms": 0.0, "e2e_prep_ms": rb.prepare_ms, "h2d_bits": 0, "d2h": 0,
+                    "all_cats": cats_dense, "net": net, "y_dev": y_dev})
+        g.close()
+        return res
     # -- e2e: host buffers in, category list of the whole job out; copies and the gather inside the timed region
     step_e2e("bits")
     gather_s[0] = 0.0
@@ -606,6 +613,10 @@ def main_ours(args):
                "vs_baseline": None, "dtype": "f32", "data": "synthetic"}
         out.update(head)
         out["clocks"] = clocks
+    if args.only_value:
+        args.no_per_layer_line = args.no_also = args.no_cpu_baseline = True
+        if rank == 0:
+            out["e2e"] = None
     if world == 1 and not args.no_per_layer_line:
         out["roofline_per_layer_kernel"] = per_layer_line(res["net"], res["y_dev"], cfg, local, stream, res["lo"], res["survivors"],
                                                           args.pattern)

@@ -328,12 +328,20 @@ int blocks_per_sm(int k, bool uniform) {
     return uniform ? blocks_per_sm_t<0, true>() : blocks_per_sm_t<0, false>();
 }
 
+// Opts a kernel in to the largest dynamic shared memory the device allows beside the kernel's own static
+// shared memory.  Called at every captured launch (a handful per graph build): the attribute is per device,
+// and a "done" flag shared between contexts would be a data race between host threads.
+template <typename Kernel>
+int allow_max_dynamic_smem(spdnn *c, Kernel kernel) {
+    cudaFuncAttributes fa;
+    CK(cudaFuncGetAttributes(&fa, kernel));
+    CK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, c->smem_optin - (int)fa.sharedSizeBytes));
+    return SPDNN_OK;
+}
+
 template <int TI, int IPT, int KT, bool UNIFORM, bool STAGED>
 int launch_resident_t(spdnn *c, const ResArgs &a, int grid, size_t smem) {
-    // set at every launch that is captured (a handful per graph build): the attribute is per device, and a flag
-    // shared between contexts would be a data race between host threads
-    CK(cudaFuncSetAttribute(resident_kernel<TI, IPT, KT, UNIFORM, STAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                            c->smem_optin - 1024));         // the kernel also has a little static shared memory
+    if (int rc = allow_max_dynamic_smem(c, resident_kernel<TI, IPT, KT, UNIFORM, STAGED>)) return rc;
     resident_kernel<TI, IPT, KT, UNIFORM, STAGED><<<grid, SPDNN_GENERIC_THREADS, smem, c->stream>>>(a);
     CK(cudaGetLastError());
     return SPDNN_OK;
@@ -341,7 +349,7 @@ int launch_resident_t(spdnn *c, const ResArgs &a, int grid, size_t smem) {
 
 template <int TI, int IPT, int KT, bool STAGED, int NT>
 int launch_alt2_t(spdnn *c, const ResArgs &a, int grid, size_t smem) {
-    CK(cudaFuncSetAttribute(alt2_kernel<TI, IPT, KT, STAGED, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, c->smem_optin - 1024));
+    if (int rc = allow_max_dynamic_smem(c, alt2_kernel<TI, IPT, KT, STAGED, NT>)) return rc;
     alt2_kernel<TI, IPT, KT, STAGED, NT><<<grid, NT, smem, c->stream>>>(a);
     CK(cudaGetLastError());
     return SPDNN_OK;
@@ -695,10 +703,10 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan, bool gated) {
                 b.tgroup_shift = st.bits_gshift; b.tring = st.bits_tring;
                 const size_t bsmem = (size_t)st.wwords * 8 + (size_t)st.bits_tring * ((size_t)st.stride << st.bits_gshift);
                 if (st.bits_tring > 0) {
-                    CK(cudaFuncSetAttribute(bits_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, c->smem_optin - 2048));
+                    if (int rc = allow_max_dynamic_smem(c, bits_kernel<true>)) return rc;
                     bits_kernel<true><<<c->tiles_cap, st.bits_threads, bsmem, c->stream>>>(b);
                 } else {
-                    CK(cudaFuncSetAttribute(bits_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, c->smem_optin - 2048));
+                    if (int rc = allow_max_dynamic_smem(c, bits_kernel<false>)) return rc;
                     bits_kernel<false><<<c->tiles_cap, st.bits_threads, bsmem, c->stream>>>(b);
                 }
                 CK(cudaGetLastError());
