@@ -287,8 +287,10 @@ int end_input(spdnn *c) {
 
 int convert_dense_device(spdnn *c, const float *dev_rows, int rows, int first_tile) {
     // rows is a multiple of 32 except for the last chunk
-    const dim3 block(32, 8), grid((rows + 31) / 32, (c->n + kLayoutCols - 1) / kLayoutCols);
+    const dim3 block(32, 8);
     if (rows <= 0) return SPDNN_OK;
+    const long long items = (long long)((rows + 31) / 32) * ((c->n + kLayoutCols - 1) / kLayoutCols);
+    const int grid = (int)std::min<long long>(items, (long long)c->sm_count * 32);
     if (c->binary_front) {
         // words first (this raises the flag when a value is neither 0 nor 1); the float tiles only once the flag is up
         const dim3 wgrid((rows + 31) / 32, (c->n + 1023) / 1024);
@@ -496,6 +498,7 @@ std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
     std::vector<Step> plan;
     int l = 0, chunk = c->chunk_first;
     int alt2_chunks = 0;           // ALT2 chunks planned so far
+    int generic_chunks = 0;        // GENERIC chunks planned so far
     while (l < c->layers) {
         Step st;
         st.first = l;
@@ -589,6 +592,20 @@ std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
                         }
                     }
                 }
+                if (R0.mode == kResGeneric) {
+                    // count_kernel pre-pass for tiles that are saturated already: uniform weight, 32 entries per class
+                    // (its adder tree is built for 32), the two word buffers in shared memory
+                    bool k32_all = k32 && R0.uniform;
+                    for (int q = 0; q < f && k32_all; ++q) k32_all = c->res[l + q]->k == 32 && c->res[l + q]->uniform;
+                    const int words = (rows + 63) / 64 * 64;
+                    if (c->bits_prepass && c->bit_form && c->clip > 0.0f && k32_all && (generic_chunks > 0 || c->bits_first_chunk) &&
+                        (size_t)words * 8 + 2048 <= (size_t)c->smem_optin) {
+                        st.wwords = words;
+                        const int passes = (maxc + 31) / 32;
+                        const int nt = c->bits_threads > 0 ? c->bits_threads : 32 * ((passes + 1) / 2);
+                        st.bits_threads = std::max(128, std::min(kBitsMaxThreads, (nt + 31) / 32 * 32));
+                    }
+                }
                 // A lone layer that reads all N rows of every image but computes few classes from
                 // them (the first layer of a network with repeated columns) gains nothing from
                 // staging the rows in shared memory: gather straight from global memory instead.
@@ -601,7 +618,8 @@ std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
         }
         if (st.ti) chunk = std::min(chunk * c->chunk_growth, c->chunk_max);
         if (st.ti && st.max_classes > 0) ++alt2_chunks;
-        if (!(st.ti && st.max_classes > 0)) st.bits_threads = 0;
+        if (st.ti && st.max_classes == 0) ++generic_chunks;
+        if (!st.ti) st.bits_threads = 0;
         plan.push_back(st);
         l += st.count;
     }
@@ -715,6 +733,21 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan, bool gated) {
                 if (c->print_schedule)
                     fprintf(stderr, "[spdnn] step %zu: pre-pass for saturated tiles, layers %d..%d  %d threads per 32 images  %d words  smem %zu B  tables %s (%d layers per copy, %d in flight)\n",
                             step, l, l + st.count - 1, st.bits_threads, st.wwords, bsmem, st.bits_tring ? "staged" : "global", 1 << st.bits_gshift, st.bits_tring);
+            }
+            if (!alt2 && st.bits_threads > 0) {
+                // pre-pass: saturated tiles of 32 images run the whole chunk as words, a class's output decided by the
+                // count of its clip-valued inputs
+                ResArgs b = a;
+                b.tile_done = c->tile_done; b.wwords = st.wwords;
+                const size_t bsmem = (size_t)st.wwords * 8;
+                if (int rc = allow_max_dynamic_smem(c, count_kernel)) return rc;
+                count_kernel<<<c->tiles_cap, st.bits_threads, bsmem, c->stream>>>(b);
+                CK(cudaGetLastError());
+                c->extra_launches += 1;
+                a.tile_done = c->tile_done;
+                if (c->print_schedule)
+                    fprintf(stderr, "[spdnn] step %zu: pre-pass for saturated tiles (count form), layers %d..%d  %d threads per 32 images  %d words  smem %zu B\n",
+                            step, l, l + st.count - 1, st.bits_threads, st.wwords, bsmem);
             }
             int rc = launch_resident(c, st.ti, st.ipt, a, grid, smem, R0.mode, R0.k == 32, R0.uniform);
             if (rc) return rc;

@@ -204,4 +204,205 @@ __global__ void __launch_bounds__(kBitsMaxThreads, 1) bits_kernel(const ResArgs 
     }
 }
 
+// ---- count_kernel: the same pre-pass for chunks of GENERIC layers (K gathered rows per class) ------------
+//
+// With a uniform weight and inputs that are all 0 or clip, the K-term sum of a class, added in any
+// order, is the sequential sum of c copies of clip, c = the number of its inputs that hold clip (adding
+// 0.0 never changes a sum).  So the output is a function of the COUNT alone, tabulated per layer with
+// the float form's own instructions (sequential adds, one multiply, bias, clamp), and because the
+// weight is positive that function does not decrease: outputs are 0 up to some count, clip from some
+// count on, unsaturated in between.  For 32 images at once the count is a bit-sliced number: a lane owns
+// a class, gathers its K = 32 row words and adds them with a tree of 31 carry-save adders (two 3-input
+// logic instructions each) into six planes, then compares the planes with the two thresholds.  A
+// count in the unsaturated range sends the tile back to the float form, as in bits_kernel.
+//
+// Word buffers are indexed by the PHYSICAL row numbers the GENERIC tables hold (resident_phys_row), the
+// tables are read from global memory (a class's 32 row numbers are 128 contiguous bytes of one lane).
+__device__ __forceinline__ void csa(unsigned int &h, unsigned int &l, unsigned int a, unsigned int b, unsigned int c) {
+    const unsigned int u = a ^ b;
+    h = (a & b) | (u & c);
+    l = u ^ c;
+}
+
+// bit i of the result = (the six-plane number of image i) >= t
+__device__ __forceinline__ unsigned int planes_ge(const unsigned int (&p)[6], int t) {
+    unsigned int gt = 0u, eq = 0xffffffffu;
+#pragma unroll
+    for (int q = 5; q >= 0; --q) {
+        if ((t >> q) & 1) eq &= p[q];
+        else { gt |= eq & p[q]; eq &= ~p[q]; }
+    }
+    return t > 63 ? 0u : (gt | eq);
+}
+
+__global__ void __launch_bounds__(kBitsMaxThreads, 1) count_kernel(const ResArgs a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ unsigned int s_or[3];
+    __shared__ int s_nev, s_ev_layer[32], s_ev_cnt[32];
+    __shared__ float s_tab[64];                  // output of the current layer for every count 0 .. K
+    if (a.gate != nullptr && *a.gate != a.gate_want) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    const LoopCtl ctl = *a.ctl_in;
+    const int live_in = ctl.live;
+    const int tile = blockIdx.x;
+    if (tile >= ((live_in + 31) >> 5)) return;
+    unsigned int *wc = reinterpret_cast<unsigned int *>(smem), *wn = wc + a.wwords;
+
+    // ---- the tile's input: one word per value id, read through the work list
+    const int j = tile * 32 + lane;
+    const bool valid = j < live_in;
+    const int jj = valid ? j : tile * 32;
+    const int src = ctl.identity ? jj : __ldg(a.slot + jj);
+    if (!ctl.identity && warp == 0 && valid) move_id(ctl, a.ids0, a.ids1, j, src);
+    const float *__restrict__ p = a.yin + (size_t)(src >> 5) * a.tile_stride + (src & 31);
+    const ResLayer L0 = a.layers[0];
+    bool ns_in = false;
+    for (int v0 = warp * 8; v0 < L0.v_in; v0 += nwarps * 8) {
+        int e[8];
+        float x[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const int v = min(v0 + q, L0.v_in - 1);
+            e[q] = L0.rep ? __ldg(L0.rep + v) : v * 32;
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) x[q] = valid ? __ldg(p + e[q]) : 0.0f;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const unsigned int w = __ballot_sync(0xffffffffu, x[q] != 0.0f);
+            ns_in |= (x[q] != 0.0f && x[q] != a.clip);
+            if (lane == 0 && v0 + q < L0.v_in) wc[resident_phys_row(v0 + q)] = w;
+        }
+    }
+    // every word past the value ids is zero in both buffers: padded table entries point at the first even row behind them
+    for (int r = L0.v_in + tid; r < a.wwords; r += blockDim.x) wc[(r < ((L0.v_in + 1) & ~1)) ? resident_phys_row(r) : r] = 0u;
+    for (int r = tid; r < a.wwords; r += blockDim.x) wn[r] = 0u;
+    if (tid == 0) {
+        s_or[0] = 0u;
+        s_nev = 0;
+    }
+    if (__syncthreads_or(ns_in ? 1 : 0)) {
+        if (tid == 0) a.tile_done[tile] = 0;
+        return;
+    }
+
+    unsigned int alive = __ballot_sync(0xffffffffu, valid);
+    const bool force_dead = a.bias > 0.0f;
+    unsigned int ns = 0u;
+    int li = 0, last_classes = 0;
+    bool unsat = false;
+    int tab_k = -1, sat_lo = 0, zero_hi = 0;
+    float tab_w = 0.0f;
+    while (li < a.nlayers) {
+        const ResLayer RL = a.layers[li];
+        const int classes = RL.classes, k = RL.k;
+        if (k != tab_k || RL.w != tab_w) {
+            // the layer's output for every count of clip-valued inputs, by the float form's instructions
+            __syncthreads();
+            if (tid <= k && tid < 64) {
+                float sum = 0.0f;
+                for (int q = 0; q < tid; ++q) sum = __fadd_rn(sum, a.clip);
+                s_tab[tid] = finish_output(__fmul_rn(sum, RL.w), a.bias, a.clip);
+            }
+            __syncthreads();
+            int zeros = 0, sats = 0;
+            bool shaped = true;
+            for (int q = 0; q <= k; ++q) {
+                const float f = s_tab[q];
+                if (f == 0.0f) { ++zeros; shaped &= (q == zeros - 1); }          // zeros first
+                if (f == a.clip) ++sats;
+                else shaped &= (sats == 0);                                       // clip last
+            }
+            zero_hi = zeros - 1;
+            sat_lo = k + 1 - sats;
+            tab_k = k; tab_w = RL.w;
+            if (!shaped) { unsat = true; break; }         // not a step function of the count: leave it to the float form
+        }
+        const unsigned int keep = force_dead ? alive : 0xffffffffu;
+        const int passes = (classes + 31) >> 5;
+        const int kp = k + 4;
+        const int32_t *__restrict__ tb = RL.blob + 4;
+        unsigned int o = 0u;
+        for (int ps = warp; ps < passes; ps += nwarps) {
+            const int u = ps * 32 + lane;
+            const bool in = u < classes;
+            const int4 *rows = reinterpret_cast<const int4 *>(tb + (size_t)(in ? u : 0) * kp);
+            unsigned int pl[6] = {0u, 0u, 0u, 0u, 0u, 0u};       // ones, twos, fours, eights, sixteens, thirty-twos
+            unsigned int s16[2];
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                unsigned int e8[2];
+#pragma unroll
+                for (int quarter = 0; quarter < 2; ++quarter) {
+                    const int4 r0 = __ldg(rows + half * 4 + quarter * 2), r1 = __ldg(rows + half * 4 + quarter * 2 + 1);
+                    const unsigned int w0 = wc[r0.x], w1 = wc[r0.y], w2 = wc[r0.z], w3 = wc[r0.w];
+                    const unsigned int w4 = wc[r1.x], w5 = wc[r1.y], w6 = wc[r1.z], w7 = wc[r1.w];
+                    unsigned int t2a, t2b, f4a, f4b;
+                    csa(t2a, pl[0], pl[0], w0, w1);
+                    csa(t2b, pl[0], pl[0], w2, w3);
+                    csa(f4a, pl[1], pl[1], t2a, t2b);
+                    csa(t2a, pl[0], pl[0], w4, w5);
+                    csa(t2b, pl[0], pl[0], w6, w7);
+                    csa(f4b, pl[1], pl[1], t2a, t2b);
+                    csa(e8[quarter], pl[2], pl[2], f4a, f4b);
+                }
+                csa(s16[half], pl[3], pl[3], e8[0], e8[1]);
+            }
+            csa(pl[5], pl[4], pl[4], s16[0], s16[1]);
+            const unsigned int x = planes_ge(pl, sat_lo) & keep;
+            const unsigned int nz = planes_ge(pl, zero_hi + 1) & keep;
+            if (in) {
+                ns |= nz & ~x;
+                wn[resident_phys_row(u)] = x;
+                o |= x;
+            }
+        }
+        {
+            // zero rows of the buffer just written (the next layer's padded entries point there; the buffer may
+            // hold outputs of a wider layer from two layers ago)
+            const int ue = (classes + 1) & ~1;
+            for (int r = classes + tid; r < ue + 2; r += blockDim.x) wn[r < ue ? resident_phys_row(r) : r] = 0u;
+        }
+        o = __reduce_or_sync(0xffffffffu, o);
+        if (lane == 0 && o) atomicOr(&s_or[li % 3], o);
+        if (tid == 0) s_or[(li + 1) % 3] = 0u;
+        __syncthreads();
+        const unsigned int now = s_or[li % 3] & alive;
+        if (now != alive && tid == 0) {
+            s_ev_layer[s_nev] = li;
+            s_ev_cnt[s_nev] = __popc(alive & ~now);
+            ++s_nev;
+        }
+        alive = now;
+        unsigned int *t = wc; wc = wn; wn = t;
+        last_classes = classes;
+        ++li;
+        if ((li % kBitsCheckEvery) == 0 || li == a.nlayers || alive == 0u) {
+            if (__syncthreads_or(ns != 0u ? 1 : 0)) { unsat = true; break; }
+        }
+        if (alive == 0u) break;
+    }
+    if (unsat) {
+        if (tid == 0) a.tile_done[tile] = 0;
+        return;
+    }
+    if (tid == 0) {
+        a.tile_done[tile] = 1;
+        for (int q = 0; q < s_nev; ++q) atomicAdd(a.died_at + s_ev_layer[q], s_ev_cnt[q]);
+        if (alive) atomicOr(a.mask + tile, alive);
+    }
+    if (alive == 0u) return;
+    const ResLayer LL = a.layers[li - 1];
+    float *out = a.yout + (size_t)tile * a.tile_stride + lane;
+    for (int u = warp; u < last_classes; u += nwarps) {
+        const float y = ((wc[resident_phys_row(u)] >> lane) & 1u) ? a.clip : 0.0f;
+        if (LL.mem_ptr == nullptr) {
+            out[(size_t)u * 32] = y;
+        } else {
+            const int mb = __ldg(LL.mem_ptr + u), me = a.reps_only ? mb + 1 : __ldg(LL.mem_ptr + u + 1);
+            for (int m = mb; m < me; ++m) out[__ldg(LL.mem + m)] = y;
+        }
+    }
+}
+
 }  // namespace spdnn_impl

@@ -331,39 +331,45 @@ __global__ void __launch_bounds__(kThreads, SPDNN_MIN_BLOCKS) layer_kernel(const
 
 // ---- layout conversion and bookkeeping kernels -------------------------------------------
 
-// Row-major [batch][N] -> tiles.  Block (32, 8), grid (ceil(batch/32), ceil(N/kLayoutCols)): a block
-// moves 32 images x kLayoutCols neurons, 512 contiguous bytes of every image's row, so that the reads
-// stay within few DRAM pages; all of a thread's 16 loads are in flight before the first store.
-constexpr int kLayoutCols = 128;
+// Row-major [batch][N] -> tiles.  Block (32, 8); a work item is 32 images x kLayoutCols neurons, 512 contiguous
+// bytes of every image's row, so that the reads stay within few DRAM pages; all of a thread's 16 loads are in
+// flight before the first store.  Blocks walk the items (tile-major) with a grid stride, so a launch that its
+// gate switches off costs a few thousand blocks' worth of nothing, not one block per item.
 // With a gate the kernel runs only once *gate is non-zero (the input is known not to be binary, see
 // spdnn_front.cuh) and marks the tiles it wrote in has_floats.
+constexpr int kLayoutCols = 128;
 static __global__ void dense_to_tiles_kernel(const float *__restrict__ in, float *__restrict__ out, int n, int batch,
                                       long long tile_stride, int first_tile, const int32_t *gate, unsigned char *has_floats) {
     __shared__ float t[32][kLayoutCols + 1];
     if (gate != nullptr && *gate == 0) return;
-    const int c0 = blockIdx.y * kLayoutCols, tile = blockIdx.x;
-    if (gate != nullptr && blockIdx.y == 0 && threadIdx.x == 0 && threadIdx.y == 0) has_floats[first_tile + tile] = 1;
-    const int img0 = tile * 32;
-    float v[4][kLayoutCols / 32];
+    const int ncb = (n + kLayoutCols - 1) / kLayoutCols;
+    const long long items = (long long)((batch + 31) / 32) * ncb;
+    for (long long item = blockIdx.x; item < items; item += gridDim.x) {
+        const int tile = (int)(item / ncb), c0 = (int)(item - (long long)tile * ncb) * kLayoutCols;
+        if (gate != nullptr && c0 == 0 && threadIdx.x == 0 && threadIdx.y == 0) has_floats[first_tile + tile] = 1;
+        const int img0 = tile * 32;
+        float v[4][kLayoutCols / 32];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        const int img = img0 + threadIdx.y + 8 * q;
+        for (int q = 0; q < 4; ++q) {
+            const int img = img0 + threadIdx.y + 8 * q;
 #pragma unroll
-        for (int k = 0; k < kLayoutCols / 32; ++k) {
-            const int c = c0 + 32 * k + threadIdx.x;
-            v[q][k] = (img < batch && c < n) ? __ldg(in + (size_t)img * n + c) : 0.0f;
+            for (int k = 0; k < kLayoutCols / 32; ++k) {
+                const int c = c0 + 32 * k + threadIdx.x;
+                v[q][k] = (img < batch && c < n) ? __ldg(in + (size_t)img * n + c) : 0.0f;
+            }
         }
-    }
 #pragma unroll
-    for (int q = 0; q < 4; ++q)
+        for (int q = 0; q < 4; ++q)
 #pragma unroll
-        for (int k = 0; k < kLayoutCols / 32; ++k) t[threadIdx.y + 8 * q][32 * k + threadIdx.x] = v[q][k];
-    __syncthreads();
-    float *o = out + (size_t)(first_tile + tile) * tile_stride;
+            for (int k = 0; k < kLayoutCols / 32; ++k) t[threadIdx.y + 8 * q][32 * k + threadIdx.x] = v[q][k];
+        __syncthreads();
+        float *o = out + (size_t)(first_tile + tile) * tile_stride;
 #pragma unroll
-    for (int r = threadIdx.y; r < kLayoutCols; r += 8) {
-        const int c = c0 + r;
-        if (c < n) o[(size_t)c * 32 + threadIdx.x] = t[threadIdx.x][r];
+        for (int r = threadIdx.y; r < kLayoutCols; r += 8) {
+            const int c = c0 + r;
+            if (c < n) o[(size_t)c * 32 + threadIdx.x] = t[threadIdx.x][r];
+        }
+        __syncthreads();
     }
 }
 

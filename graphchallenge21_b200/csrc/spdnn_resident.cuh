@@ -362,7 +362,9 @@ resident_kernel(const ResArgs a) {
     const int nblk = (live_in + TI - 1) / TI;
     const int buf_bytes = a.buf_rows * RS;
 
-    if ((int)blockIdx.x < nblk) {
+    // a tile that the count_kernel pre-pass finished is skipped (TI divides 32: a block lies inside one tile)
+    const bool tile_finished = a.tile_done != nullptr && (int)blockIdx.x < nblk && a.tile_done[(blockIdx.x * TI) >> 5] != 0;
+    if ((int)blockIdx.x < nblk && !tile_finished) {
         unsigned char *cur = smem, *nxt = smem + buf_bytes;
         unsigned char *const tbl0 = smem + 2 * buf_bytes;      // table buffer q sits at tbl0 + q * table_bytes
         const int j0 = blockIdx.x * TI;

@@ -275,6 +275,28 @@ def test_weights_streamed_from_host_memory(pattern, n, L, b, budget_mb, oracle, 
     assert 0 < len(want[0]) < b
 
 
+@pytest.mark.parametrize("env", [{}, {"SPDNN_BITS_FIRST": "1"}, {"SPDNN_BITS_FIRST": "1", "SPDNN_BITS_THREADS": "128"},
+                                 {"SPDNN_BITS_FIRST": "1", "SPDNN_CHUNK_FIRST": "2", "SPDNN_CHUNK_GROWTH": "2"}, {"SPDNN_BITS_KERNEL": "0"}],
+                         ids=lambda e: ",".join(f"{k[6:]}={v}" for k, v in e.items()) or "default")
+@pytest.mark.parametrize("n,L,b,bias,clip", [(1024, 48, 600, -0.3, 32.0), (4096, 24, 200, -0.35, 32.0), (1024, 30, 300, 0.01, 8.0),
+                                             (1024, 30, 300, -3.0, 2.5)])
+def test_count_form_on_networks_without_structure(n, L, b, bias, clip, env, monkeypatch, oracle):
+    """Pattern 'random' has no repeated columns, so every class gathers 32 rows; tiles whose activations are all 0
+    or clip run a chunk as words with each output decided by the count of clip-valued inputs.  The batch mixes
+    densities (some images saturate, some die, some stay in between for a while) with images that are
+    saturated from the start and values off the grid."""
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    net = SyntheticNetwork(n, L, "random", bias=bias)
+    y0 = mixed_density_images(n, b)
+    y0[32:96] = (mixed_density_images(n, 64, seed=77, lo=0.5, hi=0.95) * np.float32(clip))
+    y0[96:104:3] *= np.float32(0.37 * clip)
+    key = ("count", n, L, b, bias, clip)
+    if key not in _LARGE_WANT:
+        _LARGE_WANT[key] = oracle.infer(y0, [(r, None) for r in rows_of(net)], bias, clip=clip, first_image=2)
+    check(run_gpu(net, y0, first=2, clip=clip), _LARGE_WANT[key])
+
+
 def test_positive_bias_all_zero_inputs_stay_alive(oracle):
     """With a positive bias even an all-zero input has non-zero activations after layer 0, so
     nothing is ever dropped (every image is in the work list until a layer zeroes it,
