@@ -131,6 +131,7 @@ struct spdnn {
     int32_t *in_flag = nullptr;
     unsigned char *has_floats = nullptr;
     bool binary_front = true;          // SPDNN_BINARY_FRONT=0: inputs are always converted to float tiles
+    bool count_front = true;           // SPDNN_COUNT_FRONT=0: layer 0 of a binary input always gathers per image
     bool fused_front = true;           // SPDNN_FUSED_FRONT=0: layer 0 of a binary input runs in the per-layer kernel
                                        // even where the first ALT2 chunk could compute it while loading
     bool bits_prepass = true;          // SPDNN_BITS_KERNEL=0: ALT2 chunks of wide layers run without the pre-pass
@@ -817,10 +818,22 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan, bool gated) {
                 if (front == kFrontWords) {
                     LayerArgs w = a;           // binary inputs: gather from the words
                     w.xw = c->xw; w.nw = c->nw; w.gate = c->in_flag; w.gate_want = 0;
-                    int rc = launch_layer(c, d, w, grid, L.uniform);
-                    if (rc) return rc;
+                    const bool by_count = L.uniform && L.k == 32 && c->count_front;
+                    if (by_count) {
+                        // uniform weight, 32 entries per class: bit-sliced counts of 32 images at once
+                        int bps = 0;
+                        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&bps, front_count_kernel, kThreads, 0) != cudaSuccess || bps < 1) bps = 1;
+                        const long long fitems = (long long)c->tiles_cap * ((L.classes + kFrontClassesPerItem - 1) / kFrontClassesPerItem);
+                        if (fitems >= 0xffffffffLL) return fail(c, SPDNN_ERR_LIMIT, "batch too large for one launch");
+                        front_count_kernel<<<c->sm_count * bps, kThreads, 0, c->stream>>>(d, w);
+                        CK(cudaGetLastError());
+                    } else {
+                        int rc = launch_layer(c, d, w, grid, L.uniform);
+                        if (rc) return rc;
+                    }
                     c->extra_launches += 1;
-                    if (c->print_schedule) fprintf(stderr, "[spdnn] step 0, binary inputs: per-layer kernel on the input words\n");
+                    if (c->print_schedule)
+                        fprintf(stderr, "[spdnn] step 0, binary inputs: %s on the input words\n", by_count ? "counting kernel" : "per-layer kernel");
                 }
                 a.gate = c->in_flag; a.gate_want = 1;
             }
@@ -986,6 +999,7 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
         if (const char *e = getenv("SPDNN_STAGE_KB")) c->stage_chunk = (size_t)std::max(1, atoi(e)) << 10;
         if (const char *e = getenv("SPDNN_BINARY_FRONT")) c->binary_front = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_FUSED_FRONT")) c->fused_front = atoi(e) != 0;
+        if (const char *e = getenv("SPDNN_COUNT_FRONT")) c->count_front = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BITS_KERNEL")) c->bits_prepass = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BITS_FIRST")) c->bits_first_chunk = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BITS_THREADS")) c->bits_threads = std::max(0, std::min(kBitsMaxThreads, atoi(e)));

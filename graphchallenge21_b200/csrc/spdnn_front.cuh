@@ -135,4 +135,116 @@ static __global__ void mark_tiles_kernel(unsigned char *has_floats, int first_ti
     for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < tiles; t += gridDim.x * blockDim.x) has_floats[first_tile + t] = 1;
 }
 
+// ---- layer 0 of a binary input, 32 images at a time -----------------------------------------------------
+//
+// For a layer with a uniform weight and 32 entries per class the sum of a class over a binary input is
+// count * w with count = the number of its inputs that are set, every partial sum an integer and so exact in
+// fp32 whatever the order.  A lane owns a CLASS: it gathers the class's 32 row words of the tile (bit i =
+// image i) and adds them with a tree of 31 carry-save adders into a six-plane bit-sliced count of all 32
+// images at once -- about a third of the instructions of the per-image gather-and-add.  The planes are then
+// handed round the warp, class by class, and lane i turns image i's count into the float output with the
+// per-layer kernel's own instructions (multiply by w, add the bias, clamp) and stores a coalesced row.
+// Same launch protocol as layer_kernel: work items from an atomic counter, ballots, last-block rebuild.
+__device__ __forceinline__ void front_csa(unsigned int &h, unsigned int &l, unsigned int a, unsigned int b, unsigned int c) {
+    const unsigned int u = a ^ b;
+    h = (a & b) | (u & c);
+    l = u ^ c;
+}
+
+constexpr int kFrontClassesPerItem = 256;
+
+static __global__ void __launch_bounds__(kThreads, 4) front_count_kernel(const LayerDesc d, const LayerArgs a) {
+    __shared__ unsigned int s_mask;
+    __shared__ unsigned int s_item;
+    __shared__ int s_last;
+    if (a.gate != nullptr && *a.gate != a.gate_want) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const LoopCtl ctl = *a.ctl_in;                 // first launch of a pass: image j sits at position j
+    const int live_in = ctl.live;
+    const int ntiles = (live_in + 31) >> 5;
+    const int ncb = (d.classes + kFrontClassesPerItem - 1) / kFrontClassesPerItem;
+    const unsigned int items = (unsigned int)ntiles * (unsigned int)ncb;
+    for (;;) {
+        if (tid == 0) {
+            s_item = atomicAdd(a.work, 1u);
+            s_mask = 0u;
+        }
+        __syncthreads();
+        const unsigned int item = s_item;
+        if (item >= items) break;
+        const int tile = (int)(item / (unsigned int)ncb);
+        const int cb = (int)(item - (unsigned int)tile * (unsigned int)ncb);
+        const uint32_t *__restrict__ xw = a.xw + (size_t)tile * a.nw;
+        float *__restrict__ yout = a.yout + (size_t)tile * a.tile_stride + lane;
+        const bool valid = tile * 32 + lane < live_in;
+        bool any = false;
+        const int u_end = min(d.classes, (cb + 1) * kFrontClassesPerItem);
+        for (int u0 = cb * kFrontClassesPerItem + warp * 32; u0 < u_end; u0 += kWarps * 32) {
+            const int u = u0 + lane;
+            const bool in = u < u_end;
+            const int4 *o4 = reinterpret_cast<const int4 *>(d.off + (size_t)(in ? u : u0) * 32);
+            unsigned int pl[6] = {0u, 0u, 0u, 0u, 0u, 0u};       // ones, twos, fours, eights, sixteens, thirty-twos
+            unsigned int s16[2];
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                unsigned int e8[2];
+#pragma unroll
+                for (int quarter = 0; quarter < 2; ++quarter) {
+                    const int4 r0 = __ldg(o4 + half * 4 + quarter * 2), r1 = __ldg(o4 + half * 4 + quarter * 2 + 1);
+                    const unsigned int w0 = __ldg(xw + (r0.x >> 5)), w1 = __ldg(xw + (r0.y >> 5)), w2 = __ldg(xw + (r0.z >> 5)),
+                                       w3 = __ldg(xw + (r0.w >> 5)), w4 = __ldg(xw + (r1.x >> 5)), w5 = __ldg(xw + (r1.y >> 5)),
+                                       w6 = __ldg(xw + (r1.z >> 5)), w7 = __ldg(xw + (r1.w >> 5));
+                    unsigned int t2a, t2b, f4a, f4b;
+                    front_csa(t2a, pl[0], pl[0], w0, w1);
+                    front_csa(t2b, pl[0], pl[0], w2, w3);
+                    front_csa(f4a, pl[1], pl[1], t2a, t2b);
+                    front_csa(t2a, pl[0], pl[0], w4, w5);
+                    front_csa(t2b, pl[0], pl[0], w6, w7);
+                    front_csa(f4b, pl[1], pl[1], t2a, t2b);
+                    front_csa(e8[quarter], pl[2], pl[2], f4a, f4b);
+                }
+                front_csa(s16[half], pl[3], pl[3], e8[0], e8[1]);
+            }
+            front_csa(pl[5], pl[4], pl[4], s16[0], s16[1]);
+            // where the class's output goes: its first member's row, or all of them
+            int mb = u, me = u + 1, mrow = u * 32;
+            if (d.mem_ptr != nullptr && in) {
+                mb = __ldg(d.mem_ptr + u);
+                me = __ldg(d.mem_ptr + u + 1);
+                mrow = __ldg(d.mem + mb);
+            }
+            const int n_here = min(32, u_end - u0);
+            for (int cidx = 0; cidx < n_here; ++cidx) {
+                unsigned int cnt = (__shfl_sync(0xffffffffu, pl[0], cidx) >> lane) & 1u;
+                cnt |= ((__shfl_sync(0xffffffffu, pl[1], cidx) >> lane) & 1u) << 1;
+                cnt |= ((__shfl_sync(0xffffffffu, pl[2], cidx) >> lane) & 1u) << 2;
+                cnt |= ((__shfl_sync(0xffffffffu, pl[3], cidx) >> lane) & 1u) << 3;
+                cnt |= ((__shfl_sync(0xffffffffu, pl[4], cidx) >> lane) & 1u) << 4;
+                cnt |= ((__shfl_sync(0xffffffffu, pl[5], cidx) >> lane) & 1u) << 5;
+                const float y = relu_clip(__fadd_rn(__fmul_rn((float)cnt, d.w), a.bias), a.clip);
+                any |= (y != 0.0f);
+                const int row = __shfl_sync(0xffffffffu, mrow, cidx);
+                yout[row] = y;
+                if (!a.first_member_only && d.mem_ptr != nullptr) {
+                    const int b0 = __shfl_sync(0xffffffffu, mb, cidx), b1 = __shfl_sync(0xffffffffu, me, cidx);
+                    for (int m = b0 + 1; m < b1; ++m) yout[__ldg(d.mem + m)] = y;
+                }
+            }
+        }
+        const unsigned int m = __ballot_sync(0xffffffffu, any && valid);
+        if (lane == 0 && m) atomicOr(&s_mask, m);
+        __syncthreads();
+        if (tid == 0 && s_mask) atomicOr(a.mask + tile, s_mask);
+    }
+    if (tid == 0) {
+        __threadfence();
+        const unsigned int t = atomicAdd(a.counter, 1u);
+        s_last = (t == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    rebuild_worklist(a, live_in, ctl.ids_buf);
+}
+
 }  // namespace spdnn_impl
