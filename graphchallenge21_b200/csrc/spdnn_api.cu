@@ -136,6 +136,7 @@ struct spdnn {
                                        // even where the first ALT2 chunk could compute it while loading
     bool bits_prepass = true;          // SPDNN_BITS_KERNEL=0: ALT2 chunks of wide layers run without the pre-pass
     bool bits_first_chunk = false;     // SPDNN_BITS_FIRST=1: also before the first resident chunk of a pass
+    bool table_cache = true;           // SPDNN_TABLE_CACHE=0: the pre-pass always streams its layer records
     int bits_threads = 0;              // SPDNN_BITS_THREADS: threads per block of the pre-pass (0: by the classes)
     int extra_launches = 0;            // pre-pass launches of the captured schedule
     int graph_extra[2] = {0, 0};
@@ -489,6 +490,10 @@ struct Step {
     bool dense = false;            // resident chunk that reads the caller's row-major input in place
     // bits_kernel pre-pass of an ALT2 chunk (0 threads: none): its own staging of the packed stream
     int bits_threads = 0, bits_gshift = 0, bits_tring = 0, wwords = 0;
+    // ... with the chunk's distinct records cached in shared memory (cache_records > 0)
+    unsigned char *cache = nullptr;
+    unsigned short *rec_of = nullptr;
+    int cache_records = 0;
 };
 
 // The launches of one pass, front to back.
@@ -700,6 +705,7 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan, bool gated) {
                                      : resident_smem_bytes(st.ti, st.rows, st.table);
             a.bit_ok = (alt2 && c->bit_form && c->clip > 0.0f && st.wring >= 2) ? 1 : 0;
             a.tile_done = nullptr; a.wwords = 0;
+            a.cache = nullptr; a.rec_of = nullptr; a.cache_records = 0;
             a.front_words = nullptr; a.front_nw = 0; a.front_layer = nullptr; a.front_died_at = nullptr; a.front_ctl_copy = nullptr;
             a.gate = nullptr; a.gate_want = 0;
             if (front == kFrontFused && step == 1) {
@@ -720,20 +726,26 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan, bool gated) {
                 ResArgs b = a;                 // (gated like the launch it prepares)
                 b.tile_done = c->tile_done; b.wwords = st.wwords;
                 b.tgroup_shift = st.bits_gshift; b.tring = st.bits_tring;
-                const size_t bsmem = (size_t)st.wwords * 8 + (size_t)st.bits_tring * ((size_t)st.stride << st.bits_gshift);
-                if (st.bits_tring > 0) {
-                    if (int rc = allow_max_dynamic_smem(c, bits_kernel<true>)) return rc;
-                    bits_kernel<true><<<c->tiles_cap, st.bits_threads, bsmem, c->stream>>>(b);
+                b.cache = st.cache; b.rec_of = st.rec_of; b.cache_records = st.cache_records;
+                size_t bsmem = (size_t)st.wwords * 8 + (size_t)st.bits_tring * ((size_t)st.stride << st.bits_gshift);
+                if (st.cache_records > 0) {
+                    bsmem = (size_t)st.wwords * 8 + (size_t)st.cache_records * st.stride + ((size_t)st.count * 2 + 15) / 16 * 16;
+                    if (int rc = allow_max_dynamic_smem(c, bits_kernel<kBitsCached>)) return rc;
+                    bits_kernel<kBitsCached><<<c->tiles_cap, st.bits_threads, bsmem, c->stream>>>(b);
+                } else if (st.bits_tring > 0) {
+                    if (int rc = allow_max_dynamic_smem(c, bits_kernel<kBitsRing>)) return rc;
+                    bits_kernel<kBitsRing><<<c->tiles_cap, st.bits_threads, bsmem, c->stream>>>(b);
                 } else {
-                    if (int rc = allow_max_dynamic_smem(c, bits_kernel<false>)) return rc;
-                    bits_kernel<false><<<c->tiles_cap, st.bits_threads, bsmem, c->stream>>>(b);
+                    if (int rc = allow_max_dynamic_smem(c, bits_kernel<kBitsGlobal>)) return rc;
+                    bits_kernel<kBitsGlobal><<<c->tiles_cap, st.bits_threads, bsmem, c->stream>>>(b);
                 }
                 CK(cudaGetLastError());
                 c->extra_launches += 1;
                 a.tile_done = c->tile_done;
                 if (c->print_schedule)
-                    fprintf(stderr, "[spdnn] step %zu: pre-pass for saturated tiles, layers %d..%d  %d threads per 32 images  %d words  smem %zu B  tables %s (%d layers per copy, %d in flight)\n",
-                            step, l, l + st.count - 1, st.bits_threads, st.wwords, bsmem, st.bits_tring ? "staged" : "global", 1 << st.bits_gshift, st.bits_tring);
+                    fprintf(stderr, "[spdnn] step %zu: pre-pass for saturated tiles, layers %d..%d  %d threads per 32 images  %d words  smem %zu B  tables %s (%d layers per copy, %d in flight; %d distinct records cached)\n",
+                            step, l, l + st.count - 1, st.bits_threads, st.wwords, bsmem, st.cache_records ? "cached" : st.bits_tring ? "staged" : "global",
+                            1 << st.bits_gshift, st.bits_tring, st.cache_records);
             }
             if (!alt2 && st.bits_threads > 0) {
                 // pre-pass: saturated tiles of 32 images run the whole chunk as words, a class's output decided by the
@@ -865,6 +877,39 @@ int build_graph_kind(spdnn *c, int kind) {
         c->streams.push_back(st.stream);
         alt2_pack_kernel<<<st.count, 256, 0, c->stream>>>(c->res_table + st.first, st.stride, st.stream, c->bias, c->clip);
         CK(cudaGetLastError());
+        if (st.bits_threads > 0 && c->table_cache && c->stage_tables) {
+            // Layers with the same tables (same matrix, same value ids going in) share one record.  When the chunk's
+            // distinct records fit beside the word buffers, the pre-pass keeps them all in shared memory.
+            std::unordered_map<const DevRes *, int> seen;
+            std::vector<unsigned short> rec_of(st.count);
+            std::vector<int> first_layer;
+            for (int q = 0; q < st.count; ++q) {
+                const DevRes *r = c->res[st.first + q].get();
+                auto it = seen.find(r);
+                if (it == seen.end()) {
+                    it = seen.emplace(r, (int)first_layer.size()).first;
+                    first_layer.push_back(q);
+                }
+                rec_of[q] = (unsigned short)std::min(it->second, 65535);
+            }
+            const size_t d = first_layer.size();
+            const size_t rec_bytes = ((size_t)st.count * 2 + 15) / 16 * 16;
+            if (d <= 65535 && d * st.stride < ((size_t)1 << 20) &&
+                (size_t)st.wwords * 8 + d * st.stride + rec_bytes + 2048 <= (size_t)c->smem_optin) {
+                CK(cudaMalloc(&st.cache, d * st.stride));
+                c->streams.push_back(st.cache);
+                unsigned char *rec_dev = nullptr;
+                CK(cudaMalloc(&rec_dev, rec_bytes));
+                c->streams.push_back(rec_dev);
+                st.rec_of = reinterpret_cast<unsigned short *>(rec_dev);
+                for (size_t q = 0; q < d; ++q)
+                    CK(cudaMemcpyAsync(st.cache + q * st.stride, st.stream + (size_t)first_layer[q] * st.stride, st.stride,
+                                       cudaMemcpyDeviceToDevice, c->stream));
+                CK(cudaMemcpyAsync(rec_dev, rec_of.data(), (size_t)st.count * 2, cudaMemcpyHostToDevice, c->stream));
+                CK(cudaStreamSynchronize(c->stream));          // rec_of is a local
+                st.cache_records = (int)d;
+            }
+        }
     }
     CK(cudaStreamSynchronize(c->stream));
     cudaGraph_t g = nullptr;
@@ -1002,6 +1047,7 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
         if (const char *e = getenv("SPDNN_COUNT_FRONT")) c->count_front = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BITS_KERNEL")) c->bits_prepass = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BITS_FIRST")) c->bits_first_chunk = atoi(e) != 0;
+        if (const char *e = getenv("SPDNN_TABLE_CACHE")) c->table_cache = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BITS_THREADS")) c->bits_threads = std::max(0, std::min(kBitsMaxThreads, atoi(e)));
         if (const char *e = getenv("SPDNN_LAZY_EXPAND")) c->lazy_expand = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_ALT2_SMALL_BLOCKS")) c->alt2_small_blocks = atoi(e) != 0;

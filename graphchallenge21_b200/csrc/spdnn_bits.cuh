@@ -29,10 +29,18 @@ namespace spdnn_impl {
 constexpr int kBitsMaxThreads = 1024;
 constexpr int kBitsCheckEvery = 32;      // layers between two checks for an unsaturated output
 
+// Where the layer records come from.  kBitsCached: the chunk's layers repeat a few distinct records (a periodic
+// network in its steady state): all of them are brought into shared memory once, a.rec_of[layer] names the
+// record of every layer, and the layer loop touches no global memory at all.  kBitsRing: records stream through
+// a ring of a.tring buffers, groups of 1 << tgroup_shift layers per bulk copy.  kBitsGlobal: read in place.
+constexpr int kBitsGlobal = 0, kBitsRing = 1, kBitsCached = 2;
+
 // Dynamic shared memory: two word buffers of a.wwords words (a multiple of 64, at least the largest
-// v_in / classes of the chunk), then (STAGED) a.tring buffers of (stream_stride << tgroup_shift) bytes.
-template <bool STAGED>
+// v_in / classes of the chunk), then kBitsRing: a.tring buffers of (stream_stride << tgroup_shift) bytes;
+// kBitsCached: a.cache_records records of stream_stride bytes, then one uint16 per layer of the chunk.
+template <int MODE>
 __global__ void __launch_bounds__(kBitsMaxThreads, 1) bits_kernel(const ResArgs a) {
+    constexpr bool STAGED = (MODE == kBitsRing);
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ unsigned int s_or[3];             // OR of the outputs of layer li % 3: who is alive after it
     __shared__ int s_next_group;
@@ -91,6 +99,22 @@ __global__ void __launch_bounds__(kBitsMaxThreads, 1) bits_kernel(const ResArgs 
         if (tid == 0) a.tile_done[tile] = 0;
         return;
     }
+    unsigned short *const s_rec = reinterpret_cast<unsigned short *>(tbl0 + (size_t)a.cache_records * stride);
+    if (MODE == kBitsCached) {
+        // every distinct record of the chunk in one bulk copy, the layer -> record map by plain loads
+        if (tid == 0) {
+            mbar_init(&s_bar[0], 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            bulk_load_table(tbl0, a.cache, (unsigned int)(a.cache_records * stride), &s_bar[0]);
+        }
+        for (int q = tid; q < a.nlayers; q += blockDim.x) s_rec[q] = __ldg(a.rec_of + q);
+        __syncthreads();                                // the barrier's initialisation is visible to every waiter
+        const bool arrived = mbar_wait(&s_bar[0], 0u);
+        if (!__syncthreads_and(arrived ? 1 : 0)) {      // bounded wait ran out: report it, drop the tile's images
+            if (tid == 0) { atomicExch(a.status, 4); a.tile_done[tile] = 1; }
+            return;
+        }
+    }
 
     auto issue_groups = [&](int li) {               // thread 0; every thread has left layer li - 1
         const int lim = min((li >> gshift) + tring, ngroups);
@@ -127,9 +151,11 @@ __global__ void __launch_bounds__(kBitsMaxThreads, 1) bits_kernel(const ResArgs 
             if (!__syncthreads_and(arrived ? 1 : 0)) { failed = true; break; }
             waited_group = g;
         }
-        const unsigned char *T = STAGED ? tbl0 + (size_t)((li >> gshift) & (tring - 1)) * group_bytes + (size_t)(li & gmask) * stride
-                                        : a.stream + (size_t)li * stride;
-        const int4 hdr = STAGED ? *reinterpret_cast<const int4 *>(T) : __ldg(reinterpret_cast<const int4 *>(T));
+        constexpr bool IN_SMEM = (MODE != kBitsGlobal);
+        const unsigned char *T = MODE == kBitsCached ? tbl0 + (size_t)s_rec[li] * stride
+                                 : STAGED ? tbl0 + (size_t)((li >> gshift) & (tring - 1)) * group_bytes + (size_t)(li & gmask) * stride
+                                          : a.stream + (size_t)li * stride;
+        const int4 hdr = IN_SMEM ? *reinterpret_cast<const int4 *>(T) : __ldg(reinterpret_cast<const int4 *>(T));
         const int classes = hdr.x;
         if ((unsigned int)hdr.w != tt_cur) {
             tt_cur = (unsigned int)hdr.w;
@@ -141,7 +167,7 @@ __global__ void __launch_bounds__(kBitsMaxThreads, 1) bits_kernel(const ResArgs 
         const unsigned char *wcb = reinterpret_cast<const unsigned char *>(wc);
         for (int ps = warp; ps < passes; ps += nwarps) {
             const uint2 *slot = reinterpret_cast<const uint2 *>(T + 16 + ps * 256) + lane;
-            const uint2 e = STAGED ? *slot : __ldg(slot);
+            const uint2 e = IN_SMEM ? *slot : __ldg(slot);
             const unsigned int a1 = *reinterpret_cast<const unsigned int *>(wcb + (e.x & 0xffffu));
             const unsigned int b1 = *reinterpret_cast<const unsigned int *>(wcb + (e.x >> 16));
             const unsigned int a2 = *reinterpret_cast<const unsigned int *>(wcb + (e.y & 0xffffu));

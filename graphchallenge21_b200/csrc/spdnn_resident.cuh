@@ -96,6 +96,11 @@ struct ResArgs {
     // 1 = the pre-pass finished the tile and alt2_kernel's blocks of that tile skip their work; nullptr = no pre-pass
     unsigned char *tile_done;
     int wwords;               // bits_kernel: words per word buffer (a multiple of 64)
+    // bits_kernel, cached records: the distinct records of the chunk's stream (cache_records of stream_stride bytes,
+    // held in shared memory for the whole launch) and which of them each layer uses; nullptr = stream per layer
+    const unsigned char *cache;
+    const unsigned short *rec_of;
+    int cache_records;
     // First chunk of a pass on a binary input (spdnn_front.cuh): alt2_kernel computes the layer BEFORE the chunk
     // (front_layer: GENERIC tables over the neurons, uniform weight, K <= 252) from the input's bit matrix while it
     // loads, instead of reading that layer's output from yin.  nullptr = the chunk's input is in yin.
