@@ -122,10 +122,13 @@ constexpr int kAlt2MaxTableRing = 4;
 // the activation buffer that is free at that moment: while a block is in the bit form it needs
 // neither float buffer (it converts `cur` on the way in and rebuilds `cur` on the way out).
 // IPT = images per thread (4 or 8): with 8 a thread carries two float4 halves through every step.
-// NT = threads per block: 256, or 128 for chunks whose layers have at most 64 classes -- there one warp
-// does the bit form, and smaller blocks let twice as many of those warps share an SM.
+// NT = threads per block: 256; 128 for chunks whose layers have at most 64 classes -- there one warp
+// does the bit form, and smaller blocks let twice as many of those warps share an SM; 512 for chunks whose
+// buffers leave room for one block per SM only -- the float form is a chain of dependent adds per output,
+// and sixteen warps fill the issue slots that eight leave empty.
 template <int TI, int IPT, int KT, bool STAGED, int NT>
-__global__ void __launch_bounds__(NT, (NT == 128 ? 2 : 1) * SPDNN_ALT2_MIN_BLOCKS) alt2_kernel(const ResArgs a) {
+__global__ void __launch_bounds__(NT, NT == 128 ? 2 * SPDNN_ALT2_MIN_BLOCKS : NT == 512 ? SPDNN_ALT2_MIN_BLOCKS / 2 : SPDNN_ALT2_MIN_BLOCKS)
+alt2_kernel(const ResArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ unsigned int s_alive[3];          // float form: images alive after layer li % 3
     __shared__ int s_ns[3];                      // float form: layer li % 3 produced an output that is neither 0 nor clip

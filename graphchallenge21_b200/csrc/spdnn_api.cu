@@ -137,6 +137,7 @@ struct spdnn {
     bool bits_prepass = true;          // SPDNN_BITS_KERNEL=0: ALT2 chunks of wide layers run without the pre-pass
     bool bits_first_chunk = false;     // SPDNN_BITS_FIRST=1: also before the first resident chunk of a pass
     bool table_cache = true;           // SPDNN_TABLE_CACHE=0: the pre-pass always streams its layer records
+    int alt2_threads = 0;              // SPDNN_ALT2_THREADS=256|512: block size of ALT2 chunks with 4 images per thread (0: by shared memory)
     int bits_threads = 0;              // SPDNN_BITS_THREADS: threads per block of the pre-pass (0: by the classes)
     int extra_launches = 0;            // pre-pass launches of the captured schedule
     int graph_extra[2] = {0, 0};
@@ -387,6 +388,14 @@ int launch_resident(spdnn *c, int ti, int ipt, const ResArgs &a, int grid, size_
         // layers of at most 64 classes: blocks of 128 threads (one warp does the bit form; twice the blocks per SM)
         if (ipt == 8 && ti == 32 && !a.bit_multi && c->alt2_small_blocks) return launch_alt2<32, 8, 128>(c, a, grid, smem, k32);
         if (ipt == 8) return ti == 32 ? launch_alt2<32, 8, kThreads>(c, a, grid, smem, k32) : launch_alt2<16, 8, kThreads>(c, a, grid, smem, k32);
+        // one block per SM by its shared memory: 512 threads
+        const bool wide = c->alt2_threads == 512 && smem * 2 + 4096 > (size_t)c->smem_optin;
+        if (wide)
+            switch (ti) {
+                case 16: return launch_alt2<16, 4, 512>(c, a, grid, smem, k32);
+                case 8: return launch_alt2<8, 4, 512>(c, a, grid, smem, k32);
+                default: return launch_alt2<4, 4, 512>(c, a, grid, smem, k32);
+            }
         switch (ti) {
             case 16: return launch_alt2<16, 4, kThreads>(c, a, grid, smem, k32);
             case 8: return launch_alt2<8, 4, kThreads>(c, a, grid, smem, k32);
@@ -1048,6 +1057,7 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
         if (const char *e = getenv("SPDNN_BITS_KERNEL")) c->bits_prepass = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BITS_FIRST")) c->bits_first_chunk = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_TABLE_CACHE")) c->table_cache = atoi(e) != 0;
+        if (const char *e = getenv("SPDNN_ALT2_THREADS")) c->alt2_threads = atoi(e) == 512 ? 512 : atoi(e) == 256 ? 256 : 0;
         if (const char *e = getenv("SPDNN_BITS_THREADS")) c->bits_threads = std::max(0, std::min(kBitsMaxThreads, atoi(e)));
         if (const char *e = getenv("SPDNN_LAZY_EXPAND")) c->lazy_expand = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_ALT2_SMALL_BLOCKS")) c->alt2_small_blocks = atoi(e) != 0;

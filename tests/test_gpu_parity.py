@@ -212,7 +212,8 @@ def _large_case(oracle, bias, clip, n, L, b):
                                  {"SPDNN_BITS_FIRST": "1", "SPDNN_STAGE_TABLES": "0"}, {"SPDNN_BITS_FIRST": "1", "SPDNN_TABLE_GROUP": "1", "SPDNN_TABLE_RING": "2"},
                                  {"SPDNN_BITS_FIRST": "1", "SPDNN_CHUNK_FIRST": "1", "SPDNN_CHUNK_MAX": "3"},
                                  {"SPDNN_BITS_FIRST": "1", "SPDNN_TABLE_CACHE": "0"}, {"SPDNN_FUSED_FRONT": "0"},
-                                 {"SPDNN_FUSED_FRONT": "0", "SPDNN_COUNT_FRONT": "0"}],
+                                 {"SPDNN_FUSED_FRONT": "0", "SPDNN_COUNT_FRONT": "0"}, {"SPDNN_ALT2_THREADS": "512"},
+                                 {"SPDNN_ALT2_THREADS": "512", "SPDNN_RESIDENT_TI": "8", "SPDNN_BITS_KERNEL": "0"}],
                          ids=lambda e: ",".join(f"{k[6:]}={v}" for k, v in e.items()) or "default")
 @pytest.mark.parametrize("bias,clip,n,L,b", [(-0.4, 32.0, 16384, 80, 96), (-0.45, 32.0, 65536, 48, 96)])
 def test_bit_form_at_the_large_network_sizes(bias, clip, n, L, b, env, monkeypatch, oracle):
