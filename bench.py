@@ -556,6 +556,13 @@ def summarize(args, cfg, world, res, headline):
                     "value": edges_step * steps / (mx["ms_e2e_dense"] * 1e-3), "ms_per_step": mx["ms_e2e_dense"] / steps,
                     "h2d_bytes_per_step": res.get("h2d_dense"),
                     "call": "spdnn_set_input_dense (batch x N fp32, pinned host memory)"}},
+        "roofline_input_conversion": {
+            "bound": "hbm", "kernel": "dense_to_words_kernel", "achieved": res["b"] * n * (4.0 + 0.125) / (res["prep_ms"] * 1e-3) / 1e9,
+            "peak": peak, "unit": "GB/s", "frac": res["b"] * n * (4.0 + 0.125) / (res["prep_ms"] * 1e-3) / 1e9 / peak,
+            "ms": res["prep_ms"],
+            "note": "the one kernel of the timed pass that streams HBM: the dense fp32 input read once (4 bytes per activation) and "
+                    "written as one bit per activation; time by CUDA events around the whole input set-up (it also holds two "
+                    "small memsets and three launches that exit at entry for a binary input), rank 0"},
         "gpu_launches": int(res["launches"] * steps),
         "layer_loop_ms": loop_ms, "input_layout_ms": res["prep_ms"], "us_per_layer": loop_ms * 1e3 / L,
     }
