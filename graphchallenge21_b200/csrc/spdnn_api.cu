@@ -132,8 +132,9 @@ struct spdnn {
     unsigned char *has_floats = nullptr;
     bool binary_front = true;          // SPDNN_BINARY_FRONT=0: inputs are always converted to float tiles
     bool count_front = true;           // SPDNN_COUNT_FRONT=0: layer 0 of a binary input always gathers per image
-    bool fused_front = true;           // SPDNN_FUSED_FRONT=0: layer 0 of a binary input runs in the per-layer kernel
-                                       // even where the first ALT2 chunk could compute it while loading
+    bool fused_front = false;          // SPDNN_FUSED_FRONT=1: where layer 0 is followed by an ALT2 chunk, that chunk computes
+                                       // layer 0 of a binary input while it loads (measured slower than the counting kernel:
+                                       // one block per SM cannot hide the latency of its gathers)
     bool bits_prepass = true;          // SPDNN_BITS_KERNEL=0: ALT2 chunks of wide layers run without the pre-pass
     bool bits_first_chunk = false;     // SPDNN_BITS_FIRST=1: also before the first resident chunk of a pass
     bool table_cache = true;           // SPDNN_TABLE_CACHE=0: the pre-pass always streams its layer records
@@ -389,7 +390,7 @@ int launch_resident(spdnn *c, int ti, int ipt, const ResArgs &a, int grid, size_
         if (ipt == 8 && ti == 32 && !a.bit_multi && c->alt2_small_blocks) return launch_alt2<32, 8, 128>(c, a, grid, smem, k32);
         if (ipt == 8) return ti == 32 ? launch_alt2<32, 8, kThreads>(c, a, grid, smem, k32) : launch_alt2<16, 8, kThreads>(c, a, grid, smem, k32);
         // one block per SM by its shared memory: 512 threads
-        const bool wide = c->alt2_threads == 512 && smem * 2 + 4096 > (size_t)c->smem_optin;
+        const bool wide = c->alt2_threads != 256 && smem * 2 + 4096 > (size_t)c->smem_optin;
         if (wide)
             switch (ti) {
                 case 16: return launch_alt2<16, 4, 512>(c, a, grid, smem, k32);
