@@ -741,7 +741,8 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan, bool gated) {
                 b.cache = st.cache; b.rec_of = st.rec_of; b.cache_records = st.cache_records;
                 size_t bsmem = (size_t)st.wwords * 8 + (size_t)st.bits_tring * ((size_t)st.stride << st.bits_gshift);
                 if (st.cache_records > 0) {
-                    bsmem = (size_t)st.wwords * 8 + (size_t)st.cache_records * st.stride + ((size_t)st.count * 2 + 15) / 16 * 16;
+                    // two word buffers, the records, the layer -> record map, a copy of a segment's input words
+                    bsmem = (size_t)st.wwords * 12 + (size_t)st.cache_records * st.stride + ((size_t)st.count * 2 + 15) / 16 * 16;
                     if (int rc = allow_max_dynamic_smem(c, bits_kernel<kBitsCached>)) return rc;
                     bits_kernel<kBitsCached><<<c->tiles_cap, st.bits_threads, bsmem, c->stream>>>(b);
                 } else if (st.bits_tring > 0) {
@@ -907,7 +908,7 @@ int build_graph_kind(spdnn *c, int kind) {
             const size_t d = first_layer.size();
             const size_t rec_bytes = ((size_t)st.count * 2 + 15) / 16 * 16;
             if (d <= 65535 && d * st.stride < ((size_t)1 << 20) &&
-                (size_t)st.wwords * 8 + d * st.stride + rec_bytes + 2048 <= (size_t)c->smem_optin) {
+                (size_t)st.wwords * 12 + d * st.stride + rec_bytes + 2048 <= (size_t)c->smem_optin) {
                 CK(cudaMalloc(&st.cache, d * st.stride));
                 c->streams.push_back(st.cache);
                 unsigned char *rec_dev = nullptr;

@@ -37,7 +37,8 @@ constexpr int kBitsGlobal = 0, kBitsRing = 1, kBitsCached = 2;
 
 // Dynamic shared memory: two word buffers of a.wwords words (a multiple of 64, at least the largest
 // v_in / classes of the chunk), then kBitsRing: a.tring buffers of (stream_stride << tgroup_shift) bytes;
-// kBitsCached: a.cache_records records of stream_stride bytes, then one uint16 per layer of the chunk.
+// kBitsCached: a.cache_records records of stream_stride bytes, then one uint16 per layer of the chunk (rounded up to
+// 16 bytes), then a.wwords words that hold a copy of a segment's input.
 template <int MODE>
 __global__ void __launch_bounds__(kBitsMaxThreads, 1) bits_kernel(const ResArgs a) {
     constexpr bool STAGED = (MODE == kBitsRing);
@@ -143,99 +144,8 @@ __global__ void __launch_bounds__(kBitsMaxThreads, 1) bits_kernel(const ResArgs 
     int li = 0, last_classes = 0;
     int waited_group = -1;
     bool failed = false, unsat = false;
-    if (MODE == kBitsCached && a.wwords <= nwarps * 128) {
-        // Every record is in shared memory and a warp has at most two passes per layer: the layer loop as a
-        // software pipeline.  What a layer's critical path keeps is: barrier -> the word loads of its passes
-        // (all in flight together) -> logic -> stores -> barrier.  The entries of the NEXT layer are fetched
-        // while this one computes (they do not depend on the words), and who died in layer l is worked out
-        // one layer late, beside layer l + 1's loads (s_or[l % 3] stays valid until layer l + 2 clears it).
-        const int spasses = (stride - 16) >> 8;                 // passes a record has room for
-        const int p0 = warp, p1 = warp + nwarps;
-        auto entries = [&](const unsigned char *rec, int ps) -> uint2 {
-            return ps < spasses ? (reinterpret_cast<const uint2 *>(rec + 16 + ps * 256))[lane] : make_uint2(0u, 0u);
-        };
-        const unsigned char *T = tbl0 + (size_t)s_rec[0] * stride;
-        int4 hdr = *reinterpret_cast<const int4 *>(T);
-        uint2 e0 = entries(T, p0), e1 = entries(T, p1);
-        int booked = 0;                                          // layers whose deaths have been worked out
-        auto book = [&](int l) {
-            const unsigned int now = s_or[l % 3] & alive;
-            if (now != alive && tid == 0) {
-                s_ev_layer[s_nev] = l;
-                s_ev_cnt[s_nev] = __popc(alive & ~now);
-                ++s_nev;
-            }
-            alive = now;
-        };
-        while (li < a.nlayers) {
-            const int classes = hdr.x;
-            if ((unsigned int)hdr.w != tt_cur) {
-                tt_cur = (unsigned int)hdr.w;
-                tm = truth_masks(tt_cur);
-            }
-            const bool usual = (tt_cur == 0x80404000u);
-            const int passes = (classes + 63) >> 6;
-            const bool has0 = p0 < passes, has1 = p1 < passes;
-            const unsigned char *wcb = reinterpret_cast<const unsigned char *>(wc);
-            // slots of a pass the layer does not have read row 0 (their entries are zero or stale): harmless, unused
-            const unsigned int a1 = *reinterpret_cast<const unsigned int *>(wcb + (e0.x & 0xffffu));
-            const unsigned int b1 = *reinterpret_cast<const unsigned int *>(wcb + (e0.x >> 16));
-            const unsigned int a2 = *reinterpret_cast<const unsigned int *>(wcb + (e0.y & 0xffffu));
-            const unsigned int b2 = *reinterpret_cast<const unsigned int *>(wcb + (e0.y >> 16));
-            const unsigned int a3 = *reinterpret_cast<const unsigned int *>(wcb + (e1.x & 0xffffu));
-            const unsigned int b3 = *reinterpret_cast<const unsigned int *>(wcb + (e1.x >> 16));
-            const unsigned int a4 = *reinterpret_cast<const unsigned int *>(wcb + (e1.y & 0xffffu));
-            const unsigned int b4 = *reinterpret_cast<const unsigned int *>(wcb + (e1.y >> 16));
-            if (booked < li) { book(li - 1); booked = li; }
-            // the next layer's record, while the words arrive
-            int4 hdr_n = hdr;
-            uint2 e0n = e0, e1n = e1;
-            if (li + 1 < a.nlayers) {
-                const unsigned char *Tn = tbl0 + (size_t)s_rec[li + 1] * stride;
-                hdr_n = *reinterpret_cast<const int4 *>(Tn);
-                e0n = entries(Tn, p0);
-                e1n = entries(Tn, p1);
-            }
-            unsigned int x1, x2, x3, x4, n1, n2, n3, n4;
-            if (usual) {
-                x1 = a1 & b1; x2 = a2 & b2; x3 = a3 & b3; x4 = a4 & b4;
-                n1 = a1 ^ b1; n2 = a2 ^ b2; n3 = a3 ^ b3; n4 = a4 ^ b4;
-            } else {
-                x1 = select4(a1, b1, tm.hi); x2 = select4(a2, b2, tm.hi); x3 = select4(a3, b3, tm.hi); x4 = select4(a4, b4, tm.hi);
-                n1 = select4(a1, b1, tm.ns); n2 = select4(a2, b2, tm.ns); n3 = select4(a3, b3, tm.ns); n4 = select4(a4, b4, tm.ns);
-            }
-            if (force_dead) { x1 &= alive; x2 &= alive; x3 &= alive; x4 &= alive; n1 &= alive; n2 &= alive; n3 &= alive; n4 &= alive; }
-            unsigned int o = 0u;
-            if (has0) {
-                wn[p0 * 64 + lane] = x1;
-                wn[p0 * 64 + 32 + lane] = x2;
-                const bool in1 = p0 * 64 + lane < classes, in2 = p0 * 64 + 32 + lane < classes;      // only the last pass has slots past the classes
-                ns |= (in1 ? n1 : 0u) | (in2 ? n2 : 0u);
-                o |= (in1 ? x1 : 0u) | (in2 ? x2 : 0u);
-            }
-            if (has1) {
-                wn[p1 * 64 + lane] = x3;
-                wn[p1 * 64 + 32 + lane] = x4;
-                const bool in3 = p1 * 64 + lane < classes, in4 = p1 * 64 + 32 + lane < classes;
-                ns |= (in3 ? n3 : 0u) | (in4 ? n4 : 0u);
-                o |= (in3 ? x3 : 0u) | (in4 ? x4 : 0u);
-            }
-            o = __reduce_or_sync(0xffffffffu, o);
-            if (lane == 0 && o) atomicOr(&s_or[li % 3], o);
-            if (tid == 0) s_or[(li + 1) % 3] = 0u;      // layer li + 1's slot: layer li - 2's deaths were worked out a layer ago
-            __syncthreads();
-            unsigned int *t = wc; wc = wn; wn = t;
-            last_classes = classes;
-            ++li;
-            hdr = hdr_n; e0 = e0n; e1 = e1n;
-            if ((li % kBitsCheckEvery) == 0 || li == a.nlayers) {
-                book(li - 1); booked = li;
-                if (__syncthreads_or(ns != 0u ? 1 : 0)) { unsat = true; break; }
-                if (alive == 0u) break;
-            }
-        }
-    } else
-    while (li < a.nlayers) {
+    auto run_tracked = [&](int lend) {
+    while (li < lend) {
         if (STAGED && (li >> gshift) != waited_group) {
             if (tid == 0) issue_groups(li);
             const int g = li >> gshift;
@@ -302,10 +212,100 @@ __global__ void __launch_bounds__(kBitsMaxThreads, 1) bits_kernel(const ResArgs 
         unsigned int *t = wc; wc = wn; wn = t;
         last_classes = classes;
         ++li;
-        if ((li % kBitsCheckEvery) == 0 || li == a.nlayers || alive == 0u) {
+        if ((li % kBitsCheckEvery) == 0 || li == lend || alive == 0u) {
             if (__syncthreads_or(ns != 0u ? 1 : 0)) { unsat = true; break; }
         }
         if (alive == 0u) break;
+    }
+    };
+    if (MODE == kBitsCached && a.wwords <= nwarps * 128 && !force_dead) {
+        // Every record is in shared memory and a warp has at most two passes per layer.  The records are checked
+        // once: if all carry the usual truth table ((0, 0) -> 0, (clip, clip) -> clip, one clip-valued input -> an
+        // unsaturated output), a layer is x = a & b with a ^ b marking the unsaturated outputs, and the loop below
+        // runs SEGMENTS of up to kBitsCheckEvery layers with nothing per layer but that: the next layer's entries
+        // are fetched while this one computes, and who is alive is not tracked -- a dead image's words are all zero
+        // and stay so, therefore the OR of the words after the segment tells who is alive then.  Only if that
+        // differs from before (an image died inside the segment: rare) are the segment's layers run again from a
+        // copy of its input, with the per-layer bookkeeping that finds the layer of death.
+        bool all_usual = true;
+        for (int q = 0; q < a.cache_records; ++q)
+            all_usual &= (*reinterpret_cast<const unsigned int *>(tbl0 + (size_t)q * stride + 12) == 0x80404000u);
+        if (all_usual) {
+            unsigned int *const ckpt = reinterpret_cast<unsigned int *>(reinterpret_cast<unsigned char *>(s_rec) +
+                                                                        (((size_t)a.nlayers * 2 + 15) & ~(size_t)15));
+            const int spasses = (stride - 16) >> 8;                 // passes a record has room for
+            const int p0 = warp, p1 = warp + nwarps;
+            auto entries = [&](const unsigned char *rec, int ps) -> uint2 {
+                return ps < spasses ? (reinterpret_cast<const uint2 *>(rec + 16 + ps * 256))[lane] : make_uint2(0u, 0u);
+            };
+            while (li < a.nlayers && !unsat && !failed) {
+                const int l0 = li, l1 = min(li + kBitsCheckEvery, a.nlayers);
+                for (int q = tid; q < a.wwords; q += blockDim.x) ckpt[q] = wc[q];      // read before layer l0's barrier, which precedes any write to wc
+                const unsigned char *T = tbl0 + (size_t)s_rec[li] * stride;
+                int classes = *reinterpret_cast<const int *>(T);
+                uint2 e0 = entries(T, p0), e1 = entries(T, p1);
+                unsigned int nsx = 0u;
+                for (; li < l1; ++li) {
+                    const unsigned char *wcb = reinterpret_cast<const unsigned char *>(wc);
+                    const int passes = (classes + 63) >> 6;
+                    // a pass the layer does not have is skipped; a slot past the classes in its last pass reads row 0
+                    // twice (a ^ a = 0) and writes a row that nobody reads
+                    const unsigned int a1 = *reinterpret_cast<const unsigned int *>(wcb + (e0.x & 0xffffu));
+                    const unsigned int b1 = *reinterpret_cast<const unsigned int *>(wcb + (e0.x >> 16));
+                    const unsigned int a2 = *reinterpret_cast<const unsigned int *>(wcb + (e0.y & 0xffffu));
+                    const unsigned int b2 = *reinterpret_cast<const unsigned int *>(wcb + (e0.y >> 16));
+                    const unsigned int a3 = *reinterpret_cast<const unsigned int *>(wcb + (e1.x & 0xffffu));
+                    const unsigned int b3 = *reinterpret_cast<const unsigned int *>(wcb + (e1.x >> 16));
+                    const unsigned int a4 = *reinterpret_cast<const unsigned int *>(wcb + (e1.y & 0xffffu));
+                    const unsigned int b4 = *reinterpret_cast<const unsigned int *>(wcb + (e1.y >> 16));
+                    const bool has0 = p0 < passes, has1 = p1 < passes;
+                    last_classes = classes;
+                    if (li + 1 < a.nlayers) {                       // the next layer's record, while the words arrive
+                        const unsigned char *Tn = tbl0 + (size_t)s_rec[li + 1] * stride;
+                        classes = *reinterpret_cast<const int *>(Tn);
+                        e0 = entries(Tn, p0);
+                        e1 = entries(Tn, p1);
+                    }
+                    if (has0) {
+                        wn[p0 * 64 + lane] = a1 & b1;
+                        wn[p0 * 64 + 32 + lane] = a2 & b2;
+                        nsx |= (a1 ^ b1) | (a2 ^ b2);
+                    }
+                    if (has1) {
+                        wn[p1 * 64 + lane] = a3 & b3;
+                        wn[p1 * 64 + 32 + lane] = a4 & b4;
+                        nsx |= (a3 ^ b3) | (a4 ^ b4);
+                    }
+                    __syncthreads();
+                    unsigned int *t = wc; wc = wn; wn = t;
+                }
+                // who is alive after the segment: the OR of the last layer's rows
+                unsigned int o = 0u;
+                for (int q = tid; q < last_classes; q += blockDim.x) o |= wc[q];
+                o = __reduce_or_sync(0xffffffffu, o);
+                if (lane == 0 && o) atomicOr(&s_or[0], o);
+                const bool any_ns = __syncthreads_or(nsx != 0u ? 1 : 0) != 0;      // (the barrier also publishes the atomics)
+                const unsigned int now = s_or[0] & alive;
+                __syncthreads();                               // everyone has read s_or[0]
+                if (tid == 0) s_or[0] = s_or[1] = s_or[2] = 0u;
+                if (any_ns) { unsat = true; break; }
+                if (now != alive) {
+                    // somebody died inside the segment: again from its input, layer by layer (the tracked loop wants
+                    // its three slots zero and leaves them in any state)
+                    for (int q = tid; q < a.wwords; q += blockDim.x) wc[q] = ckpt[q];
+                    li = l0;
+                    __syncthreads();
+                    run_tracked(l1);
+                    __syncthreads();
+                    if (tid == 0) s_or[0] = s_or[1] = s_or[2] = 0u;
+                }
+                if (alive == 0u) break;
+            }
+        } else {
+            run_tracked(a.nlayers);
+        }
+    } else {
+        run_tracked(a.nlayers);
     }
     if (STAGED) {
         if (tid == 0) drain(li);

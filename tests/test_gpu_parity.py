@@ -194,12 +194,13 @@ def test_bit_form_of_saturated_activations(bias, clip, n, L, env, monkeypatch, o
 def _large_case(oracle, bias, clip, n, L, b):
     """Batch with every kind of image the bit form distinguishes: ordinary blobs, runs that are
     saturated from the start (whole 32-image blocks begin a chunk as words), values off the
-    1/16 grid and all-clip images."""
+    1/16 grid, all-clip images and all-zero images."""
     net = SyntheticNetwork(n, L, "radix16", bias=bias)
     y0 = synthetic_images(n, b)
     y0[32:64] *= np.float32(clip)
     y0[64:80:3] *= np.float32(0.37 * clip)
     y0[80:88] = np.float32(clip)
+    y0[40:44] = 0.0           # all-zero images inside a saturated tile: they die in the tile's first layer of the bit form
     key = (bias, clip, n, L, b)
     if key not in _LARGE_WANT:
         _LARGE_WANT[key] = oracle.infer(y0, [(r, None) for r in rows_of(net)], bias, clip=clip, first_image=11)
