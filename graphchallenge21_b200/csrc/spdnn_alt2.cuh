@@ -342,6 +342,7 @@ alt2_kernel(const ResArgs a) {
         const int work_warp = (int)((blockIdx.x / (unsigned int)max(a.sm_count, 1)) % (NT / 32));
         int ws = 0;                  // bit form: the word buffer that holds the current activations
         bool bitmode = false;
+        bool took_exact = true;      // float form: the exact-sum shortcut applied to a class of this thread in the last layer
         if (start_in_bits) {
             wring0 = reinterpret_cast<unsigned int *>(nxt);
             rows_to_bits(cur, wring0);
@@ -542,6 +543,10 @@ alt2_kernel(const ResArgs a) {
             unsigned int bits = 0;
             bool ns = false;
             const unsigned char *in = cur + sub * TB;
+            // The exact-sum shortcut needs a test of all eight inputs of a class; a thread whose classes all failed it
+            // in the last layer skips the test (same bits either way) and tries again every eighth layer.
+            const bool try_exact = a.exact_ok != 0 && (took_exact || (li & 7) == 0);
+            took_exact = false;
             for (int u = grp; u < classes; u += CPI) {
                 const unsigned int *ep = reinterpret_cast<const unsigned int *>(T + alt2_entry_offset(u));
                 const unsigned int e = STAGED ? *ep : __ldg(ep);
@@ -551,7 +556,7 @@ alt2_kernel(const ResArgs a) {
                 for (int h = 0; h < NQ; ++h) {
                     const float4 va = *reinterpret_cast<const float4 *>(in + ao + 16 * h);
                     const float4 vb = *reinterpret_cast<const float4 *>(in + bo + 16 * h);
-                    const float4 s = class_sum_alt2<KT>(va, vb, lk, lw, a.exact_ok != 0);
+                    const float4 s = class_sum_alt2<KT>(va, vb, lk, lw, try_exact, &took_exact);
                     float4 y;
                     y.x = finish_output(s.x, a.bias, a.clip);
                     y.y = finish_output(s.y, a.bias, a.clip);

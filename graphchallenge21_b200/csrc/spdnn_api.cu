@@ -118,6 +118,7 @@ struct spdnn {
     int smem_optin = 0;                // shared memory one block may opt in to
     bool stage_tables = true;          // bring the per-layer tables into shared memory with bulk copies
     int chunk_first = 8, chunk_max = 2048, chunk_growth = 4;      // SPDNN_CHUNK_FIRST / _MAX / _GROWTH
+    std::vector<int> chunk_list;       // SPDNN_CHUNKS=a,b,c,...: lengths of the first resident chunks of a pass, in order
     int chunk_growth_generic = 2;      // GENERIC chunks grow more slowly: a tile that is not saturated when its chunk starts
                                        // stays in the float form to the chunk's end, and that form costs 32 gathers per output
     int nsteps = 0;                    // launches of the last captured schedule
@@ -514,7 +515,8 @@ struct Step {
 // of layout.
 std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
     std::vector<Step> plan;
-    int l = 0, chunk = c->chunk_first;
+    int l = 0, chunk = c->chunk_list.empty() ? c->chunk_first : c->chunk_list[0];
+    int resident_chunks = 0;       // resident chunks planned so far
     int alt2_chunks = 0;           // ALT2 chunks planned so far
     int generic_chunks = 0;        // GENERIC chunks planned so far
     while (l < c->layers) {
@@ -634,7 +636,11 @@ std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
                 }
             }
         }
-        if (st.ti) chunk = std::min(chunk * (st.max_classes > 0 ? c->chunk_growth : c->chunk_growth_generic), c->chunk_max);
+        if (st.ti) {
+            ++resident_chunks;
+            if (resident_chunks < (int)c->chunk_list.size()) chunk = c->chunk_list[resident_chunks];
+            else chunk = std::min(chunk * (st.max_classes > 0 ? c->chunk_growth : c->chunk_growth_generic), c->chunk_max);
+        }
         if (st.ti && st.max_classes > 0) ++alt2_chunks;
         if (st.ti && st.max_classes == 0) ++generic_chunks;
         if (!st.ti) st.bits_threads = 0;
@@ -1072,6 +1078,15 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
         if (const char *e = getenv("SPDNN_REPS_ONLY")) c->reps_only = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_CHUNK_FIRST")) c->chunk_first = std::max(1, atoi(e));
         if (const char *e = getenv("SPDNN_CHUNK_MAX")) c->chunk_max = std::max(1, atoi(e));
+        if (const char *e = getenv("SPDNN_CHUNKS")) {
+            for (const char *q = e; *q;) {
+                char *end = nullptr;
+                const long v = strtol(q, &end, 10);
+                if (end == q) break;
+                if (v > 0) c->chunk_list.push_back((int)std::min<long>(v, 1 << 20));
+                q = (*end == ',') ? end + 1 : end;
+            }
+        }
         if (const char *e = getenv("SPDNN_CHUNK_GROWTH")) c->chunk_growth = c->chunk_growth_generic = std::max(1, std::min(64, atoi(e)));
         if (const char *e = getenv("SPDNN_HOST_BUDGET_MB")) c->host_budget = (size_t)atoll(e) << 20;
         if (const char *e = getenv("SPDNN_WEIGHT_BUDGET_MB")) c->weight_budget = (size_t)atoll(e) << 20;

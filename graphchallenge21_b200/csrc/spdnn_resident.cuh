@@ -116,9 +116,13 @@ struct ResArgs {
 
 __host__ __device__ __forceinline__ int resident_phys_row(int r) {
     // flip the low bit by the parity of the upper bits: a bijection on [0, 2m)
+#ifdef __CUDA_ARCH__
+    return r ^ (__popc((unsigned int)(r >> 1)) & 1);
+#else
     int x = r >> 1;
     x ^= x >> 16; x ^= x >> 8; x ^= x >> 4; x ^= x >> 2; x ^= x >> 1;
     return r ^ (x & 1);
+#endif
 }
 
 // Two fp32 values in one 64-bit register pair, added by ONE instruction (add.rn.f32x2, sm_100):
@@ -257,7 +261,7 @@ __device__ __forceinline__ float4 class_sum_generic(const int32_t *rows, const f
 // 16 (a + b), which is computed directly.  Saturated networks (activations 0 or 32, the steady
 // state of the challenge networks) take this path in every layer; the result bits are the same.
 template <int KT>
-__device__ __forceinline__ float4 class_sum_alt2(const float4 a, const float4 b, int k, float w, bool exact_ok) {
+__device__ __forceinline__ float4 class_sum_alt2(const float4 a, const float4 b, int k, float w, bool exact_ok, bool *took = nullptr) {
     const Acc4 pa = acc_from(a), pb = acc_from(b);
     if (KT == 32 && exact_ok) {
         const f32x2 M = pack2(786432.0f, 786432.0f), NM = pack2(-786432.0f, -786432.0f);
@@ -266,6 +270,7 @@ __device__ __forceinline__ float4 class_sum_alt2(const float4 a, const float4 b,
         if (d == 0ull) {
             Acc4 s = pa;
             acc_add(s, pb);
+            if (took) *took = true;
             return mul4(acc_get(s), 16.0f * w);
         }
     }
