@@ -119,6 +119,7 @@ struct spdnn {
     bool stage_tables = true;          // bring the per-layer tables into shared memory with bulk copies
     int chunk_first = 8, chunk_max = 2048, chunk_growth = 4;      // SPDNN_CHUNK_FIRST / _MAX / _GROWTH
     std::vector<int> chunk_list;       // SPDNN_CHUNKS=a,b,c,...: lengths of the first resident chunks of a pass, in order
+    bool chunk_growth_set = false;     // SPDNN_CHUNK_GROWTH was given: it applies to every chunk
     int chunk_growth_generic = 2;      // GENERIC chunks grow more slowly: a tile that is not saturated when its chunk starts
                                        // stays in the float form to the chunk's end, and that form costs 32 gathers per output
     int nsteps = 0;                    // launches of the last captured schedule
@@ -639,6 +640,9 @@ std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
         if (st.ti) {
             ++resident_chunks;
             if (resident_chunks < (int)c->chunk_list.size()) chunk = c->chunk_list[resident_chunks];
+            // a chunk with a bits_kernel pre-pass runs its saturated tiles at a fraction of the float form's cost and
+            // dead images cost it nothing: once such a chunk has run, the rest of the network is one chunk
+            else if (st.max_classes > 0 && st.bits_threads > 0 && !c->chunk_growth_set) chunk = c->chunk_max;
             else chunk = std::min(chunk * (st.max_classes > 0 ? c->chunk_growth : c->chunk_growth_generic), c->chunk_max);
         }
         if (st.ti && st.max_classes > 0) ++alt2_chunks;
@@ -1087,7 +1091,10 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
                 q = (*end == ',') ? end + 1 : end;
             }
         }
-        if (const char *e = getenv("SPDNN_CHUNK_GROWTH")) c->chunk_growth = c->chunk_growth_generic = std::max(1, std::min(64, atoi(e)));
+        if (const char *e = getenv("SPDNN_CHUNK_GROWTH")) {
+            c->chunk_growth = c->chunk_growth_generic = std::max(1, std::min(64, atoi(e)));
+            c->chunk_growth_set = true;
+        }
         if (const char *e = getenv("SPDNN_HOST_BUDGET_MB")) c->host_budget = (size_t)atoll(e) << 20;
         if (const char *e = getenv("SPDNN_WEIGHT_BUDGET_MB")) c->weight_budget = (size_t)atoll(e) << 20;
     }
