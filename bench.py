@@ -277,13 +277,16 @@ def run_reference_gpu_loop(cfg, pattern, _unused=None):
         for _ in range(3):
             g.set_input_dense(y0)
             ms.append(g.infer().infer_ms)
-        same = bool(np.array_equal(g.layer_live(), ref["live"]))
+        ours_live = g.layer_live().copy()
+        same = bool(np.array_equal(ours_live, ref["live"]))
     edges = batch * n * 32.0 * layers
     return {"kernel": "snig_inference (src/microbenchmark/snig.cu:19-120), host loop :211-255", "value": edges / (ref["kernel_ms"] * 1e-3),
             "unit": UNIT, "kernel_ms": ref["kernel_ms"], "sec_size": ref["sec_size"],
             "sample": f"first {batch} images x first {layers} layers of the workload; sum of the per-layer kernel times it prints",
             "ours_same_sample": {"value": edges / (min(ms) * 1e-3), "layer_loop_ms": min(ms)},
             "survivor_counts_equal_ours": same,
+            "survivors_after_layer": {str(i): [int(ref["live"][i]), int(ours_live[i])] for i in sorted({0, 1, 2, 4, 8, 16, 32, layers - 1}) if i < layers},
+            "first_layer_that_differs": None if same else int(np.nonzero(ours_live != ref["live"])[0][0]),
             "note": "all_network.cu's pattern-specific kernels read their work list past its end and are not run on shared GPUs"}
 
 

@@ -593,10 +593,11 @@ std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
                                     (size_t)tr * ((size_t)st.stride << gs) <= (size_t)c->smem_optin / 4) { st.gshift = gs; st.tring = tr; }
                     // Pre-pass for tiles that are saturated already (bits_kernel): layers of more than one pass of 64
                     // classes, where the float buffers leave this kernel's own bit form few images per block.  Not
-                    // before the first chunk of a pass, whose input is not saturated unless the images are.
+                    // before the first two chunks of a pass: the challenge networks saturate around layer 30, and a
+                    // tile that is not saturated costs the pre-pass a read of all its rows for nothing.
                     const int rows_max = std::max(rows, maxc);
                     if (c->bits_prepass && c->bit_form && c->clip > 0.0f && maxc > 64 && rows_max <= 16383 &&
-                        (alt2_chunks > 0 || c->bits_first_chunk)) {
+                        (alt2_chunks > 1 || c->bits_first_chunk)) {
                         st.wwords = (rows_max + 63) / 64 * 64;
                         const int passes = (maxc + 63) / 64;
                         int nt = c->bits_threads > 0 ? c->bits_threads : 32 * ((passes + 1) / 2);
@@ -641,8 +642,9 @@ std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
             ++resident_chunks;
             if (resident_chunks < (int)c->chunk_list.size()) chunk = c->chunk_list[resident_chunks];
             // a chunk with a bits_kernel pre-pass runs its saturated tiles at a fraction of the float form's cost and
-            // dead images cost it nothing: once such a chunk has run, the rest of the network is one chunk
-            else if (st.max_classes > 0 && st.bits_threads > 0 && !c->chunk_growth_set) chunk = c->chunk_max;
+            // dead images cost it nothing: from the first such chunk on the rest of the network is one chunk
+            else if (st.max_classes > 64 && alt2_chunks >= 1 && c->bits_prepass && c->bit_form && c->clip > 0.0f && !c->chunk_growth_set)
+                chunk = c->chunk_max;
             else chunk = std::min(chunk * (st.max_classes > 0 ? c->chunk_growth : c->chunk_growth_generic), c->chunk_max);
         }
         if (st.ti && st.max_classes > 0) ++alt2_chunks;
