@@ -284,7 +284,13 @@ def run_reference_gpu_loop(cfg, pattern, _unused=None):
             "unit": UNIT, "kernel_ms": ref["kernel_ms"], "sec_size": ref["sec_size"],
             "sample": f"first {batch} images x first {layers} layers of the workload; sum of the per-layer kernel times it prints",
             "ours_same_sample": {"value": edges / (min(ms) * 1e-3), "layer_loop_ms": min(ms)},
-            "survivor_counts_equal_ours": same,
+            "survivor_counts_equal_ours": same, "survivors_after_last_layer_equal_ours": bool(ours_live[-1] == ref["live"][-1]),
+            "layers_with_other_counts": int(np.count_nonzero(ours_live != ref["live"])),
+            "why_counts_can_differ": "snig_inference starts every sum from the bias and accumulates with unordered shared-memory atomics "
+                                     "(snig.cu:72-74, 98); the reference's CPU loop and its all_network.cu kernels, which this library follows "
+                                     "bit for bit, sum from 0.0 and add the bias last (cpu_spmm_fuse.h:46, all_network.cu:57). An activation that "
+                                     "is an exact zero in one order can be a rounding residue below 1e-5 in the other, so an image whose only "
+                                     "non-zero activations are such residues is counted one layer longer by one of the two",
             "survivors_after_layer": {str(i): [int(ref["live"][i]), int(ours_live[i])] for i in sorted({0, 1, 2, 4, 8, 16, 32, layers - 1}) if i < layers},
             "first_layer_that_differs": None if same else int(np.nonzero(ours_live != ref["live"])[0][0]),
             "note": "all_network.cu's pattern-specific kernels read their work list past its end and are not run on shared GPUs"}
