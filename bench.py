@@ -447,6 +447,7 @@ def run_workload(args, cfg, world, rank, local, stream, sampler, headline):
         g.infer_async()
 
     gather_s = [0.0]
+    cap = (B + world - 1) // world if args.scaling == "strong" else B        # the largest shard: every rank knows it
 
     def step_e2e(kind):
         if kind == "bits":
@@ -458,7 +459,7 @@ def run_workload(args, cfg, world, rank, local, stream, sampler, headline):
         g.infer_async()
         mine = g.categories()                     # D2H of this rank's result (waits for the step)
         t0 = time.perf_counter()
-        everyone = gather_categories(np.asarray(mine).copy())      # the one exchange step: all-gather of the survivors
+        everyone = gather_categories(np.asarray(mine).copy(), capacity=cap)      # the one exchange step: all-gather of the survivors
         gather_s[0] += time.perf_counter() - t0
         return everyone
 

@@ -322,10 +322,13 @@ def run_network(neuron: int, batch: int, layer: int, data_dir: str = "../data", 
     return cats
 
 
-def gather_categories(local_ids: np.ndarray, group=None) -> np.ndarray:
+def gather_categories(local_ids: np.ndarray, group=None, capacity: int | None = None) -> np.ndarray:
     """The one exchange step: every rank's ascending list of surviving global image numbers
     is gathered on all ranks and concatenated in rank order (slices are contiguous, so the
-    result is ascending).  Uses ``torch.distributed`` (NCCL or gloo) when initialised."""
+    result is ascending).  Uses ``torch.distributed`` (NCCL or gloo) when initialised.
+    ``capacity``: an upper bound of any rank's list length that every rank knows (the largest
+    shard); with it the exchange is ONE all-gather of ``capacity + 1`` int32 per rank (count, then
+    the numbers), without it the counts are exchanged first."""
     import torch
     import torch.distributed as dist
     if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
@@ -333,14 +336,26 @@ def gather_categories(local_ids: np.ndarray, group=None) -> np.ndarray:
     world = dist.get_world_size(group)
     backend = dist.get_backend(group)
     dev = torch.device("cuda", torch.cuda.current_device()) if backend == "nccl" else torch.device("cpu")
-    n_local = torch.tensor([len(local_ids)], dtype=torch.int64, device=dev)
+    local = np.ascontiguousarray(local_ids, dtype=np.int32)
+    if capacity is not None:
+        if len(local) > capacity:
+            raise ValueError("more survivors than the stated capacity")
+        mine = np.empty(capacity + 1, dtype=np.int32)
+        mine[0] = len(local)
+        mine[1:1 + len(local)] = local
+        mine[1 + len(local):] = -1
+        everyone = torch.empty(world * (capacity + 1), dtype=torch.int32, device=dev)
+        dist.all_gather_into_tensor(everyone, torch.from_numpy(mine).to(dev), group=group)
+        got = everyone.cpu().numpy().reshape(world, capacity + 1)
+        return np.concatenate([got[r, 1:1 + got[r, 0]] for r in range(world)]).astype(np.int32)
+    n_local = torch.tensor([len(local)], dtype=torch.int64, device=dev)
     counts = [torch.zeros(1, dtype=torch.int64, device=dev) for _ in range(world)]
     dist.all_gather(counts, n_local, group=group)
     counts = [int(c.item()) for c in counts]
     cap = max(max(counts), 1)
     buf = torch.full((cap,), -1, dtype=torch.int32, device=dev)
-    if len(local_ids):
-        buf[: len(local_ids)] = torch.from_numpy(np.ascontiguousarray(local_ids, dtype=np.int32)).to(dev)
+    if len(local):
+        buf[: len(local)] = torch.from_numpy(local).to(dev)
     parts = [torch.empty(cap, dtype=torch.int32, device=dev) for _ in range(world)]
     dist.all_gather(parts, buf, group=group)
     return np.concatenate([p[:c].cpu().numpy() for p, c in zip(parts, counts)]).astype(np.int32)
@@ -376,4 +391,4 @@ def run_multi_gpu(neuron: int, batch: int, layer: int, data_dir: str = "../data"
     finally:
         net.close()
     say("[END]...")
-    return gather_categories(local)
+    return gather_categories(local, capacity=(batch + world - 1) // world)
