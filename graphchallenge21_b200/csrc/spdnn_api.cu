@@ -141,6 +141,8 @@ struct spdnn {
                                        // one block per SM cannot hide the latency of its gathers)
     bool bits_prepass = true;          // SPDNN_BITS_KERNEL=0: ALT2 chunks of wide layers run without the pre-pass
     bool bits_first_chunk = false;     // SPDNN_BITS_FIRST=1: also before the first resident chunk of a pass
+    bool bits_small = false;           // SPDNN_BITS_SMALL=1: the pre-pass also for chunks whose layers have at most 64 classes
+                                       // (one warp per 32 images)
     bool table_cache = true;           // SPDNN_TABLE_CACHE=0: the pre-pass always streams its layer records
     int alt2_threads = 0;              // SPDNN_ALT2_THREADS=256|512: block size of ALT2 chunks with 4 images per thread (0: by shared memory)
     int bits_threads = 0;              // SPDNN_BITS_THREADS: threads per block of the pre-pass (0: by the classes)
@@ -596,12 +598,12 @@ std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
                     // before the first two chunks of a pass: the challenge networks saturate around layer 30, and a
                     // tile that is not saturated costs the pre-pass a read of all its rows for nothing.
                     const int rows_max = std::max(rows, maxc);
-                    if (c->bits_prepass && c->bit_form && c->clip > 0.0f && maxc > 64 && rows_max <= 16383 &&
+                    if (c->bits_prepass && c->bit_form && c->clip > 0.0f && (maxc > 64 || c->bits_small) && rows_max <= 16383 &&
                         (alt2_chunks > 1 || c->bits_first_chunk)) {
                         st.wwords = (rows_max + 63) / 64 * 64;
                         const int passes = (maxc + 63) / 64;
                         int nt = c->bits_threads > 0 ? c->bits_threads : 32 * ((passes + 1) / 2);
-                        st.bits_threads = std::max(128, std::min(kBitsMaxThreads, (nt + 31) / 32 * 32));
+                        st.bits_threads = std::max(maxc > 64 ? 128 : 32, std::min(kBitsMaxThreads, (nt + 31) / 32 * 32));
                         // table staging: groups of about 16 KB, four in flight when a group is one layer
                         st.bits_gshift = 0; st.bits_tring = 0;
                         if (c->stage_tables) {
@@ -643,7 +645,7 @@ std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
             if (resident_chunks < (int)c->chunk_list.size()) chunk = c->chunk_list[resident_chunks];
             // a chunk with a bits_kernel pre-pass runs its saturated tiles at a fraction of the float form's cost and
             // dead images cost it nothing: from the first such chunk on the rest of the network is one chunk
-            else if (st.max_classes > 64 && alt2_chunks >= 1 && c->bits_prepass && c->bit_form && c->clip > 0.0f && !c->chunk_growth_set)
+            else if ((st.max_classes > 64 || c->bits_small) && st.max_classes > 0 && alt2_chunks >= 1 && c->bits_prepass && c->bit_form && c->clip > 0.0f && !c->chunk_growth_set)
                 chunk = c->chunk_max;
             else chunk = std::min(chunk * (st.max_classes > 0 ? c->chunk_growth : c->chunk_growth_generic), c->chunk_max);
         }
@@ -1073,6 +1075,7 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
         if (const char *e = getenv("SPDNN_BITS_KERNEL")) c->bits_prepass = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BITS_FIRST")) c->bits_first_chunk = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_TABLE_CACHE")) c->table_cache = atoi(e) != 0;
+        if (const char *e = getenv("SPDNN_BITS_SMALL")) c->bits_small = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_ALT2_THREADS")) c->alt2_threads = atoi(e) == 512 ? 512 : atoi(e) == 256 ? 256 : 0;
         if (const char *e = getenv("SPDNN_BITS_THREADS")) c->bits_threads = std::max(0, std::min(kBitsMaxThreads, atoi(e)));
         if (const char *e = getenv("SPDNN_LAZY_EXPAND")) c->lazy_expand = atoi(e) != 0;

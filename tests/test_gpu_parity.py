@@ -167,7 +167,8 @@ _BIT_FORM_WANT = {}
                                  {"SPDNN_RESIDENT_TI": "8"}, {"SPDNN_STAGE_TABLES": "0"}, {"SPDNN_RESIDENT_IPT": "4"},
                                  {"SPDNN_TABLE_GROUP": "1"}, {"SPDNN_TABLE_GROUP": "2", "SPDNN_TABLE_RING": "2"},
                                  {"SPDNN_ALT2_SMALL_BLOCKS": "0"}, {"SPDNN_WORD_RING": "2"}, {"SPDNN_BITS_FIRST": "1"},
-                                 {"SPDNN_BITS_FIRST": "1", "SPDNN_BITS_THREADS": "1024", "SPDNN_CHUNK_FIRST": "40"}])
+                                 {"SPDNN_BITS_FIRST": "1", "SPDNN_BITS_THREADS": "1024", "SPDNN_CHUNK_FIRST": "40"},
+                                 {"SPDNN_BITS_SMALL": "1"}, {"SPDNN_BITS_SMALL": "1", "SPDNN_BITS_FIRST": "1"}])
 @pytest.mark.parametrize("bias,clip,n,L", [(-0.3, 32.0, 1024, 70), (0.0, 32.0, 1024, 70), (-32.0, 32.0, 1024, 70), (0.01, 32.0, 1024, 70),
                                            (-0.3, 8.0, 1024, 70), (-1.0, 2.5, 1024, 70), (-0.35, 32.0, 4096, 50), (0.0, 16.0, 4096, 50)])
 def test_bit_form_of_saturated_activations(bias, clip, n, L, env, monkeypatch, oracle):  # noqa: E302
