@@ -136,7 +136,6 @@ struct spdnn {
     unsigned char *has_floats = nullptr;
     bool binary_front = true;          // SPDNN_BINARY_FRONT=0: inputs are always converted to float tiles
     bool count_front = true;           // SPDNN_COUNT_FRONT=0: layer 0 of a binary input always gathers per image
-    bool pair_front = true;            // SPDNN_PAIR_FRONT=0: layers 0 and 1 of a binary input are never computed together
     bool fused_front = false;          // SPDNN_FUSED_FRONT=1: where layer 0 is followed by an ALT2 chunk, that chunk computes
                                        // layer 0 of a binary input while it loads (measured slower than the counting kernel:
                                        // one block per SM cannot hide the latency of its gathers)
@@ -671,11 +670,8 @@ std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
 //   kFrontWords   layer 0 runs in the per-layer kernel, whose BITS variant gathers from the words;
 //   kFrontFused   layer 0 is followed by an ALT2 chunk, which computes it from the words while loading
 //                 (the per-layer launch of layer 0 is then the float variant only);
-//   kFrontExpand  the pass starts with a resident chunk: the words are expanded to float tiles first;
-//   kFrontPair    layer 0 (uniform weight, 32 entries per class) is followed by an ALT2 chunk of at least two layers:
-//                 front_pair_kernel computes layers 0 AND 1 from the words (two counts per output and a table), and
-//                 the chunk's binary variant starts at its second layer.
-enum { kFrontNone = 0, kFrontWords = 1, kFrontFused = 2, kFrontExpand = 3, kFrontPair = 4 };
+//   kFrontExpand  the pass starts with a resident chunk: the words are expanded to float tiles first.
+enum { kFrontNone = 0, kFrontWords = 1, kFrontFused = 2, kFrontExpand = 3 };
 
 int enqueue_layers(spdnn *c, const std::vector<Step> &plan, bool gated) {
     c->last_group = 0;
@@ -689,12 +685,6 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan, bool gated) {
                 c->res[1]->mode == kResAlt2 && c->res[0]->mode == kResGeneric && c->res[0]->uniform && c->res[0]->k <= 252 &&
                 c->res[0]->v_in == c->n && c->res[0]->rep == nullptr && c->res[1]->v_in == c->res[0]->classes)
                 front = kFrontFused;
-            else if (c->pair_front && c->count_front && plan.size() > 1 && plan[1].ti != 0 && plan[1].first == 1 && plan[1].count >= 2 &&
-                     c->res[0] && c->res[1] && c->res[1]->mode == kResAlt2 && c->res[0]->mode == kResGeneric && c->res[0]->uniform &&
-                     c->res[0]->k == 32 && c->res[0]->v_in == c->n && c->res[0]->rep == nullptr &&
-                     c->res[1]->v_in == c->res[0]->classes && !c->layer[0]->pinned &&
-                     (size_t)6 * c->res[0]->classes * 4 + (size_t)kFrontPairCounts * kFrontPairCounts * 4 + 2048 <= (size_t)c->smem_optin)
-                front = kFrontPair;
         } else {
             front = kFrontExpand;
             const long long warps = (long long)c->tiles_cap * c->n;
@@ -755,18 +745,6 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan, bool gated) {
                 if (rc) return rc;
                 c->extra_launches += 1;
                 if (c->print_schedule) fprintf(stderr, "[spdnn] step 1, binary inputs: the chunk computes layer 0 from the input words\n");
-                a.gate = c->in_flag; a.gate_want = 1;
-            }
-            if (front == kFrontPair && step == 1) {
-                // binary inputs: layers 0 and 1 were computed by front_pair_kernel; this chunk starts at its second layer
-                ResArgs f = a;
-                f.layers = a.layers + 1; f.died_at = a.died_at + 1; f.nlayers = st.count - 1;
-                f.stream = a.stream ? a.stream + st.stride : nullptr;
-                f.gate = c->in_flag; f.gate_want = 0;
-                int rc = launch_resident(c, st.ti, st.ipt, f, grid, smem, R0.mode, R0.k == 32, R0.uniform);
-                if (rc) return rc;
-                c->extra_launches += 1;
-                if (c->print_schedule) fprintf(stderr, "[spdnn] step 1, binary inputs: the chunk starts at layer %d\n", l + 1);
                 a.gate = c->in_flag; a.gate_want = 1;
             }
             if (alt2 && st.bits_threads > 0) {
@@ -875,27 +853,6 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan, bool gated) {
             const long long ncb = (L.classes + d.classes_per_item - 1) / d.classes_per_item;
             if ((long long)c->tiles_cap * ncb >= 0xffffffffLL) return fail(c, SPDNN_ERR_LIMIT, "batch too large for one launch");
             int grid = c->grid_override > 0 ? c->grid_override : c->sm_count * blocks_per_sm(L.k, L.uniform);
-            if (step == 0 && front == kFrontPair) {
-                FrontPairArgs f;
-                f.xw = c->xw; f.nw = c->nw; f.yout = yout;         // layer 1's output: what step 1 reads
-                f.tile_stride = c->tile_stride;
-                f.ctl_in = c->ctl; f.ctl_out = c->ctl + 1;
-                f.slot = c->slot; f.mask = c->mask; f.ids0 = c->ids[0]; f.ids1 = c->ids[1];
-                f.counter = c->counter; f.work = c->counter + 1; f.status = c->status;
-                f.l0 = c->res_table; f.l1 = c->res_table + 1; f.died_at = c->died_at;
-                f.bias = c->bias; f.clip = c->clip;
-                f.reps_only = c->reps_only ? 1 : 0;                // the chunk's second layer reads one row per class of layer 1
-                f.gate = c->in_flag; f.gate_want = 0;
-                const size_t fsmem = (size_t)6 * c->res[0]->classes * 4 + (size_t)kFrontPairCounts * kFrontPairCounts * 4;
-                if (int rc = allow_max_dynamic_smem(c, front_pair_kernel)) return rc;
-                int bps = 0;
-                if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&bps, front_pair_kernel, 512, fsmem) != cudaSuccess || bps < 1) bps = 1;
-                front_pair_kernel<<<c->sm_count * bps, 512, fsmem, c->stream>>>(f);
-                CK(cudaGetLastError());
-                c->extra_launches += 1;
-                if (c->print_schedule) fprintf(stderr, "[spdnn] step 0, binary inputs: layers 0 and 1 from the input words (two counts per output)\n");
-                a.gate = c->in_flag; a.gate_want = 1;
-            }
             if (step == 0 && (front == kFrontWords || front == kFrontFused)) {
                 if (front == kFrontWords) {
                     LayerArgs w = a;           // binary inputs: gather from the words
@@ -1115,7 +1072,6 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
         if (const char *e = getenv("SPDNN_BINARY_FRONT")) c->binary_front = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_FUSED_FRONT")) c->fused_front = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_COUNT_FRONT")) c->count_front = atoi(e) != 0;
-        if (const char *e = getenv("SPDNN_PAIR_FRONT")) c->pair_front = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BITS_KERNEL")) c->bits_prepass = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BITS_FIRST")) c->bits_first_chunk = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_TABLE_CACHE")) c->table_cache = atoi(e) != 0;

@@ -17,7 +17,6 @@
 #pragma once
 
 #include "spdnn_kernels.cuh"
-#include "spdnn_resident.cuh"
 
 namespace spdnn_impl {
 
@@ -246,180 +245,6 @@ static __global__ void __launch_bounds__(kThreads, 4) front_count_kernel(const L
     if (!s_last) return;
     __threadfence();
     rebuild_worklist(a, live_in, ctl.ids_buf);
-}
-
-// ---- layers 0 AND 1 of a binary input ---------------------------------------------------------------------
-//
-// Where layer 0 (uniform weight, 32 entries per class, tables over the neurons) is followed by a layer in the
-// alternating-pair form over layer 0's classes, the output of layer 1 for an image is a function of TWO counts:
-// its inputs a and b are layer-0 outputs, each determined by the count of set bits among that class's 32 input
-// neurons.  The kernel tabulates that function once per block with the float form's own instructions -- the 33
-// possible layer-0 outputs (count * w + bias, clamp), then for every pair the K-term sum a+b+a+b+... , bias, clamp
-// -- and then, per tile of 32 images: (A) a lane per layer-0 class gathers the class's 32 row words and adds them
-// with the carry-save tree into six bit planes, kept in shared memory; (B) a warp per layer-1 class, lane = image,
-// rebuilds the image's two counts from the planes and stores table[count a][count b].  Layer 1 then costs a
-// dozen shared-memory reads per class and 32 images instead of 32 dependent adds per class and image.
-// Same launch protocol as layer_kernel (work items, ballots, last-block rebuild); deaths are counted for both layers.
-struct FrontPairArgs {
-    const uint32_t *xw;            // the input's words, nw per tile
-    int nw;
-    float *yout;
-    long long tile_stride;
-    const LoopCtl *ctl_in;
-    LoopCtl *ctl_out;
-    int32_t *slot;
-    uint32_t *mask;
-    int32_t *ids0, *ids1;
-    unsigned int *counter, *work;
-    int32_t *status;
-    const ResLayer *l0;            // GENERIC tables over the neurons, uniform weight, k == 32
-    const ResLayer *l1;            // ALT2 tables over l0's classes
-    int32_t *died_at;              // [0]: layer 0, [1]: layer 1
-    float bias, clip;
-    int reps_only;                 // 1: store one row per layer-1 class (its first member), else all member rows
-    const int32_t *gate;
-    int gate_want;
-};
-
-constexpr int kFrontPairCounts = 33;          // counts 0 .. 32
-
-// Dynamic shared memory: six planes of l0.classes words, then the 33 x 33 table.
-static __global__ void __launch_bounds__(512, 1) front_pair_kernel(const FrontPairArgs a) {
-    extern __shared__ __align__(16) unsigned char fsm[];
-    __shared__ unsigned int s_item, s_alive0, s_any1;
-    __shared__ int s_last;
-    if (a.gate != nullptr && *a.gate != a.gate_want) return;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
-    const ResLayer L0 = *a.l0, L1 = *a.l1;
-    const int u0n = L0.classes, u1n = L1.classes;
-    unsigned int *pl = reinterpret_cast<unsigned int *>(fsm);                 // pl[p * u0n + class]
-    float *lut = reinterpret_cast<float *>(fsm + (size_t)6 * u0n * 4);        // lut[count a * 33 + count b]
-    const LoopCtl ctl = *a.ctl_in;                                           // first launch of a pass: image j sits at position j
-    const int live_in = ctl.live;
-    const int ntiles = (live_in + 31) >> 5;
-    // the table, with the float form's own instructions
-    for (int q = tid; q < kFrontPairCounts * kFrontPairCounts; q += blockDim.x) {
-        const int ca = q / kFrontPairCounts, cb = q - ca * kFrontPairCounts;
-        const float va = relu_clip(__fadd_rn(__fmul_rn((float)ca, L0.w), a.bias), a.clip);
-        const float vb = relu_clip(__fadd_rn(__fmul_rn((float)cb, L0.w), a.bias), a.clip);
-        const float4 sum = class_sum_alt2<0>(make_float4(va, va, va, va), make_float4(vb, vb, vb, vb), L1.k, L1.w, false);
-        lut[q] = finish_output(sum.x, a.bias, a.clip);
-    }
-    // smallest count whose layer-0 output is not zero (33: none)
-    int thr0 = kFrontPairCounts;
-    for (int cnt = kFrontPairCounts - 1; cnt >= 0; --cnt)
-        if (relu_clip(__fadd_rn(__fmul_rn((float)cnt, L0.w), a.bias), a.clip) != 0.0f) thr0 = cnt;
-    const int kp = L0.k + 4;
-    for (;;) {
-        __syncthreads();                               // the table is written; the last tile's planes are no longer read
-        if (tid == 0) {
-            s_item = atomicAdd(a.work, 1u);
-            s_alive0 = 0u;
-            s_any1 = 0u;
-        }
-        __syncthreads();
-        const int tile = (int)s_item;
-        if (tile >= ntiles) break;
-        const uint32_t *__restrict__ xw = a.xw + (size_t)tile * a.nw;
-        const unsigned int valid = __ballot_sync(0xffffffffu, tile * 32 + lane < live_in);
-        // ---- (A) bit-sliced counts of every layer-0 class
-        unsigned int nz0 = 0u;
-        for (int u0 = warp * 32; u0 < u0n; u0 += nwarps * 32) {
-            const int u = u0 + lane;
-            const bool in = u < u0n;
-            const int4 *rows = reinterpret_cast<const int4 *>(L0.blob + 4 + (size_t)(in ? u : u0) * kp);
-            unsigned int p[6] = {0u, 0u, 0u, 0u, 0u, 0u};
-            unsigned int s16[2];
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                unsigned int e8[2];
-#pragma unroll
-                for (int quarter = 0; quarter < 2; ++quarter) {
-                    const int4 r0 = __ldg(rows + half * 4 + quarter * 2), r1 = __ldg(rows + half * 4 + quarter * 2 + 1);
-                    // the table names rows of a permuted buffer; the permutation is an involution
-                    const unsigned int w0 = __ldg(xw + resident_phys_row(r0.x)), w1 = __ldg(xw + resident_phys_row(r0.y)),
-                                       w2 = __ldg(xw + resident_phys_row(r0.z)), w3 = __ldg(xw + resident_phys_row(r0.w)),
-                                       w4 = __ldg(xw + resident_phys_row(r1.x)), w5 = __ldg(xw + resident_phys_row(r1.y)),
-                                       w6 = __ldg(xw + resident_phys_row(r1.z)), w7 = __ldg(xw + resident_phys_row(r1.w));
-                    unsigned int t2a, t2b, f4a, f4b;
-                    front_csa(t2a, p[0], p[0], w0, w1);
-                    front_csa(t2b, p[0], p[0], w2, w3);
-                    front_csa(f4a, p[1], p[1], t2a, t2b);
-                    front_csa(t2a, p[0], p[0], w4, w5);
-                    front_csa(t2b, p[0], p[0], w6, w7);
-                    front_csa(f4b, p[1], p[1], t2a, t2b);
-                    front_csa(e8[quarter], p[2], p[2], f4a, f4b);
-                }
-                front_csa(s16[half], p[3], p[3], e8[0], e8[1]);
-            }
-            front_csa(p[5], p[4], p[4], s16[0], s16[1]);
-            if (in) {
-#pragma unroll
-                for (int q = 0; q < 6; ++q) pl[q * u0n + u] = p[q];
-                // images whose count reaches thr0: a non-zero output of layer 0
-                unsigned int gt = 0u, eq = 0xffffffffu;
-#pragma unroll
-                for (int q = 5; q >= 0; --q) {
-                    if ((thr0 >> q) & 1) eq &= p[q];
-                    else { gt |= eq & p[q]; eq &= ~p[q]; }
-                }
-                nz0 |= (thr0 > 32) ? 0u : (gt | eq);
-            }
-        }
-        nz0 = __reduce_or_sync(0xffffffffu, nz0);
-        if (lane == 0 && nz0) atomicOr(&s_alive0, nz0);
-        __syncthreads();
-        const unsigned int alive0 = s_alive0 & valid;
-        // ---- (B) layer 1: a warp per class, lane = image
-        float *__restrict__ yout = a.yout + (size_t)tile * a.tile_stride + lane;
-        bool any = false;
-        for (int u1 = warp; u1 < u1n; u1 += nwarps) {
-            const int2 ab = __ldg(reinterpret_cast<const int2 *>(L1.blob + 4 + (size_t)u1 * 4));
-            const int ra = resident_phys_row(ab.x), rb = resident_phys_row(ab.y);
-            unsigned int ca = 0u, cb = 0u;
-#pragma unroll
-            for (int q = 0; q < 6; ++q) {
-                ca |= ((pl[q * u0n + ra] >> lane) & 1u) << q;
-                cb |= ((pl[q * u0n + rb] >> lane) & 1u) << q;
-            }
-            const float y = lut[ca * kFrontPairCounts + cb];
-            any |= (y != 0.0f);
-            if (L1.mem_ptr == nullptr) {
-                yout[(size_t)u1 * 32] = y;
-            } else {
-                const int mb = __ldg(L1.mem_ptr + u1), me = a.reps_only ? mb + 1 : __ldg(L1.mem_ptr + u1 + 1);
-                for (int m = mb; m < me; ++m) yout[__ldg(L1.mem + m)] = y;
-            }
-        }
-        const unsigned int any1 = __ballot_sync(0xffffffffu, any);
-        if (lane == 0 && any1) atomicOr(&s_any1, any1);
-        __syncthreads();
-        if (tid == 0) {
-            // an image without a non-zero output after layer 0 is dead and stays dead
-            const unsigned int alive1 = s_any1 & alive0;
-            const int d0 = __popc(valid & ~alive0), d1 = __popc(alive0 & ~alive1);
-            if (d0) atomicAdd(a.died_at, d0);
-            if (d1) atomicAdd(a.died_at + 1, d1);
-            if (alive1) atomicOr(a.mask + tile, alive1);
-        }
-    }
-    if (tid == 0) {
-        __threadfence();
-        const unsigned int t = atomicAdd(a.counter, 1u);
-        s_last = (t == gridDim.x - 1);
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    LayerArgs la;
-    la.yin = nullptr; la.yout = a.yout; la.tile_stride = a.tile_stride;
-    la.ctl_in = a.ctl_in; la.ctl_out = a.ctl_out; la.slot = a.slot; la.mask = a.mask;
-    la.ids0 = a.ids0; la.ids1 = a.ids1; la.counter = a.counter; la.work = a.work; la.status = a.status;
-    la.died_at = nullptr;
-    la.first_member_only = 0;
-    la.bias = a.bias; la.clip = a.clip;
-    la.xw = nullptr; la.nw = 0; la.gate = nullptr; la.gate_want = 0;
-    rebuild_worklist(la, live_in, ctl.ids_buf);
 }
 
 }  // namespace spdnn_impl
