@@ -137,8 +137,6 @@ alt2_kernel(const ResArgs a) {
     __shared__ int s_last, s_fail;
     __shared__ int s_next_group;                 // the next group of tables to request (used by one thread at a time)
     __shared__ __align__(8) unsigned long long s_bar[kAlt2MaxTableRing];
-    __shared__ float s_front[256];               // front layer: output for every count of ones among its K inputs
-    __shared__ unsigned int s_front_alive;
     if (a.gate != nullptr && *a.gate != a.gate_want) return;
     constexpr int NQ = IPT / 4;                  // float4 halves per thread
     constexpr int LPC = TI / IPT;                // threads per class
@@ -194,15 +192,12 @@ alt2_kernel(const ResArgs a) {
             return STAGED ? tbl0 + (size_t)((l >> gshift) & (tring - 1)) * group_bytes + (size_t)(l & gmask) * stride
                           : a.stream + (size_t)l * stride;
         };
-        const bool front = a.front_words != nullptr;
-        if (front && blockIdx.x == 0 && tid == 0) *a.front_ctl_copy = ctl;
         if (tid == 0) {
             s_next_group = 0;
             s_alive[0] = 0u;
             s_ns[0] = 0;
             s_grp[0][0] = s_grp[0][1] = s_grp[1][0] = s_grp[1][1] = 0u;
             s_fail = 0;
-            s_front_alive = 0u;
             if (STAGED) {
                 for (int q = 0; q < tring; ++q) mbar_init(&s_bar[q], 1);
                 asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -229,58 +224,9 @@ alt2_kernel(const ResArgs a) {
             }
             if (my_valid != kFull) contiguous = false;
             const ResLayer L0 = a.layers[0];
-            if (front) {
-                // The layer before the chunk, from the bit matrix of a binary input.  Its K-term sum of zeros and
-                // ones, added in ascending order, is the count of ones (every partial sum an integer, exact in
-                // fp32), so the output is s_front[count], tabulated with the float form's own instructions.  A
-                // thread counts for its IPT images at once: the images' bits of a word, spread to one byte each
-                // (the multiplication moves bit q to bit 8 q), are added byte-wise.
-                const ResLayer F = *a.front_layer;
-                for (int cnt = tid; cnt < 256; cnt += NT) s_front[cnt] = finish_output(__fmul_rn((float)cnt, F.w), a.bias, a.clip);
-                __syncthreads();
-                const uint32_t *__restrict__ xw = a.front_words + (size_t)(j0 >> 5) * a.front_nw;
-                const int shift = (j0 & 31) + sub * IPT;
-                const int kp = F.k + 4;
-                unsigned int nz = 0u;
-                for (int v = grp; v < F.classes; v += CPI) {
-                    const int4 *rows = reinterpret_cast<const int4 *>(F.blob + 4 + (size_t)v * kp);
-                    unsigned int acc[NQ];
-#pragma unroll
-                    for (int h = 0; h < NQ; ++h) acc[h] = 0u;
-                    for (int i = 0; i < F.k / 4; ++i) {
-                        const int4 t = __ldg(rows + i);
-                        // the table names rows of a permuted buffer; the permutation is an involution
-                        const unsigned int w0 = __ldg(xw + resident_phys_row(t.x)) >> shift, w1 = __ldg(xw + resident_phys_row(t.y)) >> shift;
-                        const unsigned int w2 = __ldg(xw + resident_phys_row(t.z)) >> shift, w3 = __ldg(xw + resident_phys_row(t.w)) >> shift;
-#pragma unroll
-                        for (int h = 0; h < NQ; ++h) {
-                            acc[h] += (((w0 >> (4 * h)) & 0xfu) * 0x00204081u) & 0x01010101u;
-                            acc[h] += (((w1 >> (4 * h)) & 0xfu) * 0x00204081u) & 0x01010101u;
-                            acc[h] += (((w2 >> (4 * h)) & 0xfu) * 0x00204081u) & 0x01010101u;
-                            acc[h] += (((w3 >> (4 * h)) & 0xfu) * 0x00204081u) & 0x01010101u;
-                        }
-                    }
-                    unsigned char *dst = cur + alt2_row_pos<TI>(v) * RS + sub * TB;
-#pragma unroll
-                    for (int h = 0; h < NQ; ++h) {
-                        const unsigned int ok = my_valid >> (4 * h);
-                        float4 x;
-                        x.x = (ok & 1u) ? s_front[acc[h] & 0xffu] : 0.0f;
-                        x.y = (ok & 2u) ? s_front[(acc[h] >> 8) & 0xffu] : 0.0f;
-                        x.z = (ok & 4u) ? s_front[(acc[h] >> 16) & 0xffu] : 0.0f;
-                        x.w = (ok & 8u) ? s_front[acc[h] >> 24] : 0.0f;
-                        *reinterpret_cast<float4 *>(dst + 16 * h) = x;
-                        nz |= ((x.x != 0.0f ? 1u : 0u) | (x.y != 0.0f ? 2u : 0u) | (x.z != 0.0f ? 4u : 0u) | (x.w != 0.0f ? 8u : 0u)) << (4 * h);
-                        load_ns |= (x.x != 0.0f && x.x != a.clip) || (x.y != 0.0f && x.y != a.clip) || (x.z != 0.0f && x.z != a.clip) ||
-                                   (x.w != 0.0f && x.w != a.clip);
-                    }
-                }
-                const unsigned int wm = __reduce_or_sync(0xffffffffu, nz << (sub * IPT));
-                if (lane == 0 && wm) atomicOr(&s_front_alive, wm);
-            }
-            const bool fast_dense = !front && dense && !L0.rep && L0.v_in == a.n && (a.n & 3) == 0 && (reinterpret_cast<size_t>(dense) & 15) == 0;
+            const bool fast_dense = dense && !L0.rep && L0.v_in == a.n && (a.n & 3) == 0 && (reinterpret_cast<size_t>(dense) & 15) == 0;
             if (fast_dense) load_ns |= load_dense_rows<TI, NT, true, TI != 32>(dense, a.n, j0, live_in, L0.v_in, cur, a.clip);
-            for (int v = grp; v < L0.v_in && !fast_dense && !front; v += CPI) {
+            for (int v = grp; v < L0.v_in && !fast_dense; v += CPI) {
                 // element of row r: r * 32 floats into a tile's column, r floats into a row-major image
                 size_t e = L0.rep ? (size_t)__ldg(L0.rep + v) : (size_t)v * 32;
                 if (dense) e >>= 5;
@@ -306,12 +252,6 @@ alt2_kernel(const ResArgs a) {
         // mask of valid images (bit i = image j0 + i), identical in every thread
         unsigned int alive_prev = __reduce_or_sync(0xffffffffu, my_valid << (sub * IPT));
         const bool start_in_bits = !__syncthreads_or(load_ns ? 1 : 0) && use_bits;
-        if (front) {
-            // who survived the front layer (the barrier above ordered the atomics before this read)
-            const unsigned int alive_now = alive_prev & s_front_alive;
-            if (tid == 0 && alive_now != alive_prev) atomicAdd(a.front_died_at, __popc(alive_prev & ~alive_now));
-            alive_prev = alive_now;
-        }
 
         // float rows -> one word per row (bit i = image i is non-zero; called when every value is 0 or clip)
         auto rows_to_bits = [&](const unsigned char *buf, unsigned int *w) {
@@ -349,7 +289,7 @@ alt2_kernel(const ResArgs a) {
             __syncthreads();
             bitmode = true;
         }
-        while (li < a.nlayers && alive_prev != 0u) {
+        while (li < a.nlayers) {
             if (bitmode) {
                 // ---- bit form.  Worker warps (one warp when a layer is one pass of 64 classes, else
                 //      all warps) apply groups of layers until the chunk ends, every image is dead, or a

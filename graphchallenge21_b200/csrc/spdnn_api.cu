@@ -136,9 +136,6 @@ struct spdnn {
     unsigned char *has_floats = nullptr;
     bool binary_front = true;          // SPDNN_BINARY_FRONT=0: inputs are always converted to float tiles
     bool count_front = true;           // SPDNN_COUNT_FRONT=0: layer 0 of a binary input always gathers per image
-    bool fused_front = false;          // SPDNN_FUSED_FRONT=1: where layer 0 is followed by an ALT2 chunk, that chunk computes
-                                       // layer 0 of a binary input while it loads (measured slower than the counting kernel:
-                                       // one block per SM cannot hide the latency of its gathers)
     bool bits_prepass = true;          // SPDNN_BITS_KERNEL=0: ALT2 chunks of wide layers run without the pre-pass
     bool bits_first_chunk = false;     // SPDNN_BITS_FIRST=1: also before the first resident chunk of a pass
     bool bits_small = false;           // SPDNN_BITS_SMALL=1: the pre-pass also for chunks whose layers have at most 64 classes
@@ -668,10 +665,8 @@ std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
 // layer then exist twice, one variant per value of the flag that the input conversion leaves on the device
 // (0: binary, read the words; 1: read the float tiles), and each checks the flag at entry:
 //   kFrontWords   layer 0 runs in the per-layer kernel, whose BITS variant gathers from the words;
-//   kFrontFused   layer 0 is followed by an ALT2 chunk, which computes it from the words while loading
-//                 (the per-layer launch of layer 0 is then the float variant only);
 //   kFrontExpand  the pass starts with a resident chunk: the words are expanded to float tiles first.
-enum { kFrontNone = 0, kFrontWords = 1, kFrontFused = 2, kFrontExpand = 3 };
+enum { kFrontNone = 0, kFrontWords = 1, kFrontExpand = 3 };
 
 int enqueue_layers(spdnn *c, const std::vector<Step> &plan, bool gated) {
     c->last_group = 0;
@@ -681,10 +676,6 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan, bool gated) {
     if (gated) {
         if (plan[0].ti == 0) {
             front = kFrontWords;
-            if (c->fused_front && plan.size() > 1 && plan[1].ti != 0 && plan[1].first == 1 && c->res[0] && c->res[1] &&
-                c->res[1]->mode == kResAlt2 && c->res[0]->mode == kResGeneric && c->res[0]->uniform && c->res[0]->k <= 252 &&
-                c->res[0]->v_in == c->n && c->res[0]->rep == nullptr && c->res[1]->v_in == c->res[0]->classes)
-                front = kFrontFused;
         } else {
             front = kFrontExpand;
             const long long warps = (long long)c->tiles_cap * c->n;
@@ -732,21 +723,7 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan, bool gated) {
             a.bit_ok = (alt2 && c->bit_form && c->clip > 0.0f && st.wring >= 2) ? 1 : 0;
             a.tile_done = nullptr; a.wwords = 0;
             a.cache = nullptr; a.rec_of = nullptr; a.cache_records = 0;
-            a.front_words = nullptr; a.front_nw = 0; a.front_layer = nullptr; a.front_died_at = nullptr; a.front_ctl_copy = nullptr;
             a.gate = nullptr; a.gate_want = 0;
-            if (front == kFrontFused && step == 1) {
-                // binary inputs: this chunk computes layer 0 from the words while it loads; it starts from the
-                // state before layer 0 and stands for steps 0 and 1
-                ResArgs f = a;
-                f.ctl_in = c->ctl; f.front_ctl_copy = c->ctl + 1;
-                f.front_words = c->xw; f.front_nw = c->nw; f.front_layer = c->res_table; f.front_died_at = c->died_at;
-                f.gate = c->in_flag; f.gate_want = 0;
-                int rc = launch_resident(c, st.ti, st.ipt, f, grid, smem, R0.mode, R0.k == 32, R0.uniform);
-                if (rc) return rc;
-                c->extra_launches += 1;
-                if (c->print_schedule) fprintf(stderr, "[spdnn] step 1, binary inputs: the chunk computes layer 0 from the input words\n");
-                a.gate = c->in_flag; a.gate_want = 1;
-            }
             if (alt2 && st.bits_threads > 0) {
                 // pre-pass: tiles of 32 images that are saturated already run the whole chunk as words
                 ResArgs b = a;                 // (gated like the launch it prepares)
@@ -853,8 +830,8 @@ int enqueue_layers(spdnn *c, const std::vector<Step> &plan, bool gated) {
             const long long ncb = (L.classes + d.classes_per_item - 1) / d.classes_per_item;
             if ((long long)c->tiles_cap * ncb >= 0xffffffffLL) return fail(c, SPDNN_ERR_LIMIT, "batch too large for one launch");
             int grid = c->grid_override > 0 ? c->grid_override : c->sm_count * blocks_per_sm(L.k, L.uniform);
-            if (step == 0 && (front == kFrontWords || front == kFrontFused)) {
-                if (front == kFrontWords) {
+            if (step == 0 && front == kFrontWords) {
+                {
                     LayerArgs w = a;           // binary inputs: gather from the words
                     w.xw = c->xw; w.nw = c->nw; w.gate = c->in_flag; w.gate_want = 0;
                     const bool by_count = L.uniform && L.k == 32 && c->count_front;
@@ -1070,7 +1047,6 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
         if (const char *e = getenv("SPDNN_BIT_FORM")) c->bit_form = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_STAGE_KB")) c->stage_chunk = (size_t)std::max(1, atoi(e)) << 10;
         if (const char *e = getenv("SPDNN_BINARY_FRONT")) c->binary_front = atoi(e) != 0;
-        if (const char *e = getenv("SPDNN_FUSED_FRONT")) c->fused_front = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_COUNT_FRONT")) c->count_front = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BITS_KERNEL")) c->bits_prepass = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BITS_FIRST")) c->bits_first_chunk = atoi(e) != 0;

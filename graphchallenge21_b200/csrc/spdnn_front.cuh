@@ -6,10 +6,10 @@
 // has neuron r set.  That is N/8 bytes per image instead of 4 N, and layer 0 reads it directly:
 //   * the per-layer kernel takes a gathered input as ((word >> lane) & 1) ? 1.0f : 0.0f, one
 //     broadcast 4-byte load per gather instead of a 128-byte row;
-//   * the first ALT2 chunk computes layer 0 while it loads (alt2_kernel, "front"): with a uniform
-//     weight w the K-term sum of zeros and ones in ascending order is the COUNT of ones, every
-//     partial sum an integer and therefore exact in fp32, so the output is a function of the count
-//     that is tabulated with the float path's own instructions.
+//   * with a uniform weight w and 32 entries per class, front_count_kernel computes layer 0 for 32 images
+//     at once: the K-term sum of zeros and ones in ascending order is the COUNT of ones, every partial
+//     sum an integer and therefore exact in fp32, so the output is count * w + bias, clamped, computed
+//     with the float path's own instructions from a bit-sliced count.
 // Inputs that turn out not to be binary (a value other than 0 and 1) raise a flag on the device while
 // they are converted; the launches of the first layer exist in both variants and each checks the
 // flag at entry (`gate`), so no host round-trip decides.  For those inputs the float tiles are built

@@ -101,14 +101,6 @@ struct ResArgs {
     const unsigned char *cache;
     const unsigned short *rec_of;
     int cache_records;
-    // First chunk of a pass on a binary input (spdnn_front.cuh): alt2_kernel computes the layer BEFORE the chunk
-    // (front_layer: GENERIC tables over the neurons, uniform weight, K <= 252) from the input's bit matrix while it
-    // loads, instead of reading that layer's output from yin.  nullptr = the chunk's input is in yin.
-    const uint32_t *front_words;
-    int front_nw;             // words per tile of the bit matrix
-    const ResLayer *front_layer;
-    int32_t *front_died_at;   // where the images that die in the front layer are counted
-    LoopCtl *front_ctl_copy;  // the record between the front layer and the chunk, which no launch writes in this variant
     // the launch runs only when *gate == gate_want (nullptr: always), see LayerArgs
     const int32_t *gate;
     int gate_want;

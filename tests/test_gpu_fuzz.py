@@ -19,7 +19,7 @@ SWITCHES = [{}, {"SPDNN_RESIDENT_TI": "16"}, {"SPDNN_RESIDENT_TI": "8"}, {"SPDNN
             {"SPDNN_ALT2_SMALL_BLOCKS": "0"}, {"SPDNN_CHUNK_MAX": "5"}, {"SPDNN_LAZY_EXPAND": "0"}, {"SPDNN_DENSE_DIRECT": "1"},
             {"SPDNN_RESIDENT_TI": "4"}, {"SPDNN_WORD_RING": "2"}, {"SPDNN_BITS_KERNEL": "0"},
             {"SPDNN_BITS_FIRST": "1"}, {"SPDNN_BITS_FIRST": "1", "SPDNN_CHUNK_FIRST": "2"}, {"SPDNN_BITS_FIRST": "1", "SPDNN_BITS_THREADS": "256"},
-            {"SPDNN_BINARY_FRONT": "0"}, {"SPDNN_FUSED_FRONT": "1"}, {"SPDNN_RESIDENT": "0"},
+            {"SPDNN_BINARY_FRONT": "0"}, {"SPDNN_RESIDENT": "0"},
             {"SPDNN_BITS_FIRST": "1", "SPDNN_TABLE_CACHE": "0"}, {"SPDNN_COUNT_FRONT": "0"},
             {"SPDNN_BITS_SMALL": "1"}, {"SPDNN_BITS_SMALL": "1", "SPDNN_BITS_FIRST": "1"}]
 

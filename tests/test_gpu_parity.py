@@ -85,8 +85,8 @@ def test_against_oracle(pattern, n, L, b, oracle):
                                  {"SPDNN_STAGE_TABLES": "0"}, {"SPDNN_EXACT_SHORTCUT": "0"}, {"SPDNN_RESIDENT_IPT": "4"},
                                  {"SPDNN_BIT_FORM": "0"}, {"SPDNN_DENSE_DIRECT": "1"}, {"SPDNN_LAZY_EXPAND": "0"},
                                  {"SPDNN_RESIDENT_TI": "16"}, {"SPDNN_REPS_ONLY": "0"}, {"SPDNN_BINARY_FRONT": "0"},
-                                 {"SPDNN_FUSED_FRONT": "1"}, {"SPDNN_RESIDENT": "2"}, {"SPDNN_COUNT_FRONT": "0"},
-                                 {"SPDNN_FUSED_FRONT": "1", "SPDNN_RESIDENT_TI": "16"}, {"SPDNN_RESIDENT": "0", "SPDNN_COUNT_FRONT": "0"}])
+                                 {"SPDNN_RESIDENT": "2"}, {"SPDNN_COUNT_FRONT": "0"},
+                                 {"SPDNN_RESIDENT": "0", "SPDNN_COUNT_FRONT": "0"}])
 def test_kernel_paths_agree(env, monkeypatch, oracle):
     """The per-layer kernel, and the shared-memory-resident kernel at every group size and chunk
     schedule, give the same bits as the oracle."""
@@ -213,7 +213,7 @@ def _large_case(oracle, bias, clip, n, L, b):
                                  {"SPDNN_BITS_KERNEL": "0"}, {"SPDNN_BITS_FIRST": "1"}, {"SPDNN_BITS_FIRST": "1", "SPDNN_BITS_THREADS": "128"},
                                  {"SPDNN_BITS_FIRST": "1", "SPDNN_STAGE_TABLES": "0"}, {"SPDNN_BITS_FIRST": "1", "SPDNN_TABLE_GROUP": "1", "SPDNN_TABLE_RING": "2"},
                                  {"SPDNN_BITS_FIRST": "1", "SPDNN_CHUNK_FIRST": "1", "SPDNN_CHUNK_MAX": "3"},
-                                 {"SPDNN_BITS_FIRST": "1", "SPDNN_TABLE_CACHE": "0"}, {"SPDNN_FUSED_FRONT": "1"},
+                                 {"SPDNN_BITS_FIRST": "1", "SPDNN_TABLE_CACHE": "0"},
                                  {"SPDNN_COUNT_FRONT": "0"}, {"SPDNN_ALT2_THREADS": "256"},
                                  {"SPDNN_ALT2_THREADS": "256", "SPDNN_RESIDENT_TI": "8", "SPDNN_BITS_KERNEL": "0"}],
                          ids=lambda e: ",".join(f"{k[6:]}={v}" for k, v in e.items()) or "default")
