@@ -202,3 +202,23 @@ def test_multi_rank_sharding_and_gather_gloo(tmp_path, oracle):
     for r in range(2):
         assert np.array_equal(np.load(tmp_path / f"cats{r}.npy"), want)
     assert 0 < len(want) < batch
+
+
+def test_bit_matrix_layout_of_binary_inputs():
+    """pack_bits: bit (n & 7) of byte n >> 3 of row i = neuron n of image i, rows padded to whole 32-bit words
+    (what spdnn_set_input_bits documents)."""
+    rng = np.random.default_rng(3)
+    for n in (1024, 72, 33):
+        y = (rng.random((5, n)) < 0.3).astype(np.float32) * np.float32(2.5)       # any non-zero value counts as set
+        bits = network.pack_bits(y)
+        assert bits.dtype == np.uint8 and bits.shape == (5, (n + 31) // 32 * 4)
+        back = np.unpackbits(bits, axis=1, bitorder="little")[:, :n]
+        assert np.array_equal(back, (y != 0).astype(np.uint8))
+        assert not np.unpackbits(bits, axis=1, bitorder="little")[:, n:].any()
+
+
+def test_image_generator_does_not_depend_on_its_thread_count():
+    a = synthetic_images(4096, 300, first_image=17)
+    b = synthetic_images(4096, 300, first_image=17, threads=4)
+    assert np.array_equal(a, b)
+    assert np.array_equal(synthetic_images(4096, 10, first_image=27), a[10:20])
