@@ -104,7 +104,8 @@ struct spdnn {
     ResLayer *res_table = nullptr;     // [layers] tables of the resident kernel
     bool resident = true;              // use the shared-memory-resident kernel where a chunk fits
     bool reps_only = true;             // SPDNN_REPS_ONLY=0: every launch writes all N rows
-    bool exact_shortcut = true;        // SPDNN_EXACT_SHORTCUT=0 disables the exact-sum shortcut of the ALT2 form
+    bool exact_shortcut = false;       // SPDNN_EXACT_SHORTCUT=1: exact-sum shortcut of the ALT2 float form (off: saturated tiles leave the
+                                       // float form anyway, and elsewhere its test costs more than it saves -- measured)
     bool bit_form = true;              // SPDNN_BIT_FORM=0 disables the bit form of saturated activations (ALT2)
     int table_ring_max = 2;            // SPDNN_TABLE_RING=2|4: most staged groups of ALT2 tables in flight or in use
     int word_ring_max = 33;            // SPDNN_WORD_RING: most word buffers of the bit form (layers per group + 1)

@@ -250,8 +250,10 @@ __device__ __forceinline__ float4 class_sum_generic(const int32_t *rows, const f
 // all of a and b are multiples of 1/16 -- which (x + M) - M == x tests for M = 1.5 * 2^19,
 // whose ulp is 2^-4 -- every partial sum of a+b+a+b+... is a multiple of 1/16 below 2^15 and so
 // exactly representable in fp32: each of the 32 adds is exact and the sequential sum EQUALS
-// 16 (a + b), which is computed directly.  Saturated networks (activations 0 or 32, the steady
-// state of the challenge networks) take this path in every layer; the result bits are the same.
+// 16 (a + b), which is computed directly; the result bits are the same.  Off unless SPDNN_EXACT_SHORTCUT=1:
+// saturated tiles (activations 0 or 32, the steady state of the challenge networks) run in the bit form,
+// and on the layers before that state the test of eight inputs costs more than the few classes that pass
+// it save (measured on all four challenge sizes).
 template <int KT>
 __device__ __forceinline__ float4 class_sum_alt2(const float4 a, const float4 b, int k, float w, bool exact_ok, bool *took = nullptr) {
     const Acc4 pa = acc_from(a), pb = acc_from(b);

@@ -82,7 +82,7 @@ def test_against_oracle(pattern, n, L, b, oracle):
 
 @pytest.mark.parametrize("env", [{"SPDNN_RESIDENT": "0"}, {"SPDNN_RESIDENT_TI": "8"}, {"SPDNN_RESIDENT_TI": "4"},
                                  {"SPDNN_CHUNK_FIRST": "1", "SPDNN_CHUNK_MAX": "3"}, {"SPDNN_CHUNK_FIRST": "64"},
-                                 {"SPDNN_STAGE_TABLES": "0"}, {"SPDNN_EXACT_SHORTCUT": "0"}, {"SPDNN_RESIDENT_IPT": "4"},
+                                 {"SPDNN_STAGE_TABLES": "0"}, {"SPDNN_EXACT_SHORTCUT": "1"}, {"SPDNN_RESIDENT_IPT": "4"},
                                  {"SPDNN_BIT_FORM": "0"}, {"SPDNN_DENSE_DIRECT": "1"}, {"SPDNN_LAZY_EXPAND": "0"},
                                  {"SPDNN_RESIDENT_TI": "16"}, {"SPDNN_REPS_ONLY": "0"}, {"SPDNN_BINARY_FRONT": "0"},
                                  {"SPDNN_RESIDENT": "2"}, {"SPDNN_COUNT_FRONT": "0"},
