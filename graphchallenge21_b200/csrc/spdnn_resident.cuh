@@ -358,7 +358,6 @@ resident_kernel(const ResArgs a) {
     constexpr int CPI = NT / LPC;                // classes per pass of the block
     constexpr int RS = TI * 4;                   // bytes per row
     constexpr int TB = IPT * 4;                  // bytes of a row one thread owns
-    constexpr unsigned int kFull = (IPT == 8) ? 0xFFu : 0xFu;
     const int tid = threadIdx.x, lane = tid & 31;
     const int sub = tid % LPC, grp = tid / LPC;
     const LoopCtl ctl = *a.ctl_in;
@@ -384,42 +383,42 @@ resident_kernel(const ResArgs a) {
         }
         // ---- load one row per value id of the block's images (dead images were dropped: read
         //      through the work list)
-        unsigned int my_valid = 0;
+        unsigned int my_valid;
         {
-            const float *p[IPT];
+            // Thread -> (image, row): the lanes of a warp that share a row read the TI images of the block, which lie
+            // side by side in a tile unless images died in between; a thread has one source image and up to UNR
+            // scalar loads in flight (a block that has an SM to itself cannot hide the latency of a load behind
+            // another block's arithmetic).
+            constexpr int RPP = NT / TI;             // rows per pass of the block
+            constexpr int UNR = 16;
+            const int img = tid % TI, rgrp = tid / TI;
             const float *const dense = a.dense_in ? *a.dense_in : nullptr;
-            bool contiguous = ctl.identity != 0 && !dense;
-#pragma unroll
-            for (int q = 0; q < IPT; ++q) {
-                const int j = j0 + sub * IPT + q;
-                const bool v = j < live_in;
-                my_valid |= (v ? 1u : 0u) << q;
-                const int jj = v ? j : j0;
-                const int src = ctl.identity ? jj : __ldg(a.slot + jj);
-                if (!ctl.identity && grp == 0 && v) move_id(ctl, a.ids0, a.ids1, j, src);
-                p[q] = dense ? dense + (size_t)src * a.n : a.yin + (size_t)(src >> 5) * a.tile_stride + (src & 31);
-            }
-            if (my_valid != kFull) contiguous = false;
+            const int j = j0 + img;
+            const bool valid = j < live_in;
+            my_valid = valid ? 1u << img : 0u;
+            const int src = ctl.identity ? (valid ? j : j0) : __ldg(a.slot + (valid ? j : j0));
             const ResLayer L0 = a.layers[0];
+            if (!ctl.identity && rgrp == 0 && valid) move_id(ctl, a.ids0, a.ids1, j, src);
+            const float *const pimg = dense ? dense + (size_t)src * a.n : a.yin + (size_t)(src >> 5) * a.tile_stride + (src & 31);
             const bool fast_dense = dense && !L0.rep && L0.v_in == a.n && (a.n & 3) == 0 && (reinterpret_cast<size_t>(dense) & 15) == 0;
             if (fast_dense) load_dense_rows<TI, NT, false, true>(dense, a.n, j0, live_in, L0.v_in, cur, a.clip);
-            for (int v = grp; v < L0.v_in && !fast_dense; v += CPI) {
-                // element of row r: r * 32 floats into a tile's column, r floats into a row-major image
-                size_t e = L0.rep ? (size_t)__ldg(L0.rep + v) : (size_t)v * 32;
-                if (dense) e >>= 5;
-                unsigned char *dst = cur + resident_phys_row(v) * RS + sub * TB;
+            for (int v0 = rgrp; v0 < L0.v_in && !fast_dense; v0 += RPP * UNR) {
+                float x[UNR];
+                int e[UNR];
 #pragma unroll
-                for (int h = 0; h < NQ; ++h) {
-                    float4 x;
-                    if (contiguous) {
-                        x = __ldg(reinterpret_cast<const float4 *>(p[0] + e) + h);
-                    } else {
-                        x.x = (my_valid >> (4 * h) & 1u) ? __ldg(p[4 * h + 0] + e) : 0.0f;
-                        x.y = (my_valid >> (4 * h) & 2u) ? __ldg(p[4 * h + 1] + e) : 0.0f;
-                        x.z = (my_valid >> (4 * h) & 4u) ? __ldg(p[4 * h + 2] + e) : 0.0f;
-                        x.w = (my_valid >> (4 * h) & 8u) ? __ldg(p[4 * h + 3] + e) : 0.0f;
-                    }
-                    *reinterpret_cast<float4 *>(dst + 16 * h) = x;
+                for (int t = 0; t < UNR; ++t) {
+                    const int v = min(v0 + t * RPP, L0.v_in - 1);
+                    // element of row r: r * 32 floats into a tile's column, r floats into a row-major image
+                    e[t] = L0.rep ? __ldg(L0.rep + v) : v * 32;
+                    if (dense) e[t] >>= 5;
+                }
+#pragma unroll
+                for (int t = 0; t < UNR; ++t) x[t] = valid ? __ldg(pimg + e[t]) : 0.0f;
+#pragma unroll
+                for (int t = 0; t < UNR; ++t) {
+                    const int v = v0 + t * RPP;
+                    if (v >= L0.v_in) break;
+                    *reinterpret_cast<float *>(cur + resident_phys_row(v) * RS + img * 4) = x[t];
                 }
             }
             // rows v_in .. even(v_in) + 1 are the zero rows padded table entries point at
@@ -429,9 +428,9 @@ resident_kernel(const ResArgs a) {
                 for (int h = 0; h < NQ; ++h)
                     *reinterpret_cast<float4 *>(cur + (r < ve ? resident_phys_row(r) : r) * RS + sub * TB + 16 * h) = make_float4(0, 0, 0, 0);
         }
-        // LPC divides 32, so every warp holds all sub-columns: the OR over a warp is the block's
-        // mask of valid images (bit i = image j0 + i), identical in every thread
-        unsigned int alive_prev = __reduce_or_sync(0xffffffffu, my_valid << (sub * IPT));
+        // TI divides 32, so every warp holds all images: the OR over a warp is the block's mask of valid images
+        // (bit i = image j0 + i), identical in every thread
+        unsigned int alive_prev = __reduce_or_sync(0xffffffffu, my_valid);
         __syncthreads();
 
         // ---- the layers of this chunk
@@ -543,16 +542,37 @@ resident_kernel(const ResArgs a) {
             const ResLayer LL = a.layers[li - 1];
             const int tile = j0 >> 5, lane0 = j0 & 31;
             float *out = a.yout + (size_t)tile * a.tile_stride + lane0 + sub * IPT;
-            for (int u = grp; u < last_classes; u += CPI) {
-                const unsigned char *src = cur + resident_phys_row(u) * RS + sub * TB;
+            if (LL.mem_ptr != nullptr && a.reps_only) {
+                // one row per class: the offsets of SU classes are looked up together (two dependent loads each)
+                constexpr int SU = 8;
+                for (int u0 = grp; u0 < last_classes; u0 += CPI * SU) {
+                    int o[SU];
 #pragma unroll
-                for (int h = 0; h < NQ; ++h) {
-                    const float4 y = *reinterpret_cast<const float4 *>(src + 16 * h);
-                    if (LL.mem_ptr == nullptr) {
-                        *reinterpret_cast<float4 *>(out + (size_t)u * 32 + 4 * h) = y;
-                    } else {
-                        const int mb = __ldg(LL.mem_ptr + u), me = a.reps_only ? mb + 1 : __ldg(LL.mem_ptr + u + 1);
-                        for (int m = mb; m < me; ++m) *reinterpret_cast<float4 *>(out + __ldg(LL.mem + m) + 4 * h) = y;
+                    for (int t = 0; t < SU; ++t) o[t] = __ldg(LL.mem_ptr + min(u0 + t * CPI, last_classes - 1));
+#pragma unroll
+                    for (int t = 0; t < SU; ++t) o[t] = __ldg(LL.mem + o[t]);
+#pragma unroll
+                    for (int t = 0; t < SU; ++t) {
+                        const int u = u0 + t * CPI;
+                        if (u >= last_classes) break;
+                        const unsigned char *src = cur + resident_phys_row(u) * RS + sub * TB;
+#pragma unroll
+                        for (int h = 0; h < NQ; ++h)
+                            *reinterpret_cast<float4 *>(out + o[t] + 4 * h) = *reinterpret_cast<const float4 *>(src + 16 * h);
+                    }
+                }
+            } else {
+                for (int u = grp; u < last_classes; u += CPI) {
+                    const unsigned char *src = cur + resident_phys_row(u) * RS + sub * TB;
+#pragma unroll
+                    for (int h = 0; h < NQ; ++h) {
+                        const float4 y = *reinterpret_cast<const float4 *>(src + 16 * h);
+                        if (LL.mem_ptr == nullptr) {
+                            *reinterpret_cast<float4 *>(out + (size_t)u * 32 + 4 * h) = y;
+                        } else {
+                            const int mb = __ldg(LL.mem_ptr + u), me = __ldg(LL.mem_ptr + u + 1);
+                            for (int m = mb; m < me; ++m) *reinterpret_cast<float4 *>(out + __ldg(LL.mem + m) + 4 * h) = y;
+                        }
                     }
                 }
             }
