@@ -2,9 +2,10 @@
 
     python -m graphchallenge21_b200.build [--force]
 
-Produces ``graphchallenge21_b200/libspdnn_b200.so`` (kernels + C ABI) and the drivers
+Produces ``graphchallenge21_b200/libspdnn_b200.so`` (kernels + C ABI), the drivers
 ``graphchallenge21_b200/bin/{network,multi_gpu,main}`` that keep the reference's command
-lines (src/network.cpp:58-64, src/multi_gpu.cpp:66-68).  nvcc cross-compiles without a GPU.
+lines (src/network.cpp:58-64, src/multi_gpu.cpp:66-68) and the measurement programs of
+``csrc/tools`` (``bin/add_chain_ceiling``).  nvcc cross-compiles without a GPU.
 """
 from __future__ import annotations
 
@@ -82,9 +83,28 @@ def build_drivers(force: bool = False) -> list[str]:
     return built
 
 
+def build_tools(force: bool = False) -> list[str]:
+    """Stand-alone measurement programs (csrc/tools): no library, no inputs; they print what the hardware sustains on
+    one inner loop of the library, the ceiling its profile is compared with."""
+    os.makedirs(BIN, exist_ok=True)
+    built = []
+    tdir = os.path.join(CSRC, "tools")
+    if not os.path.isdir(tdir):
+        return built
+    for f in sorted(os.listdir(tdir)):
+        if not f.endswith(".cu"):
+            continue
+        src, out = os.path.join(tdir, f), os.path.join(BIN, f[:-3])
+        if force or _stale(out, [src]):
+            _run([_nvcc(), *ARCH, *_host_cxx(), "-lineinfo", "-O3", "-std=c++17", "-o", out, src])
+        built.append(out)
+    return built
+
+
 def build_all(force: bool = False) -> str:
     lib = build_library(force)
     build_drivers(force)
+    build_tools(force)
     return lib
 
 
