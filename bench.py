@@ -366,11 +366,18 @@ def per_layer_line(net, y_dev, cfg, device, stream, first_id, want_survivors, pa
         loop_ms = sum(ms) / len(ms)
         achieved = r.algorithmic_bytes / (loop_ms * 1e-3) / 1e9
         fig = (profile_figures(n, pattern, "layer_kernel") or [{}])[0]
+        per_launch = r.algorithmic_bytes / max(int(r.loop_launches), 1)
+        # DRAM bytes per launch from the committed capture: as captured where the capture is this workload's steady state,
+        # else the captured launch's ratio of traffic to algorithmic bytes applied to this run's average launch
+        traffic = fig.get("dram_bytes_per_launch")
+        if traffic is None and fig.get("traffic_over_algorithmic") is not None:
+            traffic = fig["traffic_over_algorithmic"] * per_launch
         return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "peak_kind": peak_kind + " copy bandwidth (MEASURED_PEAKS.json hbm_gbs)", "kernel": "layer_kernel",
                 "launches_per_pass": int(r.loop_launches), "layer_loop_ms": loop_ms, "us_per_layer": loop_ms * 1e3 / L,
-                "passes": passes, "traffic": fig.get("dram_bytes_per_launch"), "traffic_source": fig.get("source"),
-                "algorithmic_bytes_per_launch": r.algorithmic_bytes / max(int(r.loop_launches), 1),
+                "passes": passes, "traffic": traffic, "traffic_source": fig.get("source"),
+                "traffic_over_algorithmic": fig.get("traffic_over_algorithmic"),
+                "algorithmic_bytes_per_launch": per_launch,
                 "note": "one launch per layer, activations in HBM between layers; layers after the first few work on the "
                         "survivors only, whose two activation buffers (%.0f MB) can partly stay in the 126 MB L2"
                         % (2.0 * r.survivors * n * 4 / 1e6)}
