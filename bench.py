@@ -634,13 +634,16 @@ def summarize(args, cfg, world, res, headline):
         "avg_launch_us": loop_ms * 1e3 / max(res["loop_launches"], 1),
         "algorithmic_bytes_per_launch": res["algo_bytes"] / max(res["loop_launches"], 1),
         "traffic": fig.get("dram_bytes_per_launch"),
-        "bound_actual": "instruction issue (float form: 32 sequential adds per output) and the latency of a dependent chain per layer "
+        "bound_actual": "the FP32 pipe (float form: 32 dependent adds per output, see fp32_pipe) and the latency of a dependent chain per layer "
                         "(bit form): activations stay in shared memory across the layers of a launch, one bit per activation once "
                         "saturated, so the HBM roofline of the per-layer formulation does not bind and frac exceeds 1; the kernels "
                         "that do stream HBM are in roofline_input_conversion and roofline_per_layer_kernel"
                         if res["group"] else "hbm",
         "issue_slots_busy_pct": fig.get("issue_slots_busy_pct"), "sm_active_cycles_per_layer": fig.get("sm_active_cycles_per_layer"),
         "ncu_source": fig.get("source"),
+        # the resource that does bind the dominant kernel's float form: additions per second against the FP32 pipe's peak
+        # and against what the same inner loop reaches alone (graphchallenge21_b200/bin/add_chain_ceiling)
+        "fp32_pipe": fig.get("fp32_pipe"),
         "ncu_kernels": [{k: r.get(k) for k in ("kernel", "form", "issue_slots_busy_pct", "sm_active_cycles_per_layer",
                                                 "dram_bytes_per_launch", "scale", "source")} for r in figs],
         "ncu_note": "figures from committed ncu captures of a smaller case of the same kernels, scaled as each record says; "
