@@ -60,7 +60,8 @@ def parse():
     p.add_argument("--no-two-contexts", action="store_true", help="skip the end-to-end loop that alternates two contexts")
     p.add_argument("--no-per-layer-line", action="store_true",
                    help="skip the extra line that times the per-layer kernel alone (SPDNN_RESIDENT=0) against the HBM roofline")
-    p.add_argument("--cpu-seconds", type=float, default=10.0, help="target CPU time of each cpu_baseline sample")
+    p.add_argument("--cpu-seconds", type=float, default=None,
+                   help="target CPU time of each cpu_baseline sample (default 10) and, when given, of each step of --impl reference")
     p.add_argument("--only-value", action="store_true",
                    help="time the HBM-resident passes only (no end-to-end loops, no extra lines): the short run a profiler capture wraps")
     return p.parse_args()
@@ -302,7 +303,7 @@ def main_reference(args):
     if rank != 0:
         return 0
     cfg = workload(args, world)
-    per_step = max(2.0, min(20.0, 90.0 / max(args.steps + args.warmup, 1)))
+    per_step = args.cpu_seconds or max(2.0, min(20.0, 90.0 / max(args.steps + args.warmup, 1)))
     for _ in range(args.warmup):
         run_cpu_reference(cfg, args.pattern, min(per_step, 2.0))
     vals, secs, last = [], 0.0, None
@@ -710,10 +711,10 @@ def main_ours(args):
             out.setdefault("also", {})["config%d" % idx] = {k: s2[k] for k in ("value", "ms_per_step", "config", "e2e", "layer_loop_ms",
                                                                                 "us_per_layer", "value_bit_matrix_input")}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cb = run_cpu_reference(cfg, args.pattern, args.cpu_seconds)
+        cb = run_cpu_reference(cfg, args.pattern, args.cpu_seconds or 10.0)
         cb.pop("seconds", None)
         out["cpu_baseline"] = cb
-        cp = run_cpu_port(cfg, args.pattern, args.cpu_seconds, prune=True)
+        cp = run_cpu_port(cfg, args.pattern, args.cpu_seconds or 10.0, prune=True)
         cp.pop("seconds", None)
         out["cpu_baseline_pruned"] = cp
         out["reference_gpu_loop"] = run_reference_gpu_loop(cfg, args.pattern, None)

@@ -222,3 +222,19 @@ def test_image_generator_does_not_depend_on_its_thread_count():
     b = synthetic_images(4096, 300, first_image=17, threads=4)
     assert np.array_equal(a, b)
     assert np.array_equal(synthetic_images(4096, 10, first_image=27), a[10:20])
+
+
+def test_reference_arm_prints_the_bench_line():
+    """`bench.py --impl reference`: the reference's CPU loop on a bounded sample, one JSON line with the keys of
+    the bench contract (runs without a GPU)."""
+    import json
+    import subprocess
+    import sys
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--config", "0", "--steps", "1",
+                        "--warmup", "0", "--cpu-seconds", "0.5"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["unit"] == "edges/s" and line["higher_is_better"] is True
+    assert line["value"] > 0 and line["cpu_baseline"]["kind"] in ("reference", "port") and line["cpu_baseline"]["cores"] >= 1
+    assert line["e2e"]["value"] == line["value"] and line["e2e"]["h2d_bytes_per_step"] == 0
+    assert line["config"]["workload"].startswith("N=1024")
