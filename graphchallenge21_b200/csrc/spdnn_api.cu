@@ -142,6 +142,7 @@ struct spdnn {
     bool bits_small = false;           // SPDNN_BITS_SMALL=1: the pre-pass also for chunks whose layers have at most 64 classes
                                        // (one warp per 32 images)
     bool table_cache = true;           // SPDNN_TABLE_CACHE=0: the pre-pass always streams its layer records
+    bool two_blocks = true;            // SPDNN_TWO_BLOCKS=0: ALT2 chunks keep the largest group of images per block even where it leaves one block per SM
     int alt2_threads = 0;              // SPDNN_ALT2_THREADS=256|512: block size of ALT2 chunks with 4 images per thread (0: by shared memory)
     int bits_threads = 0;              // SPDNN_BITS_THREADS: threads per block of the pre-pass (0: by the classes)
     int extra_launches = 0;            // pre-pass launches of the captured schedule
@@ -577,20 +578,29 @@ std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
                     st.max_classes = maxc;
                     st.stride = alt2_stream_stride(maxc);
                     st.rows_w = std::max(rows, 32);
-                    auto afits = [&](int gs, int tr) {
-                        return alt2_smem_bytes(ti, rows, st.stride, gs, tr) + 2048 <= (size_t)c->smem_optin;
-                    };
-                    st.tring = 0; st.gshift = 0;
-                    // word buffers of the bit form: as many as one activation buffer holds, 33 at most (under
-                    // two the chunk runs without the bit form)
-                    st.wring = (int)std::min<size_t>((size_t)c->word_ring_max, ((size_t)rows * ti * 4) / ((size_t)st.rows_w * 4));
                     // staging may take a quarter of the shared memory at most, so that the blocks per SM stay
-                    // what the activations allow
-                    if (c->stage_tables)
-                        for (int gs = 5; gs >= 0 && !st.tring; --gs)
-                            for (int tr = 4; tr >= 2 && !st.tring; tr /= 2)
-                                if ((1 << gs) <= c->table_group_max && ((1 << gs) < 2 * f || gs == 0) && tr <= c->table_ring_max && afits(gs, tr) &&
-                                    (size_t)tr * ((size_t)st.stride << gs) <= (size_t)c->smem_optin / 4) { st.gshift = gs; st.tring = tr; }
+                    // what the activations allow; word buffers of the bit form: as many as one activation buffer
+                    // holds, 33 at most (under two the chunk runs without the bit form)
+                    auto stage = [&](int t_i, size_t limit) {
+                        st.tring = 0; st.gshift = 0;
+                        st.wring = (int)std::min<size_t>((size_t)c->word_ring_max, ((size_t)rows * t_i * 4) / ((size_t)st.rows_w * 4));
+                        if (c->stage_tables)
+                            for (int gs = 5; gs >= 0 && !st.tring; --gs)
+                                for (int tr = 4; tr >= 2 && !st.tring; tr /= 2)
+                                    if ((1 << gs) <= c->table_group_max && ((1 << gs) < 2 * f || gs == 0) && tr <= c->table_ring_max &&
+                                        alt2_smem_bytes(t_i, rows, st.stride, gs, tr) + 2048 <= limit &&
+                                        (size_t)tr * ((size_t)st.stride << gs) <= (size_t)c->smem_optin / 4) { st.gshift = gs; st.tring = tr; }
+                        return alt2_smem_bytes(t_i, rows, st.stride, st.gshift, st.tring);
+                    };
+                    const size_t need = stage(ti, (size_t)c->smem_optin);
+                    // A block that has an SM to itself cannot hide the loading and storing of its rows, nor the tail of a
+                    // layer, behind another block's arithmetic: where half the images per block (and tables staged at
+                    // least four layers at a time) let two blocks share an SM, that is faster (measured at 16384 neurons).
+                    if (c->two_blocks && ipt == 4 && ti >= 8 && ti / 2 <= c->res_ti_max && need * 2 + 4096 > (size_t)c->smem_optin) {
+                        const size_t half = stage(ti / 2, ((size_t)c->smem_optin - 4096) / 2);
+                        if (st.tring > 0 && st.gshift >= 2 && half * 2 + 4096 <= (size_t)c->smem_optin) ti /= 2;
+                        else stage(ti, (size_t)c->smem_optin);
+                    }
                     // Pre-pass for tiles that are saturated already (bits_kernel): layers of more than one pass of 64
                     // classes, where the float buffers leave this kernel's own bit form few images per block.  Not
                     // before the first two chunks of a pass: the challenge networks saturate around layer 30, and a
@@ -1051,6 +1061,7 @@ int spdnn_create(spdnn_t **out, int device, int neurons, int layers, float bias,
         if (const char *e = getenv("SPDNN_COUNT_FRONT")) c->count_front = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BITS_KERNEL")) c->bits_prepass = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BITS_FIRST")) c->bits_first_chunk = atoi(e) != 0;
+        if (const char *e = getenv("SPDNN_TWO_BLOCKS")) c->two_blocks = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_TABLE_CACHE")) c->table_cache = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_BITS_SMALL")) c->bits_small = atoi(e) != 0;
         if (const char *e = getenv("SPDNN_ALT2_THREADS")) c->alt2_threads = atoi(e) == 512 ? 512 : atoi(e) == 256 ? 256 : 0;

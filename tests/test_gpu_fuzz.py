@@ -22,7 +22,7 @@ SWITCHES = [{}, {"SPDNN_RESIDENT_TI": "16"}, {"SPDNN_RESIDENT_TI": "8"}, {"SPDNN
             {"SPDNN_BINARY_FRONT": "0"}, {"SPDNN_RESIDENT": "0"},
             {"SPDNN_BITS_FIRST": "1", "SPDNN_TABLE_CACHE": "0"}, {"SPDNN_COUNT_FRONT": "0"},
             {"SPDNN_BITS_SMALL": "1"}, {"SPDNN_BITS_SMALL": "1", "SPDNN_BITS_FIRST": "1"}, {"SPDNN_EXACT_SHORTCUT": "1"},
-            {"SPDNN_EXACT_SHORTCUT": "1", "SPDNN_BIT_FORM": "0"}, {"SPDNN_ALT2_THREADS": "256"}]
+            {"SPDNN_EXACT_SHORTCUT": "1", "SPDNN_BIT_FORM": "0"}, {"SPDNN_ALT2_THREADS": "256"}, {"SPDNN_TWO_BLOCKS": "0"}]
 
 
 @pytest.mark.parametrize("seed", [11, 12, 13])

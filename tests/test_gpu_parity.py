@@ -213,7 +213,7 @@ def _large_case(oracle, bias, clip, n, L, b):
                                  {"SPDNN_BITS_KERNEL": "0"}, {"SPDNN_BITS_FIRST": "1"}, {"SPDNN_BITS_FIRST": "1", "SPDNN_BITS_THREADS": "128"},
                                  {"SPDNN_BITS_FIRST": "1", "SPDNN_STAGE_TABLES": "0"}, {"SPDNN_BITS_FIRST": "1", "SPDNN_TABLE_GROUP": "1", "SPDNN_TABLE_RING": "2"},
                                  {"SPDNN_BITS_FIRST": "1", "SPDNN_CHUNK_FIRST": "1", "SPDNN_CHUNK_MAX": "3"},
-                                 {"SPDNN_BITS_FIRST": "1", "SPDNN_TABLE_CACHE": "0"},
+                                 {"SPDNN_BITS_FIRST": "1", "SPDNN_TABLE_CACHE": "0"}, {"SPDNN_TWO_BLOCKS": "0"},
                                  {"SPDNN_COUNT_FRONT": "0"}, {"SPDNN_ALT2_THREADS": "256"},
                                  {"SPDNN_ALT2_THREADS": "256", "SPDNN_RESIDENT_TI": "8", "SPDNN_BITS_KERNEL": "0"}],
                          ids=lambda e: ",".join(f"{k[6:]}={v}" for k, v in e.items()) or "default")
