@@ -651,10 +651,14 @@ std::vector<Step> plan_steps(spdnn *c, bool dense_first) {
         if (st.ti) {
             ++resident_chunks;
             if (resident_chunks < (int)c->chunk_list.size()) chunk = c->chunk_list[resident_chunks];
-            // a chunk with a bits_kernel pre-pass runs its saturated tiles at a fraction of the float form's cost and
-            // dead images cost it nothing: from the first such chunk on the rest of the network is one chunk
+            // A chunk with a bits_kernel pre-pass runs its saturated tiles at a fraction of the float form's cost and
+            // dead images cost it nothing, so such chunks can be long.  But a tile that is NOT saturated when the chunk
+            // starts is the float form's for the whole chunk (at 65536 neurons about 1.4 us per layer and tile against
+            // 0.3): the first chunk with a pre-pass is as short as the chunk before it, and only the one after it takes
+            // the rest of the network -- a tile that saturates a few layers late then costs tens of layers, not
+            // thousands (measured: one such tile among 7500 images made a pass 2.6 ms longer).
             else if ((st.max_classes > 64 || c->bits_small) && st.max_classes > 0 && alt2_chunks >= 1 && c->bits_prepass && c->bit_form && c->clip > 0.0f && !c->chunk_growth_set)
-                chunk = c->chunk_max;
+                chunk = alt2_chunks >= 2 ? c->chunk_max : chunk;
             else chunk = std::min(chunk * (st.max_classes > 0 ? c->chunk_growth : c->chunk_growth_generic), c->chunk_max);
         }
         if (st.ti && st.max_classes > 0) ++alt2_chunks;
