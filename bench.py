@@ -573,6 +573,17 @@ def gather_ints(v, world):
     return [int(x.item()) for x in out]
 
 
+def gather_floats(v, world):
+    import torch
+    import torch.distributed as dist
+    if world == 1:
+        return [float(v)]
+    t = torch.tensor([float(v)], dtype=torch.float64, device="cuda")
+    out = [torch.zeros_like(t) for _ in range(world)]
+    dist.all_gather(out, t)
+    return [float(x.item()) for x in out]
+
+
 def summarize(args, cfg, world, res, headline):
     """Whole-job figures of one workload (rank 0 uses them); every rank must call it (collectives inside)."""
     n, L = cfg["neurons"], cfg["layers"]
@@ -580,6 +591,8 @@ def summarize(args, cfg, world, res, headline):
     mx = dict(zip(keys, reduce_max([res.get(k) for k in keys], world)))
     per_rank_b = gather_ints(res["b"], world)
     per_rank_surv = gather_ints(res["survivors"], world)
+    per_rank_ms = gather_floats(res["ms"] / max(args.steps, 1), world)          # the slowest rank sets `value`
+    per_rank_loop = gather_floats(res["infer_ms"], world)
     total = sum(per_rank_b)
     edges_step = float(total) * n * 32.0 * L
     steps = args.steps
@@ -591,6 +604,7 @@ def summarize(args, cfg, world, res, headline):
         "value": edges_step * steps / (mx["ms"] * 1e-3), "ms_per_step": mx["ms"] / steps,
         "config": workload_config(cfg, args, world, {
             "images_per_gpu": per_rank_b, "survivors_per_gpu": per_rank_surv, "survivors_total": int(len(res["all_cats"])),
+            "ms_per_step_per_gpu": [round(x, 4) for x in per_rank_ms], "layer_loop_ms_per_gpu": [round(x, 4) for x in per_rank_loop],
             "live_after_layer_rank0": {str(i): int(live[i]) for i in sorted({0, 1, 2, 4, 8, 16, 32, 64, 128, L - 1}) if i < L},
             "classes_per_layer": res["classes"], "resident_input": "dense fp32 batch x N in HBM (the reference's A_d)",
             "l2": ("inputs larger than L2 (%.0f MB per GPU and step), no flush" % (res["b"] * n * 4 / 1e6)) if res["b"] * n * 4 > 126e6
