@@ -328,12 +328,30 @@ __global__ void __launch_bounds__(kBitsMaxThreads, 1) bits_kernel(const ResArgs 
     // ---- the survivors' rows back to floats: all member rows, or the one row per class the next chunk reads
     const ResLayer LL = a.layers[li - 1];
     float *out = a.yout + (size_t)tile * a.tile_stride + lane;
+    if (LL.mem_ptr != nullptr && a.reps_only) {
+        // one row per class: the offsets of SU rows are looked up together (two dependent loads each) before their stores
+        constexpr int SU = 8;
+        for (int u0 = warp; u0 < last_classes; u0 += nwarps * SU) {
+            int o[SU];
+#pragma unroll
+            for (int t = 0; t < SU; ++t) o[t] = __ldg(LL.mem_ptr + min(u0 + t * nwarps, last_classes - 1));
+#pragma unroll
+            for (int t = 0; t < SU; ++t) o[t] = __ldg(LL.mem + o[t]);
+#pragma unroll
+            for (int t = 0; t < SU; ++t) {
+                const int u = u0 + t * nwarps;
+                if (u >= last_classes) break;
+                out[o[t]] = ((wc[u] >> lane) & 1u) ? a.clip : 0.0f;
+            }
+        }
+        return;
+    }
     for (int u = warp; u < last_classes; u += nwarps) {
         const float y = ((wc[u] >> lane) & 1u) ? a.clip : 0.0f;
         if (LL.mem_ptr == nullptr) {
             out[(size_t)u * 32] = y;
         } else {
-            const int mb = __ldg(LL.mem_ptr + u), me = a.reps_only ? mb + 1 : __ldg(LL.mem_ptr + u + 1);
+            const int mb = __ldg(LL.mem_ptr + u), me = __ldg(LL.mem_ptr + u + 1);
             for (int m = mb; m < me; ++m) out[__ldg(LL.mem + m)] = y;
         }
     }
